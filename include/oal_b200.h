@@ -1,0 +1,157 @@
+/*
+ * oal_b200 -- C ABI of the B200 (sm_100a) implementation of OAL's causal
+ * grouped-quadratic linear attention, forward and backward.
+ *
+ * This is the drop-in boundary for one path of the reference project
+ * (wuqianyue09/OAL): everything the reference computes between
+ *   oal_attention/hd_block_gemm_autograd.py:85-204   (_HDParallelBlockGemmFunction)
+ * and its dense-contraction seam
+ *   oal_attention/hd_block_gemm_contractions.py:26-92 (_bmm_fp32 / _bmm_add_fp32)
+ *   oal_attention/csrc/hd_cublas_compat.cpp:100-203   (bmm_fp32, the only native op)
+ * is replaced by the entry points below.  Signatures use plain pointers and
+ * sizes only; every pointer is a CUDA device pointer unless stated otherwise
+ * and the library never allocates or frees device memory: the caller owns the
+ * inputs, the outputs and one workspace blob whose size is returned by
+ * oal_workspace_bytes().  All launches go to the stream that is passed in.
+ *
+ * Return value of every int function: 0 on success, a negative OAL_ERR_* code
+ * on a contract violation (oal_last_error_string() describes it).  Numerical
+ * conditions (non-finite result, non-positive denominator, a bounded wait that
+ * ran out inside a kernel) are not return codes: kernels OR them into the
+ * caller's device status word, which the host reads at the same point where
+ * the reference synchronises (oal_attention/hd_block_gemm_runtime.py:392-408).
+ */
+#ifndef OAL_B200_H
+#define OAL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OAL_HEAD_DIM 64      /* kernels are specialised for D = Dv = 64; the host zero-pads smaller heads */
+#define OAL_MAX_GROUPS 16    /* dimension groups per query head handled by the kernels */
+#define OAL_E_PAD 80         /* [v | 1] rows (65 values) padded to a multiple of 16 */
+
+enum { OAL_DTYPE_F32 = 0, OAL_DTYPE_BF16 = 1, OAL_DTYPE_F16 = 2 };
+
+/* precision modes of the reference (oal_attention/hd_block_gemm_plan.py:52) */
+enum {
+  OAL_PRECISION_FP32_IEEE = 0,      /* fp32 arithmetic throughout, exact causal pair sums            */
+  OAL_PRECISION_BF16_TENSORCORE = 1 /* bf16 operands, fp32 accumulation, chunked state scan (tcgen05) */
+};
+
+enum {
+  OAL_OK = 0,
+  OAL_ERR_ARGUMENT = -1,   /* NULL pointer, bad size, unsupported geometry  -> ValueError */
+  OAL_ERR_DTYPE = -2,      /* unsupported dtype / precision combination     -> TypeError  */
+  OAL_ERR_WORKSPACE = -3,  /* workspace too small                            -> ValueError */
+  OAL_ERR_CUDA = -4        /* a CUDA runtime call failed                     -> RuntimeError */
+};
+
+/* bits of the device status word */
+enum {
+  OAL_STATUS_NONFINITE = 1,      /* numerator or denominator not finite                    */
+  OAL_STATUS_DENOMINATOR = 2,    /* denominator <= 0                                        */
+  OAL_STATUS_WAIT_TIMEOUT = 4    /* a bounded mbarrier wait inside a kernel gave up         */
+};
+
+/* gradient request mask, same order as the reference's requested_gradient_mask
+ * (oal_attention/hd_block_gemm_adapters.py:27-43): q, k, v, A, B, C */
+enum { OAL_GRAD_Q = 1, OAL_GRAD_K = 2, OAL_GRAD_V = 4, OAL_GRAD_COEF = 8 };
+
+typedef struct OalProblem {
+  int32_t batch;        /* B                                                            */
+  int32_t q_heads;      /* Hq                                                           */
+  int32_t kv_heads;     /* Hkv, Hq % Hkv == 0; query head h reads KV head h / (Hq/Hkv)  */
+  int32_t seq_len;      /* N >= 1 (ragged tails are masked)                             */
+  int32_t head_dim;     /* must be OAL_HEAD_DIM                                         */
+  int32_t value_dim;    /* must be OAL_HEAD_DIM                                         */
+  int32_t groups;       /* G: second extent of B [Hq,G] and C [Hq,G,G], 1..OAL_MAX_GROUPS */
+  int32_t chunk;        /* tokens per chunk of the state scan: 128 (bf16_tensorcore)    */
+  int32_t io_dtype;     /* dtype of q, k, v and of dq, dk, dv                           */
+  int32_t out_dtype;    /* dtype of out and of the upstream gradient of out             */
+  int32_t precision;    /* OAL_PRECISION_*                                              */
+  int32_t grad_mask;    /* OAL_GRAD_* bits requested from oal_backward                  */
+  float scale;          /* q is multiplied by this before anything else                 */
+  float floor;          /* normalisation floor: out = num / max(den, floor)             */
+} OalProblem;
+
+/* Bytes of workspace oal_forward (phase 0) / oal_backward (phase 1) need, and
+ * bytes of the saved chunk-state buffer the forward hands to the backward
+ * (phase 2; 0 in fp32_ieee mode).  Replaces the reference's buffer planner
+ * (oal_attention/hd_block_gemm_buffers.py:108-368).  Returns < 0 on error. */
+int64_t oal_workspace_bytes(const OalProblem* problem, int phase);
+
+/*
+ * Forward.  Replaces _hd_parallel_block_gemm_impl
+ * (oal_attention/hd_block_gemm_runtime.py:617-805) including feature building,
+ * block totals, the exclusive scan, the intra-chunk scores and the fused
+ * normalisation (oal_attention/hd_block_gemm_normalization_ops.py:113).
+ *
+ *   q [B,Hq,N,64], k [B,Hkv,N,64], v [B,Hkv,N,64]   io_dtype, row-major contiguous
+ *   dim_perm   int32 [Hq,64]   dims of each head sorted by group id
+ *   group_start int32 [Hq,OAL_MAX_GROUPS+1]  offsets into dim_perm; group g of head h
+ *              owns dim_perm[h, group_start[h,g] : group_start[h,g+1]]
+ *   coef_a fp32 [Hq], coef_b fp32 [Hq,G], coef_c fp32 [Hq,G,G] (symmetric)
+ *   out [B,Hq,N,64] out_dtype; num fp32 [B,Hq,N,64]; den fp32 [B,Hq,N]
+ *   saved_state: oal_workspace_bytes(problem, 2) bytes kept for the backward
+ *              (may be NULL when that size is 0)
+ *   state_in / state_total: sequence parallelism, both may be NULL.  state_in is
+ *              the fp32 state [B,Hkv,OAL_STATE_ROWS,OAL_E_PAD] accumulated by the
+ *              ranks that own earlier tokens; state_total receives this rank's own
+ *              contribution in the same layout (see oal_forward_local_state).
+ */
+int oal_forward(const OalProblem* problem, const void* q, const void* k, const void* v,
+                const int32_t* dim_perm, const int32_t* group_start, const float* coef_a,
+                const float* coef_b, const float* coef_c, void* out, float* num, float* den,
+                void* saved_state, const float* state_in, void* workspace, size_t workspace_bytes,
+                int32_t* status, void* stream);
+
+/*
+ * Backward.  Replaces _hd_parallel_block_gemm_autograd_backward_impl
+ * (oal_attention/hd_block_gemm_autograd.py:207-347): normalisation VJP
+ * (hd_block_gemm_backward.py:191-308), dCarry + reverse scan (:764-908), the
+ * shared-wave VJP (:1455-1992) and the feature folds / coefficient partial
+ * sums (hd_block_gemm_feature_backward.py:59-474).
+ *
+ *   grad_out out_dtype [B,Hq,N,64] or NULL; grad_num fp32 [B,Hq,N,64] or NULL;
+ *   grad_den fp32 [B,Hq,N] or NULL
+ *   dq, dk, dv io_dtype (each may be NULL if not requested in grad_mask)
+ *   d_coef_a fp32 [Hq], d_coef_b fp32 [Hq,G], d_coef_c fp32 [Hq,G,G] (symmetric
+ *   closed form sum dW s_g s_g'); NULL unless OAL_GRAD_COEF
+ *   dstate_in: sequence parallelism, gradient of the state arriving from the
+ *   ranks that own later tokens, or NULL.
+ */
+int oal_backward(const OalProblem* problem, const void* q, const void* k, const void* v,
+                 const int32_t* dim_perm, const int32_t* group_start, const float* coef_a,
+                 const float* coef_b, const float* coef_c, const float* num, const float* den,
+                 const void* saved_state, const void* grad_out, const float* grad_num,
+                 const float* grad_den, void* dq, void* dk, void* dv, float* d_coef_a,
+                 float* d_coef_b, float* d_coef_c, const float* dstate_in, void* workspace,
+                 size_t workspace_bytes, int32_t* status, void* stream);
+
+/* Text of the last error returned on the calling thread (host pointer, never NULL). */
+const char* oal_last_error_string(void);
+
+/*
+ * Self-test of the tensor-core building blocks (no counterpart in the reference, whose
+ * only native op delegates to cuBLAS: oal_attention/csrc/hd_cublas_compat.cpp:177-200).
+ * Runs one 128 x n x k bf16 GEMM with fp32 accumulation through tcgen05.mma:
+ *   mode 0: a [128,k], b [n,k] (K contiguous)      d = a b^T
+ *   mode 1: a [k,128], b [k,n] (M / N contiguous)  d = a^T b
+ *   mode 2: as mode 0 with the A operand staged in tensor memory
+ * n: multiple of 16 in 16..256, k: multiple of 16 in 16..128; a, b bf16, d fp32 [128,n].
+ */
+int oal_selftest_umma(int mode, int n, int k, const void* a, const void* b, float* d, int32_t* status,
+                      void* stream);
+
+/* Library / build identification: "oal_b200 <version> sm_100a". Host pointer. */
+const char* oal_version_string(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OAL_B200_H */

@@ -1,0 +1,179 @@
+// C ABI of oal_b200: argument checking, workspace carving and kernel sequencing.
+#include <stdio.h>
+#include <string.h>
+
+#include "oal_common.cuh"
+#include "oal_kernels.h"
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, const char* detail = "") {
+  snprintf(g_error, sizeof(g_error), fmt, detail);
+  return code;
+}
+
+int fail_cuda(cudaError_t e, const char* where) {
+  snprintf(g_error, sizeof(g_error), "%s: %s", where, cudaGetErrorString(e));
+  return OAL_ERR_CUDA;
+}
+
+size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct Carver {
+  char* base;
+  size_t off = 0;
+  explicit Carver(void* p) : base(static_cast<char*>(p)) {}
+  template <class T>
+  T* take(size_t count) {
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += align_up(count * sizeof(T));
+    return p;
+  }
+};
+
+int check_problem(const OalProblem* p) {
+  if (!p) return fail(OAL_ERR_ARGUMENT, "problem is NULL");
+  if (p->batch < 1 || p->q_heads < 1 || p->kv_heads < 1 || p->seq_len < 1)
+    return fail(OAL_ERR_ARGUMENT, "batch, head counts and seq_len must be positive");
+  if (p->q_heads % p->kv_heads) return fail(OAL_ERR_ARGUMENT, "q_heads must be divisible by kv_heads");
+  if (p->head_dim != OAL_HEAD_DIM || p->value_dim != OAL_HEAD_DIM)
+    return fail(OAL_ERR_ARGUMENT, "head_dim and value_dim must be 64 (the host pads smaller heads)");
+  if (p->groups < 1 || p->groups > OAL_MAX_GROUPS)
+    return fail(OAL_ERR_ARGUMENT, "groups must be in 1..16");
+  if (p->io_dtype < 0 || p->io_dtype > 2 || p->out_dtype < 0 || p->out_dtype > 2)
+    return fail(OAL_ERR_DTYPE, "io_dtype / out_dtype must be fp32, bf16 or fp16");
+  if (p->precision != OAL_PRECISION_FP32_IEEE && p->precision != OAL_PRECISION_BF16_TENSORCORE)
+    return fail(OAL_ERR_DTYPE, "unknown precision mode");
+  if (p->precision == OAL_PRECISION_BF16_TENSORCORE) {
+    if (p->io_dtype != OAL_DTYPE_BF16) return fail(OAL_ERR_DTYPE, "bf16_tensorcore requires bf16 q, k, v");
+    if (p->chunk != 128) return fail(OAL_ERR_ARGUMENT, "bf16_tensorcore requires chunk == 128");
+  }
+  if (!(p->floor > 0.f)) return fail(OAL_ERR_ARGUMENT, "floor must be positive");
+  return OAL_OK;
+}
+
+struct BackwardSpace {
+  float* g;
+  float* coef_pairs;
+  size_t bytes;
+};
+
+BackwardSpace carve_backward(const OalProblem* p, void* ws) {
+  Carver c(ws);
+  BackwardSpace s;
+  const size_t rows = (size_t)p->batch * p->q_heads * p->seq_len;
+  s.g = c.take<float>(rows * oal::EP);
+  s.coef_pairs = c.take<float>((size_t)p->batch * p->q_heads * oal::pairs_tiles(p->seq_len) * oal::NCOEF);
+  s.bytes = c.off;
+  return s;
+}
+
+oal::PairArgs base_args(const OalProblem* p, const void* q, const void* k, const void* v,
+                        const int32_t* perm, const int32_t* gstart, const float* A, const float* B,
+                        const float* C, int32_t* status) {
+  oal::PairArgs a;
+  memset(&a, 0, sizeof(a));
+  a.B = p->batch; a.Hq = p->q_heads; a.Hkv = p->kv_heads; a.N = p->seq_len; a.G = p->groups;
+  a.window = 0;
+  a.io_dt = p->io_dtype; a.out_dt = p->out_dtype;
+  a.scale = p->scale; a.floor = p->floor;
+  a.q = q; a.k = k; a.v = v;
+  a.dim_perm = perm; a.group_start = gstart;
+  a.A = A; a.Bc = B; a.Cc = C;
+  a.status = status;
+  return a;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* oal_last_error_string(void) { return g_error; }
+
+const char* oal_version_string(void) { return "oal_b200 0.1 sm_100a"; }
+
+int64_t oal_workspace_bytes(const OalProblem* p, int phase) {
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (phase < 0 || phase > 2) return fail(OAL_ERR_ARGUMENT, "phase must be 0 (forward), 1 (backward) or 2 (saved state)");
+  if (p->precision == OAL_PRECISION_FP32_IEEE) {
+    if (phase == 1) return (int64_t)carve_backward(p, nullptr).bytes;
+    return 0;
+  }
+  return fail(OAL_ERR_ARGUMENT, "bf16_tensorcore is not available in this build");
+}
+
+int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
+                const int32_t* group_start, const float* coef_a, const float* coef_b, const float* coef_c,
+                void* out, float* num, float* den, void* saved_state, const float* state_in,
+                void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (!q || !k || !v || !dim_perm || !group_start || !coef_a || !coef_b || !coef_c || !out || !num || !den || !status)
+    return fail(OAL_ERR_ARGUMENT, "oal_forward: NULL tensor pointer");
+  (void)saved_state; (void)workspace; (void)workspace_bytes;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p->precision == OAL_PRECISION_FP32_IEEE) {
+    if (state_in) return fail(OAL_ERR_ARGUMENT, "fp32_ieee mode keeps no chunk state: state_in must be NULL");
+    oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
+    a.out = out; a.num = num; a.den = den; a.accumulate = 0;
+    cudaError_t e = oal::pairs_forward(a, st);
+    if (e != cudaSuccess) return fail_cuda(e, "forward pair kernel");
+    return OAL_OK;
+  }
+  return fail(OAL_ERR_ARGUMENT, "bf16_tensorcore is not available in this build");
+}
+
+int oal_backward(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
+                 const int32_t* group_start, const float* coef_a, const float* coef_b, const float* coef_c,
+                 const float* num, const float* den, const void* saved_state, const void* grad_out,
+                 const float* grad_num, const float* grad_den, void* dq, void* dk, void* dv,
+                 float* d_coef_a, float* d_coef_b, float* d_coef_c, const float* dstate_in, void* workspace,
+                 size_t workspace_bytes, int32_t* status, void* stream) {
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (!q || !k || !v || !dim_perm || !group_start || !coef_a || !coef_b || !coef_c || !num || !den || !status)
+    return fail(OAL_ERR_ARGUMENT, "oal_backward: NULL tensor pointer");
+  const int mask = p->grad_mask;
+  if ((mask & OAL_GRAD_Q) && !dq) return fail(OAL_ERR_ARGUMENT, "dq requested but NULL");
+  if ((mask & OAL_GRAD_K) && !dk) return fail(OAL_ERR_ARGUMENT, "dk requested but NULL");
+  if ((mask & OAL_GRAD_V) && !dv) return fail(OAL_ERR_ARGUMENT, "dv requested but NULL");
+  if ((mask & OAL_GRAD_COEF) && (!d_coef_a || !d_coef_b || !d_coef_c))
+    return fail(OAL_ERR_ARGUMENT, "coefficient gradients requested but NULL");
+  (void)saved_state;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p->precision == OAL_PRECISION_FP32_IEEE) {
+    if (dstate_in) return fail(OAL_ERR_ARGUMENT, "fp32_ieee mode keeps no chunk state: dstate_in must be NULL");
+    BackwardSpace s = carve_backward(p, workspace);
+    if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_backward: workspace too small");
+    const size_t rows = (size_t)p->batch * p->q_heads * p->seq_len;
+    cudaError_t e = oal::norm_vjp(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor, s.g, rows, st);
+    if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
+    oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
+    a.g = s.g;
+    if (mask & (OAL_GRAD_Q | OAL_GRAD_COEF)) {
+      a.dq = (mask & OAL_GRAD_Q) ? dq : nullptr;
+      a.coef_partial = (mask & OAL_GRAD_COEF) ? s.coef_pairs : nullptr;
+      e = oal::pairs_backward_q(a, st);
+      if (e != cudaSuccess) return fail_cuda(e, "backward query-side pair kernel");
+      if (mask & OAL_GRAD_COEF) {
+        e = oal::reduce_coefs(s.coef_pairs, oal::pairs_tiles(p->seq_len), nullptr, 0, p->batch, p->q_heads,
+                              p->groups, d_coef_a, d_coef_b, d_coef_c, st);
+        if (e != cudaSuccess) return fail_cuda(e, "coefficient reduction kernel");
+      }
+    }
+    if (mask & (OAL_GRAD_K | OAL_GRAD_V)) {
+      a.dq = nullptr; a.coef_partial = nullptr;
+      a.dk = (mask & OAL_GRAD_K) ? dk : nullptr;
+      a.dv = (mask & OAL_GRAD_V) ? dv : nullptr;
+      e = oal::pairs_backward_kv(a, st);
+      if (e != cudaSuccess) return fail_cuda(e, "backward key/value-side pair kernel");
+    }
+    return OAL_OK;
+  }
+  return fail(OAL_ERR_ARGUMENT, "bf16_tensorcore is not available in this build");
+}
+
+}  // extern "C"

@@ -1,0 +1,43 @@
+// Internal launch interface between the C-ABI translation unit and the kernel files.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace oal {
+
+// Arguments of the token-pair kernels (oal_pairs.cu).
+struct PairArgs {
+  int B, Hq, Hkv, N, G;
+  int window;            // 0: whole causal prefix; >0: keys of the query's own chunk only (multiple of 64)
+  int io_dt, out_dt;
+  float scale, floor;
+  const void *q, *k, *v;
+  const int32_t *dim_perm, *group_start;
+  const float *A, *Bc, *Cc;
+  int32_t* status;
+  // forward
+  void* out;
+  float *num, *den;
+  int accumulate;        // num/den already hold the cross-chunk term
+  // backward
+  const float* g;        // [B,Hq,N,80] augmented upstream gradient
+  void *dq, *dk, *dv;
+  const float *dq_init, *dk_init, *dv_init;   // fp32 cross-chunk parts to add, or null
+  float* coef_partial;   // [B][Hq][tiles][NCOEF] or null
+};
+
+cudaError_t pairs_forward(const PairArgs& a, cudaStream_t st);
+cudaError_t pairs_backward_q(const PairArgs& a, cudaStream_t st);
+cudaError_t pairs_backward_kv(const PairArgs& a, cudaStream_t st);
+int pairs_tiles(int n);
+
+cudaError_t norm_vjp(const void* grad_out, int out_dt, const float* grad_num, const float* grad_den,
+                     const float* num, const float* den, float floor_v, float* g, size_t rows,
+                     cudaStream_t st);
+
+cudaError_t reduce_coefs(const float* p0, int tiles0, const float* p1, int tiles1, int B, int Hq, int G,
+                         float* dA, float* dB, float* dC, cudaStream_t st);
+
+}  // namespace oal

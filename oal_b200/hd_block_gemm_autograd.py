@@ -1,0 +1,225 @@
+"""autograd boundary of the operator.
+
+Counterpart of the reference's ``_HDParallelBlockGemmFunction``
+(oal_attention/hd_block_gemm_autograd.py:85-204): three differentiable outputs
+``(out, numerator, denominator)``, first-order backward only, gradients returned
+in the input dtypes, the plan's gradient mask must equal ``needs_input_grad``.
+The tensor inputs are the group-aware coefficients ``A [Hq]``, ``B [Hq,G]``,
+``C [Hq,G,G]`` (what the sibling Function of the reference takes,
+oal_attention/triton/grouped_quadratic_backward.py:136-151): with the groups
+known, the kernels can form the intra-chunk weights from G small dot products.
+The expansion factor -> (A, B, C) stays ordinary differentiable torch code in
+the adapters, as in the reference (hd_block_gemm_adapters.py:278-301).
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .hd_block_gemm import HDParallelBlockPlan, make_problem
+
+_DENOMINATOR_ERROR = "HD Block-GEMM denominator must be finite and strictly positive"
+
+
+@dataclass(frozen=True)
+class GroupTables:
+    """Device-resident description of the dimension groups of every query head."""
+
+    dim_perm: torch.Tensor      # int32 [Hq, 64]: dims sorted by group id (padded dims first, group 0)
+    group_start: torch.Tensor   # int32 [Hq, 17]: group g owns dim_perm[h, start[g]:start[g+1]]
+    group_count: int            # G = extent of B / C
+
+
+def build_group_tables(groups: torch.Tensor, group_count: int) -> GroupTables:
+    """``groups`` int [Hq, D] (D <= 64) -> sorted permutation + offsets on the same device."""
+    hq, d = groups.shape
+    g64 = groups.to(torch.int64)
+    if d < _lib.HEAD_DIM:
+        g64 = F.pad(g64, (0, _lib.HEAD_DIM - d), value=0)
+    perm = torch.argsort(g64, dim=1, stable=True).to(torch.int32)
+    counts = torch.zeros(hq, _lib.MAX_GROUPS, dtype=torch.int64, device=groups.device)
+    counts.scatter_add_(1, g64, torch.ones_like(g64))
+    start = torch.zeros(hq, _lib.MAX_GROUPS + 1, dtype=torch.int64, device=groups.device)
+    start[:, 1:] = counts.cumsum(1)
+    return GroupTables(perm.contiguous(), start.to(torch.int32).contiguous(), int(group_count))
+
+
+def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _grad_bits(mask) -> int:
+    bits = 0
+    if mask[0]:
+        bits |= _lib.GRAD_Q
+    if mask[1]:
+        bits |= _lib.GRAD_K
+    if mask[2]:
+        bits |= _lib.GRAD_V
+    if any(mask[3:]):
+        bits |= _lib.GRAD_COEF
+    return bits
+
+
+def _pad_last(t: torch.Tensor) -> torch.Tensor:
+    d = t.shape[-1]
+    return t if d == _lib.HEAD_DIM else F.pad(t, (0, _lib.HEAD_DIM - d)).contiguous()
+
+
+def raise_on_status(status: torch.Tensor) -> None:
+    """One host synchronisation at the point where the reference synchronises
+    (oal_attention/hd_block_gemm_runtime.py:392-408)."""
+    bits = int(status.item())
+    if bits & _lib.STATUS_WAIT_TIMEOUT:
+        raise RuntimeError("oal_b200 kernel gave up on a bounded wait (device status word)")
+    if bits & (_lib.STATUS_NONFINITE | _lib.STATUS_DENOMINATOR):
+        raise RuntimeError(f"{_DENOMINATOR_ERROR} (device status {bits})")
+
+
+def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: float,
+                 plan: HDParallelBlockPlan, *, state_in=None, check=True):
+    """Launch the forward kernels.  Returns (out, num, den[B,Hq,N,1], saved_state, padded q,k,v)."""
+    if q.device.type != "cuda":
+        raise RuntimeError("oal_b200 runs on CUDA tensors only (there is no CPU path)")
+    lib = _lib.load()
+    B, Hq, Hkv, N, D, Dv = plan.geometry
+    qp, kp, vp = _pad_last(q), _pad_last(k), _pad_last(v)
+    out_dtype = getattr(torch, plan.output_dtype)
+    kernel_out = out_dtype if out_dtype != torch.float64 else torch.float32
+    dev = q.device
+    problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=q.dtype, out_dtype=kernel_out,
+                           precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
+                           floor=float(floor))
+    out = torch.empty(B, Hq, N, _lib.HEAD_DIM, dtype=kernel_out, device=dev)
+    num = torch.empty(B, Hq, N, _lib.HEAD_DIM, dtype=torch.float32, device=dev)
+    den = torch.empty(B, Hq, N, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws = torch.empty(max(plan.forward_workspace_bytes, 16), dtype=torch.uint8, device=dev)
+    saved = (torch.empty(plan.saved_state_bytes, dtype=torch.uint8, device=dev)
+             if plan.saved_state_bytes else None)
+    a32, b32, c32 = (t.detach().to(torch.float32).contiguous() for t in (a, b, c))
+    rc = lib.oal_forward(ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(kp), _lib.ptr(vp),
+                         _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start), _lib.ptr(a32),
+                         _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(out), _lib.ptr(num), _lib.ptr(den),
+                         _lib.ptr(saved), _lib.ptr(state_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status),
+                         _stream_ptr(dev))
+    _lib.check(rc)
+    if check:
+        raise_on_status(status)
+    if Dv != _lib.HEAD_DIM:
+        out, num = out[..., :Dv].contiguous(), num[..., :Dv].contiguous()
+    if out_dtype != kernel_out:
+        out = out.to(out_dtype)
+    return out, num, den.view(B, Hq, N, 1), saved, (qp, kp, vp, a32, b32, c32)
+
+
+def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scale, floor,
+                  plan: HDParallelBlockPlan, mask, grad_out, grad_num, grad_den, *, dstate_in=None):
+    """Launch the backward kernels; returns (dq, dk, dv, dA, dB, dC) with None where not requested."""
+    lib = _lib.load()
+    qp, kp, vp, a32, b32, c32 = saved_inputs
+    B, Hq, Hkv, N, D, Dv = plan.geometry
+    dev = qp.device
+    out_dtype = getattr(torch, plan.output_dtype)
+    kernel_out = out_dtype if out_dtype != torch.float64 else torch.float32
+    bits = _grad_bits(mask)
+    problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=qp.dtype, out_dtype=kernel_out,
+                           precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
+                           floor=float(floor), grad_mask=bits)
+
+    def prep(gt, dtype, width):
+        if gt is None:
+            return None
+        gt = gt.to(dtype)
+        if gt.shape[-1] != width and width == _lib.HEAD_DIM:
+            gt = F.pad(gt, (0, width - gt.shape[-1]))
+        return gt.contiguous()
+
+    go = prep(grad_out, kernel_out, _lib.HEAD_DIM)
+    gn = prep(grad_num, torch.float32, _lib.HEAD_DIM)
+    gd = prep(grad_den, torch.float32, 1)
+    num_p = num if num.shape[-1] == _lib.HEAD_DIM else F.pad(num, (0, _lib.HEAD_DIM - num.shape[-1])).contiguous()
+    G = tables.group_count
+    dq = torch.empty_like(qp) if bits & _lib.GRAD_Q else None
+    dk = torch.empty_like(kp) if bits & _lib.GRAD_K else None
+    dv = torch.empty_like(vp) if bits & _lib.GRAD_V else None
+    dA = torch.empty(Hq, dtype=torch.float32, device=dev) if bits & _lib.GRAD_COEF else None
+    dB = torch.empty(Hq, G, dtype=torch.float32, device=dev) if bits & _lib.GRAD_COEF else None
+    dC = torch.empty(Hq, G, G, dtype=torch.float32, device=dev) if bits & _lib.GRAD_COEF else None
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws = torch.empty(max(plan.backward_workspace_bytes, 16), dtype=torch.uint8, device=dev)
+    rc = lib.oal_backward(ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(kp), _lib.ptr(vp),
+                          _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start), _lib.ptr(a32),
+                          _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(num_p), _lib.ptr(den.contiguous()),
+                          _lib.ptr(saved_state), _lib.ptr(go), _lib.ptr(gn), _lib.ptr(gd), _lib.ptr(dq),
+                          _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dA), _lib.ptr(dB), _lib.ptr(dC),
+                          _lib.ptr(dstate_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status), _stream_ptr(dev))
+    _lib.check(rc)
+    if D != _lib.HEAD_DIM:
+        dq = None if dq is None else dq[..., :D].contiguous()
+        dk = None if dk is None else dk[..., :D].contiguous()
+    if Dv != _lib.HEAD_DIM:
+        dv = None if dv is None else dv[..., :Dv].contiguous()
+    return dq, dk, dv, dA, dB, dC
+
+
+class _HDParallelBlockGemmFunction(torch.autograd.Function):
+    """Planned forward + analytic first-order backward on the CUDA kernels."""
+
+    @staticmethod
+    def forward(ctx: Any, q, k, v, a, b, c, tables: GroupTables, scale: float, eps: float,
+                plan: HDParallelBlockPlan):
+        mask = tuple(bool(x) for x in ctx.needs_input_grad[:6])
+        if plan.requested_gradient_mask != mask:
+            raise ValueError("plan gradient mask must exactly match the six tensor inputs")
+        ctx.set_materialize_grads(False)
+        out, num, den, saved_state, padded = forward_impl(q, k, v, a, b, c, tables, scale, eps, plan)
+        ctx.tables, ctx.scale, ctx.eps, ctx.plan, ctx.mask = tables, float(scale), float(eps), plan, mask
+        ctx.input_dtypes = tuple(t.dtype for t in (q, k, v, a, b, c))
+        ctx.has_state = saved_state is not None
+        if any(mask):
+            tensors = list(padded) + [num, den]
+            if saved_state is not None:
+                tensors.append(saved_state)
+            ctx.save_for_backward(*tensors)
+        return out, num, den
+
+    @staticmethod
+    def backward(ctx: Any, grad_output, grad_numerator, grad_denominator):
+        if torch.is_grad_enabled():
+            raise RuntimeError("HD Block-GEMM does not support double backward")
+        saved = ctx.saved_tensors
+        padded, num, den = saved[:6], saved[6], saved[7]
+        state = saved[8] if ctx.has_state else None
+        mask = ctx.mask
+        if grad_output is None and grad_numerator is None and grad_denominator is None:
+            return (None,) * 10
+        dq, dk, dv, dA, dB, dC = backward_impl(padded, num, den, state, ctx.tables, ctx.scale, ctx.eps,
+                                               ctx.plan, mask, grad_output, grad_numerator,
+                                               grad_denominator)
+        grads = [dq, dk, dv, dA, dB, dC]
+        result = []
+        for requested, g, dtype in zip(mask, grads, ctx.input_dtypes):
+            if not requested:
+                result.append(None)
+            elif g is None:
+                raise RuntimeError("requested HD Block-GEMM gradient was not produced")
+            else:
+                result.append(g.to(dtype))
+        return (*result, None, None, None, None)
+
+
+def hd_parallel_block_gemm(q, k, v, a, b, c, *, tables, scale, eps, plan):
+    """Forward only (no autograd graph), same return triple."""
+    out, num, den, _, _ = forward_impl(q, k, v, a, b, c, tables, scale, eps, plan)
+    return out, num, den
+
+
+def hd_parallel_block_gemm_autograd(q, k, v, a, b, c, *, tables, scale, eps, plan):
+    return _HDParallelBlockGemmFunction.apply(q, k, v, a, b, c, tables, scale, eps, plan)

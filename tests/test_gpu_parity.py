@@ -1,0 +1,136 @@
+"""GPU parity: the CUDA operator (through the C ABI) against golden vectors produced by the
+reference and against the fp64 CPU oracle on the same seeded inputs.
+
+Tolerances are the ones the task states: max normalized error <= 1e-4 in fp32 mode and
+<= 2e-2 with bf16 inputs/outputs and fp32 accumulation."""
+
+import pytest
+import torch
+
+from oal_b200 import synthetic
+from tests.helpers import ERR, assert_close, oracle_dense, run_operator
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32 = 1e-4
+TOL_BF16 = 2e-2
+
+
+@pytest.mark.parametrize("stem", ["two_groups", "different_active_group_counts"])
+def test_known_answer_fixtures_fp32(kat, stem):
+    import oal_b200
+
+    rec = kat(stem)
+    t = lambda key: torch.tensor(rec[key], dtype=torch.float32, device="cuda")
+    groups = torch.tensor(rec["dim_groups"], dtype=torch.int32, device="cuda")
+    out, num, den = oal_b200.grouped_causal_attention(t("q"), t("k"), t("v"), groups, t("factor"),
+                                                      scale=rec["scale"], kernel_eps=rec["kernel_eps"],
+                                                      precision="fp32_ieee")
+    want = lambda key: torch.tensor(rec[key], dtype=torch.float64)
+    assert ERR(num, want("numerator")) < 1e-6
+    assert ERR(den, want("denominator")) < 1e-6
+    assert ERR(out, want("output")) < 1e-6
+    out2 = oal_b200.oal_attention(t("q"), t("k"), t("v"), groups, t("factor"), scale=rec["scale"],
+                                  kernel_eps=rec["kernel_eps"])
+    assert torch.equal(out2, out)
+
+
+def test_config1_fp32_against_reference_golden(golden):
+    g = golden("config1")
+    case = synthetic.config1_case(int(g["seed"]))
+    res = run_operator(case, precision="fp32_ieee")
+    res["dC_sym"] = 2 * res.pop("dC")
+    assert_close(res, g, TOL_FP32, keys=["out", "num", "den", "dq", "dk", "dv", "dA", "dB", "dC_sym"],
+                 label="config1")
+
+
+def test_mixed_fp32_against_reference_golden(golden):
+    """GQA, ragged N, per-head groups with different active counts, zero-padded factor,
+    upstream gradients on out, numerator and denominator."""
+    g = golden("mixed")
+    res = run_operator(synthetic.mixed_case(0), precision="fp32_ieee")
+    assert_close(res, g, TOL_FP32, keys=["out", "num", "den", "dq", "dk", "dv", "dfactor"], label="mixed")
+
+
+def test_qwen_small_fp32_inputs_bf16_rounded(golden):
+    g = golden("qwen_small")
+    case = synthetic.qwen_head_case(0, batch=1, n=320, hq=7, hkv=1, g=8, bf16=True)
+    res = run_operator(case, precision="fp32_ieee")
+    assert_close(res, g, TOL_FP32, keys=["out", "num", "den", "dq", "dk", "dv", "dfactor"], label="qwen_small")
+
+
+def test_qwen_small_bf16_io_fp32_mode(golden):
+    """bf16 tensors in and out, fp32 arithmetic: only the output roundings remain."""
+    g = golden("qwen_small")
+    case = synthetic.qwen_head_case(0, batch=1, n=320, hq=7, hkv=1, g=8, bf16=True)
+    res = run_operator(case, precision="fp32_ieee", io_dtype=torch.bfloat16)
+    assert_close(res, g, TOL_BF16, keys=["out", "dq", "dk", "dv"], label="qwen_small bf16 io")
+    assert_close(res, g, TOL_FP32, keys=["num", "den", "dfactor"], label="qwen_small bf16 io")
+
+
+@pytest.mark.parametrize("n", [1, 63, 65, 197])
+def test_ragged_lengths_fp32(n):
+    case = synthetic.mixed_case(7 + n, batch=1, hq=4, hkv=2, n=n, gmax=3)
+    assert_close(run_operator(case, precision="fp32_ieee"), oracle_dense(case), TOL_FP32, label=f"N={n}")
+
+
+@pytest.mark.parametrize("d,dv", [(32, 64), (64, 16), (24, 40)])
+def test_small_head_dims_fp32(d, dv):
+    case = synthetic.mixed_case(11, batch=1, hq=2, hkv=1, n=70, d=d, dv=dv, gmax=3)
+    assert_close(run_operator(case, precision="fp32_ieee"), oracle_dense(case), TOL_FP32, label=f"D={d},Dv={dv}")
+
+
+@pytest.mark.parametrize("g", [1, 4, 16])
+def test_group_counts_fp32(g):
+    case = synthetic.qwen_head_case(3, batch=1, n=130, hq=2, hkv=1, g=g, bf16=False, outlier_scale=4.0)
+    assert_close(run_operator(case, precision="fp32_ieee"), oracle_dense(case), TOL_FP32, label=f"G={g}")
+
+
+@pytest.mark.parametrize("need", [("q", "coef"), ("k", "v"), ("v",), ()])
+def test_gradient_mask_subsets_fp32(need):
+    case = synthetic.mixed_case(5, batch=1, hq=4, hkv=2, n=90, gmax=4)
+    res = run_operator(case, precision="fp32_ieee", need=need)
+    ref = oracle_dense(case)
+    expect = {"out", "num", "den"}
+    expect |= {"dq"} if "q" in need else set()
+    expect |= {"dk"} if "k" in need else set()
+    expect |= {"dv"} if "v" in need else set()
+    expect |= {"dfactor"} if "coef" in need else set()
+    assert set(res) == expect
+    assert_close(res, ref, TOL_FP32, label=str(need))
+
+
+def test_run_to_run_determinism_fp32():
+    case = synthetic.mixed_case(9, batch=2, hq=4, hkv=2, n=200, gmax=4)
+    a = run_operator(case, precision="fp32_ieee")
+    b = run_operator(case, precision="fp32_ieee")
+    for key in a:
+        assert torch.equal(a[key], b[key]), key
+
+
+def test_nonpositive_denominator_raises():
+    """A negative constant makes every weight negative: the device status word turns into the
+    reference's RuntimeError (no device assert, the context stays usable)."""
+    import oal_b200
+
+    case = synthetic.config1_case(0, n=40)
+    q, k, v = (t.cuda() for t in (case.q, case.k, case.v))
+    a = torch.full_like(case.A, -1e6).cuda()
+    with pytest.raises(RuntimeError, match="denominator must be finite and strictly positive"):
+        oal_b200.grouped_coefficient_attention(q, k, v, case.dim_groups.cuda(), a, case.B.cuda() * 0,
+                                               case.C.cuda() * 0, scale=case.scale)
+    out, _, _ = oal_b200.grouped_coefficient_attention(q, k, v, case.dim_groups.cuda(), case.A.cuda(),
+                                                       case.B.cuda(), case.C.cuda(), scale=case.scale)
+    assert torch.isfinite(out).all()
+
+
+def test_double_backward_refused():
+    import oal_b200
+
+    case = synthetic.config1_case(0, n=16)
+    q = case.q.cuda().requires_grad_()
+    out, _, _ = oal_b200.grouped_coefficient_attention(q, case.k.cuda(), case.v.cuda(), case.dim_groups.cuda(),
+                                                       case.A.cuda(), case.B.cuda(), case.C.cuda(),
+                                                       scale=case.scale)
+    with pytest.raises(RuntimeError, match="double backward"):
+        torch.autograd.grad(out.sum(), q, create_graph=True)
