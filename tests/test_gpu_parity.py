@@ -113,14 +113,13 @@ def test_nonpositive_denominator_raises():
     reference's RuntimeError (no device assert, the context stays usable)."""
     import oal_b200
 
-    case = synthetic.config1_case(0, n=40)
-    q, k, v = (t.cuda() for t in (case.q, case.k, case.v))
-    a = torch.full_like(case.A, -1e6).cuda()
+    case = synthetic.qwen_head_case(2, batch=1, n=40, hq=2, hkv=1, g=4, bf16=False)
+    q, k, v, groups = (t.cuda() for t in (case.q, case.k, case.v, case.dim_groups))
+    a = torch.full((2,), -1e6, device="cuda")
+    zb, zc = torch.zeros(2, 4, device="cuda"), torch.zeros(2, 4, 4, device="cuda")
     with pytest.raises(RuntimeError, match="denominator must be finite and strictly positive"):
-        oal_b200.grouped_coefficient_attention(q, k, v, case.dim_groups.cuda(), a, case.B.cuda() * 0,
-                                               case.C.cuda() * 0, scale=case.scale)
-    out, _, _ = oal_b200.grouped_coefficient_attention(q, k, v, case.dim_groups.cuda(), case.A.cuda(),
-                                                       case.B.cuda(), case.C.cuda(), scale=case.scale)
+        oal_b200.grouped_coefficient_attention(q, k, v, groups, a, zb, zc, scale=case.scale)
+    out, _, _ = oal_b200.grouped_causal_attention(q, k, v, groups, case.factor.cuda(), scale=case.scale)
     assert torch.isfinite(out).all()
 
 
