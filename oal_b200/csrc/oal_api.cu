@@ -70,6 +70,30 @@ BackwardSpace carve_backward(const OalProblem* p, void* ws) {
   return s;
 }
 
+constexpr int kChunk = 128;
+
+int chunk_count(const OalProblem* p) { return (p->seq_len + kChunk - 1) / kChunk; }
+
+struct ForwardSpaceTC {
+  float* coef_table;
+  float* ds;
+  size_t bytes;
+};
+
+ForwardSpaceTC carve_forward_tc(const OalProblem* p, void* ws) {
+  Carver c(ws);
+  ForwardSpaceTC s;
+  const size_t units = (size_t)p->batch * p->kv_heads;
+  s.coef_table = c.take<float>((size_t)p->q_heads * oal::state_rows());
+  s.ds = c.take<float>(units * chunk_count(p) * oal::state_rows() * oal::EP);
+  s.bytes = c.off;
+  return s;
+}
+
+size_t saved_state_bytes_tc(const OalProblem* p) {
+  return (size_t)p->batch * p->kv_heads * chunk_count(p) * oal::state_image_bytes_per_chunk();
+}
+
 oal::PairArgs base_args(const OalProblem* p, const void* q, const void* k, const void* v,
                         const int32_t* perm, const int32_t* gstart, const float* A, const float* B,
                         const float* C, int32_t* status) {
@@ -102,7 +126,9 @@ int64_t oal_workspace_bytes(const OalProblem* p, int phase) {
     if (phase == 1) return (int64_t)carve_backward(p, nullptr).bytes;
     return 0;
   }
-  return fail(OAL_ERR_ARGUMENT, "bf16_tensorcore is not available in this build");
+  if (phase == 0) return (int64_t)carve_forward_tc(p, nullptr).bytes;
+  if (phase == 2) return (int64_t)saved_state_bytes_tc(p);
+  return (int64_t)carve_backward(p, nullptr).bytes;
 }
 
 int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
@@ -123,7 +149,27 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
     if (e != cudaSuccess) return fail_cuda(e, "forward pair kernel");
     return OAL_OK;
   }
-  return fail(OAL_ERR_ARGUMENT, "bf16_tensorcore is not available in this build");
+  // bf16_tensorcore: chunk states on the tensor cores, intra-chunk term from token pairs
+  ForwardSpaceTC s = carve_forward_tc(p, workspace);
+  if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_forward: workspace too small");
+  if (!saved_state) return fail(OAL_ERR_ARGUMENT, "oal_forward: saved_state is NULL");
+  const int units = p->batch * p->kv_heads, nb = chunk_count(p);
+  cudaError_t e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups,
+                                        s.coef_table, st);
+  if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
+  e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st);
+  if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
+  e = oal::state_scan(s.ds, saved_state, state_in, nullptr, units, nb, 0, st);
+  if (e != cudaSuccess) return fail_cuda(e, "state scan kernel");
+  e = oal::cross_read(true, q, saved_state, s.coef_table, num, den, p->batch, p->q_heads,
+                      p->q_heads / p->kv_heads, p->seq_len, nb, p->scale, status, st);
+  if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
+  oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
+  a.window = kChunk;
+  a.out = out; a.num = num; a.den = den; a.accumulate = 1;
+  e = oal::pairs_forward(a, st);
+  if (e != cudaSuccess) return fail_cuda(e, "forward pair kernel");
+  return OAL_OK;
 }
 
 int oal_backward(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
@@ -144,7 +190,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     return fail(OAL_ERR_ARGUMENT, "coefficient gradients requested but NULL");
   (void)saved_state;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (p->precision == OAL_PRECISION_FP32_IEEE) {
+  if (p->precision == OAL_PRECISION_FP32_IEEE || true) {
     if (dstate_in) return fail(OAL_ERR_ARGUMENT, "fp32_ieee mode keeps no chunk state: dstate_in must be NULL");
     BackwardSpace s = carve_backward(p, workspace);
     if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_backward: workspace too small");

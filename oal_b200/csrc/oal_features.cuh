@@ -1,0 +1,122 @@
+// Quadratic feature map of the chunked scan, laid out for the tensor cores.
+//
+// The reference materialises phi_k = [1, k_d, k_r k_c (r >= c)] and
+// phi_q = [A, B_{g(d)} q_d, m C_{g(r)g(c)} q_r q_c] as [tokens, 2145] matrices in HBM
+// (oal_attention/hd_block_gemm_feature_forward.py:225-253, :373-385; pair order
+// oal_attention/hd_block_gemm_cache.py:105-121).  Here a feature tile only ever exists
+// in shared memory: each thread owns one token, keeps its 64-element row in registers
+// and emits 16-byte chunks of 8 consecutive features as bf16.  The feature order is
+// internal (the running state is never exposed), chosen so that every index below is a
+// compile-time constant:
+//   chunks   0..259  pair features p = 8*chunk + j, p = r(r+1)/2 + c  (r >= c)
+//   chunks 260..267  linear features d = 8*(chunk-260) + j
+//   chunk  268       [constant, 0 x 7]
+//   chunks 269..271  zero padding
+// 16 chunks (128 features) form a slab: 17 slabs, 2176 feature rows.
+#pragma once
+
+#include <utility>
+
+#include "oal_common.cuh"
+#include "oal_umma.cuh"
+
+namespace oal {
+
+constexpr int F_PAIR_CHUNKS = 260;
+constexpr int F_LIN_CHUNK0 = 260;
+constexpr int F_CONST_CHUNK = 268;
+constexpr int F_CHUNKS = 272;
+constexpr int F_SLABS = 17;
+constexpr int F_ROWS = F_SLABS * 128;          // 2176
+constexpr int CT = 128;                        // tokens per chunk of the scan
+constexpr int SLAB_A_BYTES = 128 * CT * 2;     // feature slab tile  [16 chunks][128 tokens][8] bf16
+constexpr int SLAB_S_BYTES = (EP / 8) * 128 * 16;   // state slab image [10][128 features][8 e] bf16
+
+struct RC {
+  int r, c;
+};
+__host__ __device__ constexpr RC pair_rc(int p) {
+  int r = 0;
+  while ((r + 1) * (r + 2) / 2 <= p) ++r;
+  return RC{r, p - r * (r + 1) / 2};
+}
+
+// One chunk of 8 features of the token whose row is x[64].  QUERY multiplies by the
+// per-head coefficient table (same feature order, fp32, in shared memory).
+template <int CH, bool QUERY>
+__device__ __forceinline__ uint4 feature_chunk(const float (&x)[HD], const float* coef) {
+  float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if constexpr (CH < F_PAIR_CHUNKS) {
+    constexpr RC p0 = pair_rc(8 * CH + 0), p1 = pair_rc(8 * CH + 1), p2 = pair_rc(8 * CH + 2),
+                 p3 = pair_rc(8 * CH + 3), p4 = pair_rc(8 * CH + 4), p5 = pair_rc(8 * CH + 5),
+                 p6 = pair_rc(8 * CH + 6), p7 = pair_rc(8 * CH + 7);
+    f[0] = x[p0.r] * x[p0.c]; f[1] = x[p1.r] * x[p1.c]; f[2] = x[p2.r] * x[p2.c]; f[3] = x[p3.r] * x[p3.c];
+    f[4] = x[p4.r] * x[p4.c]; f[5] = x[p5.r] * x[p5.c]; f[6] = x[p6.r] * x[p6.c]; f[7] = x[p7.r] * x[p7.c];
+  } else if constexpr (CH < F_CONST_CHUNK) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = x[8 * (CH - F_LIN_CHUNK0) + j];
+  } else if constexpr (CH == F_CONST_CHUNK) {
+    f[0] = 1.f;
+#pragma unroll
+    for (int j = 1; j < 8; ++j) f[j] = 0.f;
+  } else {
+    return make_uint4(0u, 0u, 0u, 0u);
+  }
+  if constexpr (QUERY) {
+    const float4 c0 = *reinterpret_cast<const float4*>(coef + 8 * CH);
+    const float4 c1 = *reinterpret_cast<const float4*>(coef + 8 * CH + 4);
+    f[0] *= c0.x; f[1] *= c0.y; f[2] *= c0.z; f[3] *= c0.w;
+    f[4] *= c1.x; f[5] *= c1.y; f[6] *= c1.z; f[7] *= c1.w;
+  }
+  return make_uint4(umma::pack_bf16(f[0], f[1]), umma::pack_bf16(f[2], f[3]), umma::pack_bf16(f[4], f[5]),
+                    umma::pack_bf16(f[6], f[7]));
+}
+
+template <int S, int HALF, bool QUERY, int... J>
+__device__ __forceinline__ void half_slab_impl(const float (&x)[HD], const float* coef, uint4* tile, int token,
+                                               std::integer_sequence<int, J...>) {
+  ((tile[(HALF * 8 + J) * CT + token] = feature_chunk<S * 16 + HALF * 8 + J, QUERY>(x, coef)), ...);
+}
+
+// Write chunks [8*half, 8*half+8) of slab s of this thread's token into the slab tile
+// ([16 chunks][128 tokens] x 16 bytes).  s and half are runtime values; the bodies are static.
+template <bool QUERY>
+__device__ __forceinline__ void write_half_slab(int s, int half, const float (&x)[HD], const float* coef,
+                                                uint4* tile, int token) {
+  using Seq = std::make_integer_sequence<int, 8>;
+#define OAL_SLAB_CASE(S)                                                        \
+  case S:                                                                       \
+    if (half == 0) half_slab_impl<S, 0, QUERY>(x, coef, tile, token, Seq{});    \
+    else half_slab_impl<S, 1, QUERY>(x, coef, tile, token, Seq{});              \
+    break;
+  switch (s) {
+    OAL_SLAB_CASE(0) OAL_SLAB_CASE(1) OAL_SLAB_CASE(2) OAL_SLAB_CASE(3) OAL_SLAB_CASE(4) OAL_SLAB_CASE(5)
+    OAL_SLAB_CASE(6) OAL_SLAB_CASE(7) OAL_SLAB_CASE(8) OAL_SLAB_CASE(9) OAL_SLAB_CASE(10) OAL_SLAB_CASE(11)
+    OAL_SLAB_CASE(12) OAL_SLAB_CASE(13) OAL_SLAB_CASE(14) OAL_SLAB_CASE(15) OAL_SLAB_CASE(16)
+    default: break;
+  }
+#undef OAL_SLAB_CASE
+}
+
+// Row `i` (or zeros when i >= N) of a bf16 [.., N, 64] tensor into registers, times mul.
+__device__ __forceinline__ void load_row_bf16(float (&x)[HD], const __nv_bfloat16* base, int i, int N, float mul) {
+  if (i < N) {
+    const uint4* p = reinterpret_cast<const uint4*>(base + (size_t)i * HD);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 t = p[c];
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+        x[8 * c + 2 * j] = mul * __low2float(h);
+        x[8 * c + 2 * j + 1] = mul * __high2float(h);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int d = 0; d < HD; ++d) x[d] = 0.f;
+  }
+}
+
+}  // namespace oal

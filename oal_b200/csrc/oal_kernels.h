@@ -40,4 +40,18 @@ cudaError_t norm_vjp(const void* grad_out, int out_dt, const float* grad_num, co
 cudaError_t reduce_coefs(const float* p0, int tiles0, const float* p1, int tiles1, int B, int Hq, int G,
                          float* dA, float* dB, float* dC, cudaStream_t st);
 
+// ---- tensor-core state kernels (oal_state.cu) ---------------------------------------
+size_t state_rows();                       // feature rows of the running state (2176)
+size_t state_image_bytes_per_chunk();      // bytes of one bf16 state image [17 slabs][10][128][8]
+
+cudaError_t build_coef_table(const int32_t* dim_perm, const int32_t* group_start, const float* A,
+                             const float* Bc, const float* Cc, int Hq, int G, float* table, cudaStream_t st);
+cudaError_t state_update(const void* k, const void* v, float* ds, int units, int N, int NB, int32_t* status,
+                         cudaStream_t st);
+cudaError_t state_scan(const float* ds, void* image, const float* state_in, float* state_total, int units,
+                       int NB, int reverse, cudaStream_t st);
+cudaError_t cross_read(bool query, const void* x, const void* image, const float* coef_table, float* out64,
+                       float* out1, int B, int H, int rep, int N, int NB, float mul, int32_t* status,
+                       cudaStream_t st);
+
 }  // namespace oal

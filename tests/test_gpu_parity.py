@@ -133,3 +133,30 @@ def test_double_backward_refused():
                                                        scale=case.scale)
     with pytest.raises(RuntimeError, match="double backward"):
         torch.autograd.grad(out.sum(), q, create_graph=True)
+
+
+# ---------------------------------------------------------------------------
+# bf16_tensorcore mode: chunk states on tcgen05, bf16 operands, fp32 accumulation
+# ---------------------------------------------------------------------------
+def test_qwen_small_bf16_tensorcore(golden):
+    g = golden("qwen_small")
+    case = synthetic.qwen_head_case(0, batch=1, n=320, hq=7, hkv=1, g=8, bf16=True)
+    res = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
+    assert_close(res, g, TOL_BF16, keys=["out", "num", "den", "dq", "dk", "dv", "dfactor"],
+                 label="qwen_small bf16_tensorcore")
+
+
+@pytest.mark.parametrize("n", [1, 127, 129, 700])
+def test_ragged_lengths_bf16_tensorcore(n):
+    case = synthetic.mixed_case(20 + n, batch=2, hq=4, hkv=2, n=n, gmax=3)
+    for t in ("q", "k", "v", "grad_out"):
+        setattr(case, t, getattr(case, t).bfloat16().float())
+    res = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
+    assert_close(res, oracle_dense(case), TOL_BF16, label=f"bf16 N={n}")
+
+
+def test_chunked_long_sequence_bf16_tensorcore():
+    """N = 2048 (16 chunks) at the Qwen head shape with x20 outlier channels."""
+    case = synthetic.qwen_head_case(4, batch=1, n=2048, hq=7, hkv=1, g=8, bf16=True)
+    res = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
+    assert_close(res, oracle_dense(case), TOL_BF16, label="bf16 N=2048")
