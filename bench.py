@@ -1,0 +1,328 @@
+"""Benchmark of the OAL causal grouped-quadratic attention path (forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward + backward of the operator over one batch of seeded synthetic input.
+Workload: the Qwen2.5-0.5B attention-layer shape of the headline configuration
+(B=4, 14 query / 2 KV heads, d=64, N=4096, G=8 groups {2,2,4,4,8,12,16,16}, four x20 outlier
+channels, bf16 tensors, fp32 state).  With N GPUs every rank runs the same workload on its own
+batch (batch x KV-head units are independent: no collective on the data path, weak scaling).
+
+The one JSON line printed by rank 0 carries
+  value      tokens/s with the inputs already resident in HBM (CUDA events, max over ranks)
+  e2e        tokens/s through the public operator call with HOST tensors: pinned host -> device
+             copies of q, k, v and the upstream gradient and device -> host copies of out, dq,
+             dk, dv inside the timed region
+  roofline   the dominant kernel against the measured bf16 tensor peak (MEASURED_PEAKS.json)
+  cpu_baseline  the CPU oracle's chunked implementation of the same path on this box's cores
+--impl reference times that CPU implementation alone (the reference is Python/torch CPU code for
+this path; the oracle restates it), on a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = dict(batch=4, hq=14, hkv=2, n=4096, g=8)
+D = 64
+METRIC = "oal_attention_fwd_bwd_tokens_per_s"
+
+
+def flop_per_token(hq: int, hkv: int, t: int = 64) -> float:
+    """Algorithmic FLOPs per token position (multiply-add = 2, causal half only, no padding):
+    (Hq+Hkv) 6 F E for the state GEMMs + Hq 3 (D+E)(T+1) for the intra-chunk ones."""
+    f, e = 1 + D + D * (D + 1) // 2, D + 1
+    return (hq + hkv) * 6 * f * e + hq * 3 * (D + e) * (t + 1)
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(tflops=float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 1420.0))),
+                    hbm=float(d.get("hbm_gbs", 6454.6)), source="measured")
+    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            self.proc.wait(timeout=5)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], 0.0, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = max(mx, float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=mx or None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# --------------------------------------------------------------------------------------
+# CPU arm: the oracle's chunked implementation (restating the reference's production path)
+# --------------------------------------------------------------------------------------
+def cpu_reference_run(steps: int, warmup: int) -> dict:
+    from oal_b200 import synthetic
+    from oracle import oal_oracle as orc
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample = dict(batch=1, hq=WORKLOAD["hq"], hkv=WORKLOAD["hkv"], n=WORKLOAD["n"], g=WORKLOAD["g"])
+    case = synthetic.qwen_head_case(0, bf16=True, **sample)
+    a, b, c = orc.expand_factor(case.factor, sample["hq"], case.kernel_eps, torch.float32)
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        orc.chunked_forward_backward(case.q, case.k, case.v, case.dim_groups, a, b, c, scale=case.scale,
+                                     token_block=64, grad_out=case.grad_out)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    tokens = sample["batch"] * sample["n"]
+    best, mean = min(times), sum(times) / len(times)
+    return dict(tokens_per_s=tokens / best, mean_s=mean, best_s=best, cores=cores,
+                threads=torch.get_num_threads(),
+                sample=f"one batch row of the workload (B=1, Hq=14, Hkv=2, N=4096, G=8), fp32, chunk 64, "
+                       f"best of {steps} after {warmup} warm-up")
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = cpu_reference_run(max(1, min(args.steps, 3)), max(1, min(args.warmup, 1)))
+    line = dict(metric=METRIC, value=r["tokens_per_s"], unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=r["best_s"] * 1e3, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
+                config=dict(workload="qwen2.5-0.5b attention layer shape, causal fwd+bwd, one batch row "
+                                     "(B=1, Hq=14, Hkv=2, N=4096, d=64, G=8)", l2="inputs and state larger than L2"),
+                cpu_baseline=dict(value=r["tokens_per_s"], unit="tokens/s", cores=r["threads"], kind="port",
+                                  sample=r["sample"]),
+                e2e=dict(value=r["tokens_per_s"], unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+def run_gpu_arm(args) -> None:
+    import torch.distributed as dist
+
+    import oal_b200
+    from oal_b200 import _lib, synthetic
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    w = WORKLOAD
+    precision = args.precision
+    sets = []
+    for s in range(2):        # two input sets, alternated between steps
+        case = synthetic.qwen_head_case(100 * rank + s, bf16=True, **w)
+        host = dict(q=case.q.bfloat16().pin_memory(), k=case.k.bfloat16().pin_memory(),
+                    v=case.v.bfloat16().pin_memory(), dout=case.grad_out.bfloat16().pin_memory())
+        sets.append(dict(case=case, host=host, dev={k_: v_.to(dev) for k_, v_ in host.items()}))
+    case0 = sets[0]["case"]
+    groups = case0.dim_groups.to(dev)
+    factor = case0.factor.to(dev).requires_grad_()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    q0 = sets[0]["dev"]["q"].clone().requires_grad_()
+    k0 = sets[0]["dev"]["k"].clone().requires_grad_()
+    v0 = sets[0]["dev"]["v"].clone().requires_grad_()
+    prepared = oal_b200.prepare_grouped_hd_block_gemm(q0, k0, v0, groups, factor, scale=case0.scale,
+                                                      kernel_eps=case0.kernel_eps, precision=precision,
+                                                      token_block=64, feature_wave_blocks=4)
+
+    def step(t):
+        q = t["q"].detach().requires_grad_()
+        k = t["k"].detach().requires_grad_()
+        v = t["v"].detach().requires_grad_()
+        factor.grad = None
+        out, _, _ = oal_b200.run_prepared_grouped_hd_block_gemm(prepared, q, k, v, factor)
+        out.backward(t["dout"])
+        return out, q.grad, k.grad, v.grad
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        step(sets[i % 2]["dev"])
+    barrier()
+
+    # ---- timed region: K steps, CUDA events on the launching stream, L2 flushed between steps
+    launches0 = _lib.launch_count()
+    events = []
+    with ClockSampler(local) as clocks:
+        barrier()
+        for i in range(args.steps):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step(sets[i % 2]["dev"])
+            e1.record()
+            events.append((e0, e1))
+        barrier()
+    launches = _lib.launch_count() - launches0
+    total_ms = sum(a.elapsed_time(b) for a, b in events)
+    clock_summary = clocks.summary()
+
+    # ---- end to end through the public call with host tensors
+    def e2e_step(host):
+        t = {k_: v_.to(dev, non_blocking=True) for k_, v_ in host.items()}
+        out, dq, dk, dv = step(t)
+        return [x.to("cpu", non_blocking=True) for x in (out, dq, dk, dv)]
+
+    e2e_step(sets[0]["host"])
+    barrier()
+    e2e_events = []
+    for i in range(args.steps):
+        flush.fill_(i & 0xFF)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        e2e_step(sets[i % 2]["host"])
+        e1.record()
+        e2e_events.append((e0, e1))
+    barrier()
+    e2e_ms = sum(a.elapsed_time(b) for a, b in e2e_events)
+    h2d = sum(t.numel() * t.element_size() for t in sets[0]["host"].values())
+    d2h = 2 * sets[0]["host"]["q"].numel() * 2 + 2 * sets[0]["host"]["k"].numel() * 2
+
+    # ---- per-kernel breakdown (separate pass with the library's event pairs switched on)
+    _lib.profile_enable(True)
+    prof_steps = min(args.steps, 5)
+    for i in range(prof_steps):
+        flush.fill_(i & 0xFF)
+        step(sets[i % 2]["dev"])
+    torch.cuda.synchronize()
+    report = _lib.profile_report()
+    _lib.profile_enable(False)
+
+    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = times.tolist()
+    tokens_per_step = w["batch"] * w["n"] * world
+    value = tokens_per_step * args.steps / (total_ms * 1e-3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms * 1e-3)
+
+    if rank == 0:
+        peaks = measured_peaks()
+        fpt = flop_per_token(w["hq"], w["hkv"], 64)
+        f, e = 1 + D + D * (D + 1) // 2, D + 1
+        tok = w["batch"] * w["n"]
+        # algorithmic FLOPs of each kernel per launch (unpadded F = 2145, E = 65)
+        kernel_flops = {
+            "state_update": w["hkv"] * 2 * f * e * tok,
+            "cross_read_q": w["hq"] * 2 * f * e * tok,
+            "dstate_heads": w["hq"] * 2 * f * e * tok,
+            "feature_grad_q": w["hq"] * 2 * f * e * tok,
+            "feature_grad_k": w["hkv"] * 2 * f * e * tok,
+            "cross_read_k": w["hkv"] * 2 * f * e * tok,
+        }
+        kernels = {name: dict(launches=cnt, ms_per_launch=ms / max(cnt, 1), share=None)
+                   for name, (cnt, ms) in report.items()}
+        tot = sum(ms for _, ms in report.values()) or 1.0
+        for name, (cnt, ms) in report.items():
+            kernels[name]["share"] = round(ms / tot, 4)
+        tc = {n_: k_ for n_, k_ in kernels.items() if n_ in kernel_flops}
+        roofline = None
+        if tc:
+            top = max(tc, key=lambda n_: tc[n_]["ms_per_launch"] * tc[n_]["launches"])
+            achieved = kernel_flops[top] / (tc[top]["ms_per_launch"] * 1e-3) / 1e12
+            roofline = dict(bound="tensor", kernel=top, achieved=round(achieved, 2), peak=peaks["tflops"],
+                            unit="TFLOP/s", frac=round(achieved / peaks["tflops"], 4), traffic=None,
+                            peak_source=peaks["source"] + " (sustained bf16)",
+                            whole_step_frac=round(value * fpt / 1e12 / peaks["tflops"], 4))
+        cpu = cpu_reference_run(2, 1) if world >= 1 and not args.no_cpu_baseline else None
+        line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps,
+                    warmup=max(args.warmup, 3), ms_per_step=total_ms / args.steps, higher_is_better=True,
+                    scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                    config=dict(workload="qwen2.5-0.5b attention layer shape, causal fwd+bwd (B=4 per GPU, "
+                                         "Hq=14, Hkv=2, N=4096, d=64, G=8, bf16 io, fp32 state)",
+                                precision=precision, parallelism=f"batch x kv-head units, {world} rank(s), no collective",
+                                l2="256 MiB buffer written between timed steps", flop_per_token=fpt),
+                    e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+                    gpu_launches=int(launches), clocks=clock_summary, roofline=roofline, kernels=kernels)
+        if cpu:
+            line["cpu_baseline"] = dict(value=cpu["tokens_per_s"], unit="tokens/s", cores=cpu["threads"],
+                                        kind="port", sample=cpu["sample"])
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--precision", default="bf16_tensorcore", choices=["bf16_tensorcore", "fp32_ieee"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -148,6 +148,18 @@ const char* oal_last_error_string(void);
 int oal_selftest_umma(int mode, int n, int k, const void* a, const void* b, float* d, int32_t* status,
                       void* stream);
 
+/*
+ * Launch accounting and opt-in per-kernel timing (thin counterpart of the reference's stage
+ * profiler, oal_attention/hd_block_gemm_profiling.py:195-378).  oal_launch_count() is the number
+ * of kernels this library has launched in the process so far.  After oal_profile_enable(1) every
+ * launch is bracketed by a CUDA-event pair on its stream; oal_profile_report() waits for them and
+ * writes a JSON object {"kernel": [launches, total_ms], ...} into the host buffer, then forgets
+ * them.  oal_profile_enable(0) switches the events off again.
+ */
+int64_t oal_launch_count(void);
+void oal_profile_enable(int enable);
+int oal_profile_report(char* buffer, size_t capacity);
+
 /* Library / build identification: "oal_b200 <version> sm_100a". Host pointer. */
 const char* oal_version_string(void);
 

@@ -31,6 +31,9 @@ EXPORTED_SYMBOLS = (
     "oal_last_error_string",
     "oal_version_string",
     "oal_selftest_umma",
+    "oal_launch_count",
+    "oal_profile_enable",
+    "oal_profile_report",
 )
 
 
@@ -78,6 +81,11 @@ def load() -> ctypes.CDLL:
     lib.oal_backward.restype = ctypes.c_int
     lib.oal_selftest_umma.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp, f32p, i32p, vp]
     lib.oal_selftest_umma.restype = ctypes.c_int
+    lib.oal_launch_count.restype = ctypes.c_int64
+    lib.oal_profile_enable.argtypes = [ctypes.c_int]
+    lib.oal_profile_enable.restype = None
+    lib.oal_profile_report.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    lib.oal_profile_report.restype = ctypes.c_int
     lib.oal_last_error_string.restype = ctypes.c_char_p
     lib.oal_version_string.restype = ctypes.c_char_p
     _lib = lib
@@ -104,3 +112,21 @@ def workspace_bytes(problem: OalProblem, phase: int) -> int:
     n = load().oal_workspace_bytes(ctypes.byref(problem), phase)
     check(n)
     return int(n)
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(load().oal_launch_count())
+
+
+def profile_enable(on: bool) -> None:
+    load().oal_profile_enable(1 if on else 0)
+
+
+def profile_report() -> dict:
+    """{"kernel name": [launches, total milliseconds]} since the last report (synchronises)."""
+    import json
+
+    buf = ctypes.create_string_buffer(8192)
+    check(load().oal_profile_report(buf, len(buf)))
+    return json.loads(buf.value.decode())

@@ -2,6 +2,12 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
 #include "oal_common.cuh"
 #include "oal_kernels.h"
 
@@ -18,6 +24,38 @@ int fail_cuda(cudaError_t e, const char* where) {
   snprintf(g_error, sizeof(g_error), "%s: %s", where, cudaGetErrorString(e));
   return OAL_ERR_CUDA;
 }
+
+// ---- launch accounting and optional per-kernel timing -----------------------------------
+// Counterpart of the reference's opt-in stage profiler (oal_attention/hd_block_gemm_profiling.py):
+// a launch counter that is always on, and CUDA-event pairs around every launch when enabled.
+struct ProfEntry {
+  const char* name;
+  cudaEvent_t start, stop;
+};
+std::mutex g_prof_mutex;
+std::vector<ProfEntry> g_prof_entries;
+std::atomic<int> g_prof_enabled{0};
+std::atomic<long long> g_launches{0};
+
+struct LaunchScope {
+  cudaStream_t st;
+  bool timed = false;
+  ProfEntry entry{};
+  LaunchScope(const char* name, cudaStream_t stream, int launches = 1) : st(stream) {
+    g_launches += launches;
+    if (!g_prof_enabled.load()) return;
+    entry.name = name;
+    if (cudaEventCreate(&entry.start) != cudaSuccess || cudaEventCreate(&entry.stop) != cudaSuccess) return;
+    timed = true;
+    cudaEventRecord(entry.start, st);
+  }
+  ~LaunchScope() {
+    if (!timed) return;
+    cudaEventRecord(entry.stop, st);
+    std::lock_guard<std::mutex> lock(g_prof_mutex);
+    g_prof_entries.push_back(entry);
+  }
+};
 
 size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
@@ -118,6 +156,47 @@ const char* oal_last_error_string(void) { return g_error; }
 
 const char* oal_version_string(void) { return "oal_b200 0.1 sm_100a"; }
 
+int64_t oal_launch_count(void) { return g_launches.load(); }
+
+void oal_profile_enable(int enable) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  for (auto& e : g_prof_entries) {
+    cudaEventDestroy(e.start);
+    cudaEventDestroy(e.stop);
+  }
+  g_prof_entries.clear();
+  g_prof_enabled.store(enable ? 1 : 0);
+}
+
+int oal_profile_report(char* buffer, size_t capacity) {
+  std::lock_guard<std::mutex> lock(g_prof_mutex);
+  std::map<std::string, std::pair<int, double>> agg;
+  for (auto& e : g_prof_entries) {
+    if (cudaEventSynchronize(e.stop) != cudaSuccess) return fail(OAL_ERR_CUDA, "oal_profile_report: event synchronise failed");
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e.start, e.stop);
+    auto& slot = agg[e.name];
+    slot.first += 1;
+    slot.second += ms;
+    cudaEventDestroy(e.start);
+    cudaEventDestroy(e.stop);
+  }
+  g_prof_entries.clear();
+  std::string out = "{";
+  bool first = true;
+  for (auto& kv : agg) {
+    char item[160];
+    snprintf(item, sizeof(item), "%s\"%s\": [%d, %.6f]", first ? "" : ", ", kv.first.c_str(), kv.second.first,
+             kv.second.second);
+    out += item;
+    first = false;
+  }
+  out += "}";
+  if (!buffer || out.size() + 1 > capacity) return fail(OAL_ERR_ARGUMENT, "oal_profile_report: buffer too small");
+  memcpy(buffer, out.c_str(), out.size() + 1);
+  return OAL_OK;
+}
+
 int64_t oal_workspace_bytes(const OalProblem* p, int phase) {
   int rc = check_problem(p);
   if (rc) return rc;
@@ -145,7 +224,8 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
     if (state_in) return fail(OAL_ERR_ARGUMENT, "fp32_ieee mode keeps no chunk state: state_in must be NULL");
     oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
     a.out = out; a.num = num; a.den = den; a.accumulate = 0;
-    cudaError_t e = oal::pairs_forward(a, st);
+    cudaError_t e;
+    { LaunchScope scope("pairs_forward", st); e = oal::pairs_forward(a, st); }
     if (e != cudaSuccess) return fail_cuda(e, "forward pair kernel");
     return OAL_OK;
   }
@@ -154,20 +234,22 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
   if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_forward: workspace too small");
   if (!saved_state) return fail(OAL_ERR_ARGUMENT, "oal_forward: saved_state is NULL");
   const int units = p->batch * p->kv_heads, nb = chunk_count(p);
-  cudaError_t e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups,
-                                        s.coef_table, st);
+  cudaError_t e;
+  { LaunchScope scope("coef_table", st);
+    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, s.coef_table, st); }
   if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
-  e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st);
+  { LaunchScope scope("state_update", st); e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
-  e = oal::state_scan(s.ds, saved_state, state_in, nullptr, units, nb, 0, st);
+  { LaunchScope scope("state_scan", st); e = oal::state_scan(s.ds, saved_state, state_in, nullptr, units, nb, 0, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state scan kernel");
-  e = oal::cross_read(true, q, saved_state, s.coef_table, num, den, p->batch, p->q_heads,
-                      p->q_heads / p->kv_heads, p->seq_len, nb, p->scale, status, st);
+  { LaunchScope scope("cross_read_q", st);
+    e = oal::cross_read(true, q, saved_state, s.coef_table, num, den, p->batch, p->q_heads,
+                        p->q_heads / p->kv_heads, p->seq_len, nb, p->scale, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
   oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
   a.window = kChunk;
   a.out = out; a.num = num; a.den = den; a.accumulate = 1;
-  e = oal::pairs_forward(a, st);
+  { LaunchScope scope("pairs_forward", st); e = oal::pairs_forward(a, st); }
   if (e != cudaSuccess) return fail_cuda(e, "forward pair kernel");
   return OAL_OK;
 }
@@ -195,18 +277,21 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     BackwardSpace s = carve_backward(p, workspace);
     if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_backward: workspace too small");
     const size_t rows = (size_t)p->batch * p->q_heads * p->seq_len;
-    cudaError_t e = oal::norm_vjp(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor, s.g, rows, st);
+    cudaError_t e;
+    { LaunchScope scope("norm_vjp", st);
+      e = oal::norm_vjp(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor, s.g, rows, st); }
     if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
     oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
     a.g = s.g;
     if (mask & (OAL_GRAD_Q | OAL_GRAD_COEF)) {
       a.dq = (mask & OAL_GRAD_Q) ? dq : nullptr;
       a.coef_partial = (mask & OAL_GRAD_COEF) ? s.coef_pairs : nullptr;
-      e = oal::pairs_backward_q(a, st);
+      { LaunchScope scope("pairs_backward_q", st); e = oal::pairs_backward_q(a, st); }
       if (e != cudaSuccess) return fail_cuda(e, "backward query-side pair kernel");
       if (mask & OAL_GRAD_COEF) {
-        e = oal::reduce_coefs(s.coef_pairs, oal::pairs_tiles(p->seq_len), nullptr, 0, p->batch, p->q_heads,
-                              p->groups, d_coef_a, d_coef_b, d_coef_c, st);
+        { LaunchScope scope("reduce_coefs", st);
+          e = oal::reduce_coefs(s.coef_pairs, oal::pairs_tiles(p->seq_len), nullptr, 0, p->batch, p->q_heads,
+                                p->groups, d_coef_a, d_coef_b, d_coef_c, st); }
         if (e != cudaSuccess) return fail_cuda(e, "coefficient reduction kernel");
       }
     }
@@ -214,7 +299,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
       a.dq = nullptr; a.coef_partial = nullptr;
       a.dk = (mask & OAL_GRAD_K) ? dk : nullptr;
       a.dv = (mask & OAL_GRAD_V) ? dv : nullptr;
-      e = oal::pairs_backward_kv(a, st);
+      { LaunchScope scope("pairs_backward_kv", st); e = oal::pairs_backward_kv(a, st); }
       if (e != cudaSuccess) return fail_cuda(e, "backward key/value-side pair kernel");
     }
     return OAL_OK;

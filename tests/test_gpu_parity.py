@@ -160,3 +160,23 @@ def test_chunked_long_sequence_bf16_tensorcore():
     case = synthetic.qwen_head_case(4, batch=1, n=2048, hq=7, hkv=1, g=8, bf16=True)
     res = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
     assert_close(res, oracle_dense(case), TOL_BF16, label="bf16 N=2048")
+
+
+@pytest.mark.parametrize("precision,tol", [("fp32_ieee", TOL_FP32), ("bf16_tensorcore", TOL_BF16)])
+def test_qwen_n4096_rows_against_reference_golden(golden, precision, tol):
+    """Full headline sequence length for one KV head and its 7 query heads; the golden file keeps
+    every 64th token of the fp64 dense statement and of the reference's chunked fp32 path."""
+    g = golden("qwen_n4096_rows")
+    stride = int(g["row_stride"])
+    case = synthetic.qwen_head_case(1, batch=1, n=4096, hq=7, hkv=1, g=8, bf16=True)
+    assert synthetic.tensor_digest(case.q, case.k, case.v, case.dim_groups) == g["input_digest"]
+    io = torch.bfloat16 if precision == "bf16_tensorcore" else torch.float32
+    res = run_operator(case, precision=precision, io_dtype=io)
+    rows = {k: (v[:, :, ::stride] if v.ndim == 4 else v) for k, v in res.items()}
+    ref = {k[len("dense_"):]: v for k, v in g.items() if k.startswith("dense_")}
+    from oracle import oal_oracle as orc
+    factor = case.factor.double().clone().requires_grad_()
+    fa, fb, fc = orc.expand_factor(factor, 7, case.kernel_eps)
+    ((fa * ref["dA"]).sum() + (fb * ref["dB"]).sum() + (fc * ref["dC"]).sum()).backward()
+    ref["dfactor"] = factor.grad
+    assert_close(rows, ref, tol, keys=["out", "num", "den", "dq", "dk", "dv", "dfactor"], label=precision)
