@@ -132,6 +132,43 @@ size_t saved_state_bytes_tc(const OalProblem* p) {
   return (size_t)p->batch * p->kv_heads * chunk_count(p) * oal::state_image_bytes_per_chunk();
 }
 
+struct BackwardSpaceTC {
+  float* g;
+  float* coef_pairs;
+  void* gimg;
+  float* coef_table;
+  float* dcarry;
+  void* dt_img;
+  float* dcoef_partial;
+  float* dcoef;
+  float* slots;
+  float *dq_cross, *dk_cross, *dv_cross;
+  size_t bytes;
+};
+
+BackwardSpaceTC carve_backward_tc(const OalProblem* p, void* ws) {
+  Carver c(ws);
+  BackwardSpaceTC s;
+  const size_t units = (size_t)p->batch * p->kv_heads, nb = chunk_count(p);
+  const size_t qrows = (size_t)p->batch * p->q_heads * p->seq_len;
+  const size_t krows = (size_t)p->batch * p->kv_heads * p->seq_len;
+  const size_t slab_image = oal::state_image_bytes_per_chunk() / 17;
+  s.g = c.take<float>(qrows * oal::EP);
+  s.coef_pairs = c.take<float>((size_t)p->batch * p->q_heads * oal::pairs_tiles(p->seq_len) * oal::NCOEF);
+  s.gimg = c.take<char>((size_t)p->batch * p->q_heads * nb * slab_image);
+  s.coef_table = c.take<float>((size_t)p->q_heads * oal::state_rows());
+  s.dcarry = c.take<float>(units * nb * oal::state_rows() * oal::EP);
+  s.dt_img = c.take<char>(units * nb * oal::state_image_bytes_per_chunk());
+  s.dcoef_partial = c.take<float>((size_t)p->batch * nb * p->q_heads * oal::state_rows());
+  s.dcoef = c.take<float>((size_t)p->q_heads * oal::state_rows());
+  s.slots = c.take<float>((size_t)p->q_heads * oal::NCOEF);
+  s.dq_cross = c.take<float>(qrows * oal::HD);
+  s.dk_cross = c.take<float>(krows * oal::HD);
+  s.dv_cross = c.take<float>(krows * oal::VD);
+  s.bytes = c.off;
+  return s;
+}
+
 oal::PairArgs base_args(const OalProblem* p, const void* q, const void* k, const void* v,
                         const int32_t* perm, const int32_t* gstart, const float* A, const float* B,
                         const float* C, int32_t* status) {
@@ -207,7 +244,7 @@ int64_t oal_workspace_bytes(const OalProblem* p, int phase) {
   }
   if (phase == 0) return (int64_t)carve_forward_tc(p, nullptr).bytes;
   if (phase == 2) return (int64_t)saved_state_bytes_tc(p);
-  return (int64_t)carve_backward(p, nullptr).bytes;
+  return (int64_t)carve_backward_tc(p, nullptr).bytes;
 }
 
 int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
@@ -270,9 +307,8 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
   if ((mask & OAL_GRAD_V) && !dv) return fail(OAL_ERR_ARGUMENT, "dv requested but NULL");
   if ((mask & OAL_GRAD_COEF) && (!d_coef_a || !d_coef_b || !d_coef_c))
     return fail(OAL_ERR_ARGUMENT, "coefficient gradients requested but NULL");
-  (void)saved_state;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (p->precision == OAL_PRECISION_FP32_IEEE || true) {
+  if (p->precision == OAL_PRECISION_FP32_IEEE) {
     if (dstate_in) return fail(OAL_ERR_ARGUMENT, "fp32_ieee mode keeps no chunk state: dstate_in must be NULL");
     BackwardSpace s = carve_backward(p, workspace);
     if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_backward: workspace too small");
@@ -290,7 +326,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
       if (e != cudaSuccess) return fail_cuda(e, "backward query-side pair kernel");
       if (mask & OAL_GRAD_COEF) {
         { LaunchScope scope("reduce_coefs", st);
-          e = oal::reduce_coefs(s.coef_pairs, oal::pairs_tiles(p->seq_len), nullptr, 0, p->batch, p->q_heads,
+          e = oal::reduce_coefs(s.coef_pairs, oal::pairs_tiles(p->seq_len), nullptr, p->batch, p->q_heads,
                                 p->groups, d_coef_a, d_coef_b, d_coef_c, st); }
         if (e != cudaSuccess) return fail_cuda(e, "coefficient reduction kernel");
       }
@@ -304,7 +340,81 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     }
     return OAL_OK;
   }
-  return fail(OAL_ERR_ARGUMENT, "bf16_tensorcore is not available in this build");
+  // bf16_tensorcore
+  if (!saved_state) return fail(OAL_ERR_ARGUMENT, "oal_backward: saved_state is NULL");
+  BackwardSpaceTC s = carve_backward_tc(p, workspace);
+  if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_backward: workspace too small");
+  const int nb = chunk_count(p), units = p->batch * p->kv_heads, rep = p->q_heads / p->kv_heads;
+  const bool want_q = mask & OAL_GRAD_Q, want_k = mask & OAL_GRAD_K, want_v = mask & OAL_GRAD_V;
+  const bool want_c = mask & OAL_GRAD_COEF;
+  cudaError_t e;
+  { LaunchScope scope("norm_vjp", st);
+    e = oal::norm_vjp_image(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor, s.g, s.gimg,
+                            p->batch * p->q_heads, p->seq_len, nb, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
+  { LaunchScope scope("coef_table", st);
+    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, s.coef_table, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
+  if (want_k || want_v || want_c) {
+    { LaunchScope scope("dstate_heads", st);
+      e = oal::dstate_heads(q, s.gimg, want_c ? saved_state : nullptr, s.coef_table, s.dcarry,
+                            want_c ? s.dcoef_partial : nullptr, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
+                            p->scale, status, st); }
+    if (e != cudaSuccess) return fail_cuda(e, "state gradient kernel");
+  }
+  if (want_k || want_v) {
+    { LaunchScope scope("state_scan_reverse", st);
+      e = oal::state_scan(s.dcarry, s.dt_img, dstate_in, nullptr, units, nb, 1, st); }
+    if (e != cudaSuccess) return fail_cuda(e, "reverse state scan kernel");
+  }
+  oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
+  a.window = kChunk;
+  a.g = s.g;
+  if (want_q || want_c) {
+    if (want_q) {
+      { LaunchScope scope("feature_grad_q", st);
+        e = oal::feature_grad(true, q, s.gimg, nullptr, saved_state, s.coef_table, s.dq_cross, p->batch, p->q_heads,
+                              rep, p->seq_len, nb, p->scale, p->scale, status, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "query feature gradient kernel");
+    }
+    a.dq = want_q ? dq : nullptr;
+    a.dq_init = want_q ? s.dq_cross : nullptr;
+    a.coef_partial = want_c ? s.coef_pairs : nullptr;
+    { LaunchScope scope("pairs_backward_q", st); e = oal::pairs_backward_q(a, st); }
+    if (e != cudaSuccess) return fail_cuda(e, "backward query-side pair kernel");
+    if (want_c) {
+      { LaunchScope scope("dcoef_reduce", st, 2);
+        e = oal::dcoef_reduce(s.dcoef_partial, p->batch * nb, p->q_heads, dim_perm, group_start, s.dcoef, s.slots, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "coefficient gradient reduction kernels");
+      { LaunchScope scope("reduce_coefs", st);
+        e = oal::reduce_coefs(s.coef_pairs, oal::pairs_tiles(p->seq_len), s.slots, p->batch, p->q_heads, p->groups,
+                              d_coef_a, d_coef_b, d_coef_c, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "coefficient reduction kernel");
+    }
+  }
+  if (want_k || want_v) {
+    if (want_k) {
+      { LaunchScope scope("feature_grad_k", st);
+        e = oal::feature_grad(false, k, nullptr, v, s.dt_img, nullptr, s.dk_cross, p->batch, p->kv_heads, 1,
+                              p->seq_len, nb, 1.f, 1.f, status, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "key feature gradient kernel");
+    }
+    if (want_v) {
+      { LaunchScope scope("cross_read_k", st);
+        e = oal::cross_read(false, k, s.dt_img, nullptr, s.dv_cross, nullptr, p->batch, p->kv_heads, 1, p->seq_len,
+                            nb, 1.f, status, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "key cross read kernel");
+    }
+    a.dq = nullptr; a.dq_init = nullptr; a.coef_partial = nullptr;
+    a.dk = want_k ? dk : nullptr;
+    a.dv = want_v ? dv : nullptr;
+    a.dk_init = want_k ? s.dk_cross : nullptr;
+    a.dv_init = want_v ? s.dv_cross : nullptr;
+    { LaunchScope scope("pairs_backward_kv", st); e = oal::pairs_backward_kv(a, st); }
+    if (e != cudaSuccess) return fail_cuda(e, "backward key/value-side pair kernel");
+  }
+  return OAL_OK;
+
 }
 
 }  // extern "C"

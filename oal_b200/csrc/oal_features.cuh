@@ -119,4 +119,24 @@ __device__ __forceinline__ void load_row_bf16(float (&x)[HD], const __nv_bfloat1
   }
 }
 
+// Bounded mbarrier waits for one CTA: the first wait that expires raises a shared flag and every
+// later wait returns at once, so a kernel always terminates; the flag ends up in the status word.
+struct Waiter {
+  int* dead;          // shared flag: a wait expired somewhere in this CTA
+  __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity) {
+    if (*reinterpret_cast<volatile int*>(dead)) return;
+    if (!umma::mbar_wait(bar, parity)) *reinterpret_cast<volatile int*>(dead) = 1;
+  }
+};
+
+
+// 16-byte image chunk (8 consecutive e of one token) of U = [v | 1 | 0]
+__device__ __forceinline__ uint4 u_image_chunk(const __nv_bfloat16* vrow, int ec, bool valid) {
+  if (!valid) return make_uint4(0u, 0u, 0u, 0u);
+  if (ec < VD / 8) return *reinterpret_cast<const uint4*>(vrow + 8 * ec);
+  if (ec == VD / 8) return make_uint4(0x00003F80u, 0u, 0u, 0u);   // bf16(1.0) in element 0
+  return make_uint4(0u, 0u, 0u, 0u);
+}
+
+
 }  // namespace oal

@@ -37,7 +37,8 @@ cudaError_t norm_vjp(const void* grad_out, int out_dt, const float* grad_num, co
                      const float* num, const float* den, float floor_v, float* g, size_t rows,
                      cudaStream_t st);
 
-cudaError_t reduce_coefs(const float* p0, int tiles0, const float* p1, int tiles1, int B, int Hq, int G,
+// extra: [Hq][NCOEF] slots already summed over the batch (cross-chunk term), or null
+cudaError_t reduce_coefs(const float* p0, int tiles0, const float* extra, int B, int Hq, int G,
                          float* dA, float* dB, float* dC, cudaStream_t st);
 
 // ---- tensor-core state kernels (oal_state.cu) ---------------------------------------
@@ -53,5 +54,19 @@ cudaError_t state_scan(const float* ds, void* image, const float* state_in, floa
 cudaError_t cross_read(bool query, const void* x, const void* image, const float* coef_table, float* out64,
                        float* out1, int B, int H, int rep, int N, int NB, float mul, int32_t* status,
                        cudaStream_t st);
+
+
+// ---- tensor-core backward kernels (oal_state_bwd.cu) ----------------------------------
+cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img, const float* coef_table,
+                         float* dcarry, float* dcoef_partial, int B, int Hq, int Hkv, int N, int NB, float scale,
+                         int32_t* status, cudaStream_t st);
+cudaError_t feature_grad(bool query, const void* x, const void* gimg, const void* v, const void* image,
+                         const float* coef_table, float* dx, int B, int H, int rep, int N, int NB, float mul,
+                         float outmul, int32_t* status, cudaStream_t st);
+cudaError_t dcoef_reduce(const float* partial, int outer, int Hq, const int32_t* dim_perm,
+                         const int32_t* group_start, float* dcoef, float* slots, cudaStream_t st);
+cudaError_t norm_vjp_image(const void* grad_out, int out_dt, const float* grad_num, const float* grad_den,
+                           const float* num, const float* den, float floor_v, float* g, void* gimg, int heads,
+                           int N, int NB, cudaStream_t st);
 
 }  // namespace oal

@@ -619,9 +619,9 @@ __global__ void __launch_bounds__(256) norm_vjp_kernel(const void* grad_out, int
 }
 
 // Fixed-order reduction of the per-tile coefficient partial sums.
-//   partial [B][Hq][tiles][NCOEF]  (+ optional second buffer of the same shape)
-__global__ void reduce_coefs_kernel(const float* p0, int tiles0, const float* p1, int tiles1, int B,
-                                    int Hq, int G, float* dA, float* dB, float* dC) {
+//   partial [B][Hq][tiles][NCOEF]; extra [Hq][NCOEF] (already summed over the batch) or null
+__global__ void reduce_coefs_kernel(const float* p0, int tiles0, const float* extra, int B, int Hq, int G,
+                                    float* dA, float* dB, float* dC) {
   const int h = blockIdx.x;
   for (int x = threadIdx.x; x < 1 + G + G * G; x += blockDim.x) {
     int slot;
@@ -631,11 +631,9 @@ __global__ void reduce_coefs_kernel(const float* p0, int tiles0, const float* p1
       int g = (x - 1 - G) / G, g2 = (x - 1 - G) % G;
       slot = 1 + GMAX + (g <= g2 ? tri_index(g, g2) : tri_index(g2, g));
     }
-    float t = 0.f;
-    for (int b = 0; b < B; ++b) {
+    float t = extra ? extra[(size_t)h * NCOEF + slot] : 0.f;
+    for (int b = 0; b < B; ++b)
       for (int i = 0; i < tiles0; ++i) t += p0[((size_t)(b * Hq + h) * tiles0 + i) * NCOEF + slot];
-      for (int i = 0; i < tiles1; ++i) t += p1[((size_t)(b * Hq + h) * tiles1 + i) * NCOEF + slot];
-    }
     if (x == 0) dA[h] = t;
     else if (x <= G) dB[h * G + x - 1] = t;
     else dC[(size_t)h * G * G + (x - 1 - G)] = t;
@@ -698,9 +696,9 @@ cudaError_t norm_vjp(const void* grad_out, int out_dt, const float* grad_num, co
   return cudaGetLastError();
 }
 
-cudaError_t reduce_coefs(const float* p0, int tiles0, const float* p1, int tiles1, int B, int Hq, int G,
+cudaError_t reduce_coefs(const float* p0, int tiles0, const float* extra, int B, int Hq, int G,
                          float* dA, float* dB, float* dC, cudaStream_t st) {
-  reduce_coefs_kernel<<<Hq, 128, 0, st>>>(p0, tiles0, p1, tiles1, B, Hq, G, dA, dB, dC);
+  reduce_coefs_kernel<<<Hq, 128, 0, st>>>(p0, tiles0, extra, B, Hq, G, dA, dB, dC);
   return cudaGetLastError();
 }
 

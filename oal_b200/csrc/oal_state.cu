@@ -22,14 +22,6 @@ using namespace umma;
 __device__ __forceinline__ int group_first_slab(int g) { return g == 0 ? 0 : 1 + 4 * g; }   // 0,5,9,13
 __device__ __forceinline__ int group_slab_count(int g) { return g == 0 ? 5 : 4; }
 
-struct Waiter {
-  int* dead;          // shared flag: a wait expired somewhere in this CTA
-  __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity) {
-    if (*reinterpret_cast<volatile int*>(dead)) return;
-    if (!mbar_wait(bar, parity)) *reinterpret_cast<volatile int*>(dead) = 1;
-  }
-};
-
 // ---------------------------------------------------------------------------
 // per-head coefficient table in feature order (fp32 [Hq][F_ROWS])
 // ---------------------------------------------------------------------------
@@ -60,14 +52,6 @@ __global__ void coef_table_kernel(const int32_t* dim_perm, const int32_t* group_
     }
     table[(size_t)h * F_ROWS + f] = v;
   }
-}
-
-// 16-byte image chunk (8 consecutive e of one token) of U = [v | 1 | 0]
-__device__ __forceinline__ uint4 u_image_chunk(const __nv_bfloat16* vrow, int ec, bool valid) {
-  if (!valid) return make_uint4(0u, 0u, 0u, 0u);
-  if (ec < VD / 8) return *reinterpret_cast<const uint4*>(vrow + 8 * ec);
-  if (ec == VD / 8) return make_uint4(0x00003F80u, 0u, 0u, 0u);   // bf16(1.0) in element 0
-  return make_uint4(0u, 0u, 0u, 0u);
 }
 
 // ---------------------------------------------------------------------------
