@@ -133,6 +133,27 @@ int oal_backward(const OalProblem* problem, const void* q, const void* k, const 
                  float* d_coef_b, float* d_coef_c, const float* dstate_in, void* workspace,
                  size_t workspace_bytes, int32_t* status, void* stream);
 
+/*
+ * Forward for callers that cannot allocate (no counterpart in the reference, which allocates every
+ * buffer with torch.empty).  Same computation and outputs as oal_forward in bf16_tensorcore mode, but
+ * the scratch memory comes from a fixed array inside the library instead of a caller workspace, and
+ * the call performs no cudaMalloc / cudaFree or other allocating call.  Meant for hosts whose device
+ * memory is frozen after start-up (serving processes with a pre-carved pool, plugins run from
+ * allocator-free callbacks).
+ *   Limits: batch * kv_heads * ceil(seq_len / 128) <= 16 and q_heads <= 64; larger problems return
+ *   OAL_ERR_WORKSPACE.  The array (about 11.7 MB) is resident on every GPU that loads the library.
+ *   The first call on each device resolves the array's device address; make that call outside any
+ *   stream capture, with the device current.
+ *   All calls on a device share the array and it keeps the previous call's contents; every element
+ *   that is read is rewritten first, so nothing needs clearing, but two calls that overlap on the GPU
+ *   (different streams, or different host threads) race on it: serialise them.
+ *   saved_state still belongs to the caller (oal_workspace_bytes(problem, 2) bytes).
+ */
+int oal_forward_static_scratch(const OalProblem* problem, const void* q, const void* k, const void* v,
+                               const int32_t* dim_perm, const int32_t* group_start, const float* coef_a,
+                               const float* coef_b, const float* coef_c, void* out, float* num, float* den,
+                               void* saved_state, int32_t* status, void* stream);
+
 /* Text of the last error returned on the calling thread (host pointer, never NULL). */
 const char* oal_last_error_string(void);
 

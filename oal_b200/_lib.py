@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "oal_launch_count",
     "oal_profile_enable",
     "oal_profile_report",
+    "oal_forward_static_scratch",
 )
 
 
@@ -76,6 +77,9 @@ def load() -> ctypes.CDLL:
     lib.oal_forward.argtypes = [pp, vp, vp, vp, i32p, i32p, f32p, f32p, f32p, vp, f32p, f32p, vp, f32p,
                                 vp, ctypes.c_size_t, i32p, vp]
     lib.oal_forward.restype = ctypes.c_int
+    lib.oal_forward_static_scratch.argtypes = [pp, vp, vp, vp, i32p, i32p, f32p, f32p, f32p, vp, f32p, f32p, vp,
+                                               i32p, vp]
+    lib.oal_forward_static_scratch.restype = ctypes.c_int
     lib.oal_backward.argtypes = [pp, vp, vp, vp, i32p, i32p, f32p, f32p, f32p, f32p, f32p, vp, vp, f32p,
                                  f32p, vp, vp, vp, f32p, f32p, f32p, f32p, vp, ctypes.c_size_t, i32p, vp]
     lib.oal_backward.restype = ctypes.c_int

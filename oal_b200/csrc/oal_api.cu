@@ -417,4 +417,87 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
 
 }
 
+// ---------------------------------------------------------------------------------------------
+// Forward with library-owned scratch (no caller workspace, no allocation of any kind).
+//
+// Some hosts of this library cannot obtain device memory at call time: an inference server whose
+// memory pool was carved up and frozen at start-up, a plugin that runs inside someone else's
+// allocator-free execution callback, a process near its memory limit where cudaMalloc may fail or
+// stall.  For them the tensor-core forward keeps its two scratch buffers -- the per-head coefficient
+// table and the per-chunk state increments -- in the file-scope device array below.  The array has
+// a fixed size, so the entry point only accepts problems up to kStaticMaxUnitChunks (batch x KV heads
+// x 128-token chunks) and kStaticMaxHeads query heads; every GPU that loads the library holds the
+// array (about 11.7 MB) until the process exits.
+// ---------------------------------------------------------------------------------------------
+constexpr int kStaticMaxUnitChunks = 16;
+constexpr int kStaticMaxHeads = 64;
+constexpr size_t kStaticStateFloats = (size_t)kStaticMaxUnitChunks * 2176 * OAL_E_PAD;
+constexpr size_t kStaticTableFloats = (size_t)kStaticMaxHeads * 2176;
+static __device__ __align__(256) float g_static_scratch[kStaticTableFloats + kStaticStateFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_static_scratch on the current device, resolved once per device.  In host code
+// the array's name is only a handle for the runtime, not an address a kernel could use.
+int static_scratch_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kMaxDevices) return fail(OAL_ERR_ARGUMENT, "device ordinal out of range for the static scratch table");
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[dev]) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static scratch)");
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return OAL_OK;
+}
+}  // namespace
+
+int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k, const void* v,
+                               const int32_t* dim_perm, const int32_t* group_start, const float* coef_a,
+                               const float* coef_b, const float* coef_c, void* out, float* num, float* den,
+                               void* saved_state, int32_t* status, void* stream) {
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (p->precision != OAL_PRECISION_BF16_TENSORCORE)
+    return fail(OAL_ERR_DTYPE, "oal_forward_static_scratch: only bf16_tensorcore uses scratch memory (fp32_ieee forward needs none: call oal_forward)");
+  if (!q || !k || !v || !dim_perm || !group_start || !coef_a || !coef_b || !coef_c || !out || !num || !den || !status || !saved_state)
+    return fail(OAL_ERR_ARGUMENT, "oal_forward_static_scratch: NULL tensor pointer");
+  const int units = p->batch * p->kv_heads, nb = chunk_count(p);
+  if ((long long)units * nb > kStaticMaxUnitChunks)
+    return fail(OAL_ERR_WORKSPACE, "oal_forward_static_scratch: batch x kv_heads x ceil(seq_len/128) exceeds the static scratch limit of 16; use oal_forward with a caller workspace");
+  if (p->q_heads > kStaticMaxHeads)
+    return fail(OAL_ERR_WORKSPACE, "oal_forward_static_scratch: more than 64 query heads; use oal_forward with a caller workspace");
+  float* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  float* coef_table = scratch;
+  float* ds = scratch + kStaticTableFloats;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  { LaunchScope scope("coef_table", st);
+    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, coef_table, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
+  { LaunchScope scope("state_update", st); e = oal::state_update(k, v, ds, units, p->seq_len, nb, status, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
+  { LaunchScope scope("state_scan", st); e = oal::state_scan(ds, saved_state, nullptr, nullptr, units, nb, 0, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "state scan kernel");
+  { LaunchScope scope("cross_read_q", st);
+    e = oal::cross_read(true, q, saved_state, coef_table, num, den, p->batch, p->q_heads, p->q_heads / p->kv_heads,
+                        p->seq_len, nb, p->scale, status, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
+  oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
+  a.window = kChunk;
+  a.out = out; a.num = num; a.den = den; a.accumulate = 1;
+  { LaunchScope scope("pairs_forward", st); e = oal::pairs_forward(a, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "forward pair kernel");
+  return OAL_OK;
+}
+
 }  // extern "C"
