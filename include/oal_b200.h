@@ -60,7 +60,12 @@ enum {
 
 /* gradient request mask, same order as the reference's requested_gradient_mask
  * (oal_attention/hd_block_gemm_adapters.py:27-43): q, k, v, A, B, C */
-enum { OAL_GRAD_Q = 1, OAL_GRAD_K = 2, OAL_GRAD_V = 4, OAL_GRAD_COEF = 8 };
+enum {
+  OAL_GRAD_Q = 1, OAL_GRAD_K = 2, OAL_GRAD_V = 4, OAL_GRAD_COEF = 8,
+  /* oal_backward only: the workspace still holds what oal_backward_local_state computed for this
+   * very call (same problem, same workspace, nothing launched on it in between): skip that stage */
+  OAL_GRAD_REUSE_STATE_STAGE = 16
+};
 
 typedef struct OalProblem {
   int32_t batch;        /* B                                                            */
@@ -99,10 +104,9 @@ int64_t oal_workspace_bytes(const OalProblem* problem, int phase);
  *   out [B,Hq,N,64] out_dtype; num fp32 [B,Hq,N,64]; den fp32 [B,Hq,N]
  *   saved_state: oal_workspace_bytes(problem, 2) bytes kept for the backward
  *              (may be NULL when that size is 0)
- *   state_in / state_total: sequence parallelism, both may be NULL.  state_in is
- *              the fp32 state [B,Hkv,OAL_STATE_ROWS,OAL_E_PAD] accumulated by the
- *              ranks that own earlier tokens; state_total receives this rank's own
- *              contribution in the same layout (see oal_forward_local_state).
+ *   state_in:  sequence parallelism, may be NULL: the fp32 state
+ *              [B*Hkv, OAL_STATE_ROWS, OAL_E_PAD] accumulated by the ranks that own earlier
+ *              tokens (see oal_forward_local_state).
  */
 int oal_forward(const OalProblem* problem, const void* q, const void* k, const void* v,
                 const int32_t* dim_perm, const int32_t* group_start, const float* coef_a,
@@ -132,6 +136,27 @@ int oal_backward(const OalProblem* problem, const void* q, const void* k, const 
                  const float* grad_den, void* dq, void* dk, void* dv, float* d_coef_a,
                  float* d_coef_b, float* d_coef_c, const float* dstate_in, void* workspace,
                  size_t workspace_bytes, int32_t* status, void* stream);
+
+/*
+ * Sequence parallelism (new; the reference is single-GPU, there is nothing to be compatible with).
+ * A rank that owns a contiguous token range first computes the sum of its own chunk-state
+ * increments, the ranks exchange these (one all-gather of batch*kv_heads*OAL_STATE_ROWS*OAL_E_PAD
+ * floats), and each rank passes the sum over the ranks before it as `state_in` to oal_forward.
+ * Backward mirrors it with the state gradient: oal_backward_local_state, exchange, sum over the
+ * ranks after it as `dstate_in` to oal_backward (with OAL_GRAD_REUSE_STATE_STAGE when the same
+ * workspace is passed to both calls back to back).
+ *   state_total / dstate_total: fp32 [batch*kv_heads, OAL_STATE_ROWS, OAL_E_PAD]
+ *   workspace: oal_workspace_bytes(problem, 0) for the forward call, (problem, 1) for the backward.
+ */
+#define OAL_STATE_ROWS 2176
+int oal_forward_local_state(const OalProblem* problem, const void* k, const void* v, float* state_total,
+                            void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+int oal_backward_local_state(const OalProblem* problem, const void* q, const int32_t* dim_perm,
+                             const int32_t* group_start, const float* coef_a, const float* coef_b,
+                             const float* coef_c, const float* num, const float* den, const void* saved_state,
+                             const void* grad_out, const float* grad_num, const float* grad_den,
+                             float* dstate_total, void* workspace, size_t workspace_bytes, int32_t* status,
+                             void* stream);
 
 /*
  * Forward for callers that cannot allocate (no counterpart in the reference, which allocates every

@@ -20,7 +20,8 @@ E_PAD = 80
 DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 PRECISION_CODES = {"fp32_ieee": 0, "bf16_tensorcore": 1}
 
-GRAD_Q, GRAD_K, GRAD_V, GRAD_COEF = 1, 2, 4, 8
+GRAD_Q, GRAD_K, GRAD_V, GRAD_COEF, GRAD_REUSE_STATE_STAGE = 1, 2, 4, 8, 16
+STATE_ROWS = 2176
 STATUS_NONFINITE, STATUS_DENOMINATOR, STATUS_WAIT_TIMEOUT = 1, 2, 4
 
 # every symbol include/oal_b200.h declares
@@ -35,6 +36,8 @@ EXPORTED_SYMBOLS = (
     "oal_profile_enable",
     "oal_profile_report",
     "oal_forward_static_scratch",
+    "oal_forward_local_state",
+    "oal_backward_local_state",
 )
 
 
@@ -80,6 +83,11 @@ def load() -> ctypes.CDLL:
     lib.oal_forward_static_scratch.argtypes = [pp, vp, vp, vp, i32p, i32p, f32p, f32p, f32p, vp, f32p, f32p, vp,
                                                i32p, vp]
     lib.oal_forward_static_scratch.restype = ctypes.c_int
+    lib.oal_forward_local_state.argtypes = [pp, vp, vp, f32p, vp, ctypes.c_size_t, i32p, vp]
+    lib.oal_forward_local_state.restype = ctypes.c_int
+    lib.oal_backward_local_state.argtypes = [pp, vp, i32p, i32p, f32p, f32p, f32p, f32p, f32p, vp, vp, f32p, f32p,
+                                             f32p, vp, ctypes.c_size_t, i32p, vp]
+    lib.oal_backward_local_state.restype = ctypes.c_int
     lib.oal_backward.argtypes = [pp, vp, vp, vp, i32p, i32p, f32p, f32p, f32p, f32p, f32p, vp, vp, f32p,
                                  f32p, vp, vp, vp, f32p, f32p, f32p, f32p, vp, ctypes.c_size_t, i32p, vp]
     lib.oal_backward.restype = ctypes.c_int

@@ -169,6 +169,33 @@ BackwardSpaceTC carve_backward_tc(const OalProblem* p, void* ws) {
   return s;
 }
 
+// Stage A of the tensor-core backward: everything that does not depend on later tokens' state
+// gradient (normalisation VJP, coefficient table, per-chunk dCarry and coefficient partial sums).
+int backward_state_stage(const OalProblem* p, const void* q, const int32_t* dim_perm, const int32_t* group_start,
+                         const float* coef_a, const float* coef_b, const float* coef_c, const float* num,
+                         const float* den, const void* saved_state, const void* grad_out, const float* grad_num,
+                         const float* grad_den, const BackwardSpaceTC& s, int32_t* status, cudaStream_t st) {
+  const int nb = chunk_count(p);
+  const int mask = p->grad_mask;
+  const bool want_c = mask & OAL_GRAD_COEF;
+  cudaError_t e;
+  { LaunchScope scope("norm_vjp", st);
+    e = oal::norm_vjp_image(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor, s.g, s.gimg,
+                            p->batch * p->q_heads, p->seq_len, nb, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
+  { LaunchScope scope("coef_table", st);
+    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, s.coef_table, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
+  if (mask & (OAL_GRAD_K | OAL_GRAD_V | OAL_GRAD_COEF)) {
+    { LaunchScope scope("dstate_heads", st);
+      e = oal::dstate_heads(q, s.gimg, want_c ? saved_state : nullptr, s.coef_table, s.dcarry,
+                            want_c ? s.dcoef_partial : nullptr, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
+                            p->scale, status, st); }
+    if (e != cudaSuccess) return fail_cuda(e, "state gradient kernel");
+  }
+  return OAL_OK;
+}
+
 oal::PairArgs base_args(const OalProblem* p, const void* q, const void* k, const void* v,
                         const int32_t* perm, const int32_t* gstart, const float* A, const float* B,
                         const float* C, int32_t* status) {
@@ -348,19 +375,10 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
   const bool want_q = mask & OAL_GRAD_Q, want_k = mask & OAL_GRAD_K, want_v = mask & OAL_GRAD_V;
   const bool want_c = mask & OAL_GRAD_COEF;
   cudaError_t e;
-  { LaunchScope scope("norm_vjp", st);
-    e = oal::norm_vjp_image(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor, s.g, s.gimg,
-                            p->batch * p->q_heads, p->seq_len, nb, st); }
-  if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
-  { LaunchScope scope("coef_table", st);
-    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, s.coef_table, st); }
-  if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
-  if (want_k || want_v || want_c) {
-    { LaunchScope scope("dstate_heads", st);
-      e = oal::dstate_heads(q, s.gimg, want_c ? saved_state : nullptr, s.coef_table, s.dcarry,
-                            want_c ? s.dcoef_partial : nullptr, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
-                            p->scale, status, st); }
-    if (e != cudaSuccess) return fail_cuda(e, "state gradient kernel");
+  if (!(mask & OAL_GRAD_REUSE_STATE_STAGE)) {
+    rc = backward_state_stage(p, q, dim_perm, group_start, coef_a, coef_b, coef_c, num, den, saved_state, grad_out,
+                              grad_num, grad_den, s, status, st);
+    if (rc) return rc;
   }
   if (want_k || want_v) {
     { LaunchScope scope("state_scan_reverse", st);
@@ -415,6 +433,51 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
   }
   return OAL_OK;
 
+}
+
+int oal_forward_local_state(const OalProblem* p, const void* k, const void* v, float* state_total, void* workspace,
+                            size_t workspace_bytes, int32_t* status, void* stream) {
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (p->precision != OAL_PRECISION_BF16_TENSORCORE)
+    return fail(OAL_ERR_DTYPE, "oal_forward_local_state: chunk states exist only in bf16_tensorcore mode");
+  if (!k || !v || !state_total || !status) return fail(OAL_ERR_ARGUMENT, "oal_forward_local_state: NULL tensor pointer");
+  ForwardSpaceTC s = carve_forward_tc(p, workspace);
+  if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_forward_local_state: workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int units = p->batch * p->kv_heads, nb = chunk_count(p);
+  cudaError_t e;
+  { LaunchScope scope("state_update", st); e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
+  { LaunchScope scope("state_total", st); e = oal::state_scan(s.ds, nullptr, nullptr, state_total, units, nb, 0, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "state total kernel");
+  return OAL_OK;
+}
+
+int oal_backward_local_state(const OalProblem* p, const void* q, const int32_t* dim_perm, const int32_t* group_start,
+                             const float* coef_a, const float* coef_b, const float* coef_c, const float* num,
+                             const float* den, const void* saved_state, const void* grad_out, const float* grad_num,
+                             const float* grad_den, float* dstate_total, void* workspace, size_t workspace_bytes,
+                             int32_t* status, void* stream) {
+  int rc = check_problem(p);
+  if (rc) return rc;
+  if (p->precision != OAL_PRECISION_BF16_TENSORCORE)
+    return fail(OAL_ERR_DTYPE, "oal_backward_local_state: chunk states exist only in bf16_tensorcore mode");
+  if (!q || !dim_perm || !group_start || !coef_a || !coef_b || !coef_c || !num || !den || !saved_state || !dstate_total || !status)
+    return fail(OAL_ERR_ARGUMENT, "oal_backward_local_state: NULL tensor pointer");
+  BackwardSpaceTC s = carve_backward_tc(p, workspace);
+  if (!workspace || workspace_bytes < s.bytes) return fail(OAL_ERR_WORKSPACE, "oal_backward_local_state: workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  OalProblem local = *p;
+  local.grad_mask |= OAL_GRAD_K;      // dCarry is needed whatever the caller finally asks for
+  rc = backward_state_stage(&local, q, dim_perm, group_start, coef_a, coef_b, coef_c, num, den, saved_state, grad_out,
+                            grad_num, grad_den, s, status, st);
+  if (rc) return rc;
+  cudaError_t e;
+  { LaunchScope scope("state_total", st);
+    e = oal::state_scan(s.dcarry, nullptr, nullptr, dstate_total, p->batch * p->kv_heads, chunk_count(p), 1, st); }
+  if (e != cudaSuccess) return fail_cuda(e, "state gradient total kernel");
+  return OAL_OK;
 }
 
 // ---------------------------------------------------------------------------------------------

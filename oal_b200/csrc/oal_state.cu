@@ -170,9 +170,11 @@ __global__ void __launch_bounds__(256) state_scan_kernel(const float* ds, __nv_b
     const int c = reverse ? NB - 1 - n : n;
     const float4* p = reinterpret_cast<const float4*>(ds + (((size_t)u * NB + c) * F_ROWS + f) * EP + 8 * ec);
     const float4 a0 = p[0], a1 = p[1];
-    uint4 o = make_uint4(pack_bf16(run[0], run[1]), pack_bf16(run[2], run[3]), pack_bf16(run[4], run[5]),
-                         pack_bf16(run[6], run[7]));
-    reinterpret_cast<uint4*>(image)[((((size_t)u * NB + c) * F_SLABS + slab) * (EP / 8) + ec) * 128 + fr] = o;
+    if (image) {
+      uint4 o = make_uint4(pack_bf16(run[0], run[1]), pack_bf16(run[2], run[3]), pack_bf16(run[4], run[5]),
+                           pack_bf16(run[6], run[7]));
+      reinterpret_cast<uint4*>(image)[((((size_t)u * NB + c) * F_SLABS + slab) * (EP / 8) + ec) * 128 + fr] = o;
+    }
     run[0] += a0.x; run[1] += a0.y; run[2] += a0.z; run[3] += a0.w;
     run[4] += a1.x; run[5] += a1.y; run[6] += a1.z; run[7] += a1.w;
   }

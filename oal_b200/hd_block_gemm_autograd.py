@@ -120,8 +120,12 @@ def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: flo
 
 
 def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scale, floor,
-                  plan: HDParallelBlockPlan, mask, grad_out, grad_num, grad_den, *, dstate_in=None):
-    """Launch the backward kernels; returns (dq, dk, dv, dA, dB, dC) with None where not requested."""
+                  plan: HDParallelBlockPlan, mask, grad_out, grad_num, grad_den, *, dstate_in=None,
+                  workspace=None, reuse_state_stage=False):
+    """Launch the backward kernels; returns (dq, dk, dv, dA, dB, dC) with None where not requested.
+
+    ``workspace`` / ``reuse_state_stage``: sequence parallelism passes the workspace that
+    ``oal_backward_local_state`` has just filled so that stage is not computed twice."""
     lib = _lib.load()
     qp, kp, vp, a32, b32, c32 = saved_inputs
     B, Hq, Hkv, N, D, Dv = plan.geometry
@@ -131,7 +135,8 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
     bits = _grad_bits(mask)
     problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=qp.dtype, out_dtype=kernel_out,
                            precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
-                           floor=float(floor), grad_mask=bits)
+                           floor=float(floor),
+                           grad_mask=bits | (_lib.GRAD_REUSE_STATE_STAGE if reuse_state_stage else 0))
 
     def prep(gt, dtype, width):
         if gt is None:
@@ -153,7 +158,8 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
     dB = torch.empty(Hq, G, dtype=torch.float32, device=dev) if bits & _lib.GRAD_COEF else None
     dC = torch.empty(Hq, G, G, dtype=torch.float32, device=dev) if bits & _lib.GRAD_COEF else None
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    ws = torch.empty(max(plan.backward_workspace_bytes, 16), dtype=torch.uint8, device=dev)
+    ws = workspace if workspace is not None else torch.empty(max(plan.backward_workspace_bytes, 16),
+                                                             dtype=torch.uint8, device=dev)
     rc = lib.oal_backward(ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(kp), _lib.ptr(vp),
                           _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start), _lib.ptr(a32),
                           _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(num_p), _lib.ptr(den.contiguous()),
