@@ -25,7 +25,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -58,52 +57,52 @@ def measured_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.samples, self.max_mhz, self.bits = index, [], None, 0
+        self.stop, self.thread, self.error = threading.Event(), None, None
+
+    def _run(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            while not self.stop.is_set():
+                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                try:
+                    self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                except Exception:
+                    self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                time.sleep(0.005)
+        except Exception as exc:      # NVML missing: report no samples rather than fail the run
+            self.error = repr(exc)
 
     def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+        time.sleep(0.05)
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
-
     def __exit__(self, *exc):
-        if self.proc:
-            self.proc.terminate()
-            self.proc.wait(timeout=5)
+        self.stop.set()
+        self.thread.join(timeout=5)
 
     def summary(self) -> dict:
-        sm, mx, reasons = [], 0.0, set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx = max(mx, float(parts[1]))
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[2:6]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=mx or None,
-                    reasons=sorted(reasons), samples=len(sm))
+        reasons = sorted(name for bit, name in self.REASONS.items() if self.bits & bit)
+        out = dict(sm_mhz=statistics.median(self.samples) if self.samples else None, sm_max_mhz=self.max_mhz,
+                   reasons=reasons, samples=len(self.samples))
+        if self.error:
+            out["error"] = self.error
+        return out
 
 
 # --------------------------------------------------------------------------------------
@@ -168,7 +167,7 @@ def run_gpu_arm(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
 
-    w = WORKLOAD
+    w = dict(WORKLOAD, batch=args.batch)
     precision = args.precision
     sets = []
     for s in range(2):        # two input sets, alternated between steps
@@ -294,7 +293,7 @@ def run_gpu_arm(args) -> None:
         line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps,
                     warmup=max(args.warmup, 3), ms_per_step=total_ms / args.steps, higher_is_better=True,
                     scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
-                    config=dict(workload="qwen2.5-0.5b attention layer shape, causal fwd+bwd (B=4 per GPU, "
+                    config=dict(workload=f"qwen2.5-0.5b attention layer shape, causal fwd+bwd (B={w['batch']} per GPU, "
                                          "Hq=14, Hkv=2, N=4096, d=64, G=8, bf16 io, fp32 state)",
                                 precision=precision, parallelism=f"batch x kv-head units, {world} rank(s), no collective",
                                 l2="256 MiB buffer written between timed steps", flop_per_token=fpt),
@@ -312,11 +311,13 @@ def run_gpu_arm(args) -> None:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--precision", default="bf16_tensorcore", choices=["bf16_tensorcore", "fp32_ieee"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=WORKLOAD["batch"],
+                    help="batch rows per GPU (default: the headline workload's 4; smaller only for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
