@@ -55,7 +55,9 @@ enum {
 enum {
   OAL_STATUS_NONFINITE = 1,      /* numerator or denominator not finite                    */
   OAL_STATUS_DENOMINATOR = 2,    /* denominator <= 0                                        */
-  OAL_STATUS_WAIT_TIMEOUT = 4    /* a bounded mbarrier wait inside a kernel gave up         */
+  OAL_STATUS_WAIT_TIMEOUT = 4,   /* a bounded mbarrier wait inside a kernel gave up; bits 8..15
+                                    then hold the id of the wait site                       */
+  OAL_STATUS_BAD_LAYOUT = 8      /* a head needs more padded slabs than problem.padded_slabs */
 };
 
 /* gradient request mask, same order as the reference's requested_gradient_mask
@@ -82,6 +84,8 @@ typedef struct OalProblem {
   int32_t grad_mask;    /* OAL_GRAD_* bits requested from oal_backward                  */
   float scale;          /* q is multiplied by this before anything else                 */
   float floor;          /* normalisation floor: out = num / max(den, floor)             */
+  int32_t padded_slabs; /* upper bound over heads of sum_g ceil(|group g| / 16), 4..11, or 0 when
+                           unknown (then 11 is assumed); sizes shared-memory operand images  */
 } OalProblem;
 
 /* Bytes of workspace oal_forward (phase 0) / oal_backward (phase 1) need, and

@@ -22,7 +22,7 @@ PRECISION_CODES = {"fp32_ieee": 0, "bf16_tensorcore": 1}
 
 GRAD_Q, GRAD_K, GRAD_V, GRAD_COEF, GRAD_REUSE_STATE_STAGE = 1, 2, 4, 8, 16
 STATE_ROWS = 2176
-STATUS_NONFINITE, STATUS_DENOMINATOR, STATUS_WAIT_TIMEOUT = 1, 2, 4
+STATUS_NONFINITE, STATUS_DENOMINATOR, STATUS_WAIT_TIMEOUT, STATUS_BAD_LAYOUT = 1, 2, 4, 8
 
 # every symbol include/oal_b200.h declares
 EXPORTED_SYMBOLS = (
@@ -57,6 +57,7 @@ class OalProblem(ctypes.Structure):
         ("grad_mask", ctypes.c_int32),
         ("scale", ctypes.c_float),
         ("floor", ctypes.c_float),
+        ("padded_slabs", ctypes.c_int32),
     ]
 
 

@@ -155,7 +155,7 @@ BackwardSpaceTC carve_backward_tc(const OalProblem* p, void* ws) {
   const size_t slab_image = oal::state_image_bytes_per_chunk() / 17;
   s.g = c.take<float>(qrows * oal::EP);
   s.coef_pairs = c.take<float>((size_t)p->batch * p->q_heads * oal::pairs_tiles(p->seq_len) * oal::NCOEF);
-  s.gimg = c.take<char>((size_t)p->batch * p->q_heads * nb * slab_image);
+  s.gimg = c.take<char>(2 * (size_t)p->batch * p->q_heads * nb * slab_image);   // hi image, then lo image
   s.coef_table = c.take<float>((size_t)p->q_heads * oal::state_rows());
   s.dcarry = c.take<float>(units * nb * oal::state_rows() * oal::EP);
   s.dt_img = c.take<char>(units * nb * oal::state_image_bytes_per_chunk());
@@ -310,6 +310,13 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
     e = oal::cross_read(true, q, saved_state, s.coef_table, num, den, p->batch, p->q_heads,
                         p->q_heads / p->kv_heads, p->seq_len, nb, p->scale, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
+  if (p->groups <= 8) {
+    { LaunchScope scope("intra_forward", st);
+      e = oal::intra_forward(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
+                             p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor, st); }
+    if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
+    return OAL_OK;
+  }
   oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
   a.window = kChunk;
   a.out = out; a.num = num; a.den = den; a.accumulate = 1;
@@ -374,6 +381,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
   const int nb = chunk_count(p), units = p->batch * p->kv_heads, rep = p->q_heads / p->kv_heads;
   const bool want_q = mask & OAL_GRAD_Q, want_k = mask & OAL_GRAD_K, want_v = mask & OAL_GRAD_V;
   const bool want_c = mask & OAL_GRAD_COEF;
+  const bool tc_intra = p->groups <= 8;      // intra-chunk term on the tensor cores (else token-pair kernels)
   cudaError_t e;
   if (!(mask & OAL_GRAD_REUSE_STATE_STAGE)) {
     rc = backward_state_stage(p, q, dim_perm, group_start, coef_a, coef_b, coef_c, num, den, saved_state, grad_out,
@@ -395,18 +403,26 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
                               rep, p->seq_len, nb, p->scale, p->scale, status, st); }
       if (e != cudaSuccess) return fail_cuda(e, "query feature gradient kernel");
     }
-    a.dq = want_q ? dq : nullptr;
-    a.dq_init = want_q ? s.dq_cross : nullptr;
-    a.coef_partial = want_c ? s.coef_pairs : nullptr;
-    { LaunchScope scope("pairs_backward_q", st); e = oal::pairs_backward_q(a, st); }
-    if (e != cudaSuccess) return fail_cuda(e, "backward query-side pair kernel");
+    if (tc_intra) {
+      { LaunchScope scope("intra_backward_q", st);
+        e = oal::intra_backward_q(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_q ? dq : nullptr,
+                                  want_q ? s.dq_cross : nullptr, want_c ? s.coef_pairs : nullptr, status, p->batch,
+                                  p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->scale, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward query-side kernel");
+    } else {
+      a.dq = want_q ? dq : nullptr;
+      a.dq_init = want_q ? s.dq_cross : nullptr;
+      a.coef_partial = want_c ? s.coef_pairs : nullptr;
+      { LaunchScope scope("pairs_backward_q", st); e = oal::pairs_backward_q(a, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "backward query-side pair kernel");
+    }
     if (want_c) {
       { LaunchScope scope("dcoef_reduce", st, 2);
         e = oal::dcoef_reduce(s.dcoef_partial, p->batch * nb, p->q_heads, dim_perm, group_start, s.dcoef, s.slots, st); }
       if (e != cudaSuccess) return fail_cuda(e, "coefficient gradient reduction kernels");
       { LaunchScope scope("reduce_coefs", st);
-        e = oal::reduce_coefs(s.coef_pairs, oal::pairs_tiles(p->seq_len), s.slots, p->batch, p->q_heads, p->groups,
-                              d_coef_a, d_coef_b, d_coef_c, st); }
+        e = oal::reduce_coefs(s.coef_pairs, tc_intra ? nb : oal::pairs_tiles(p->seq_len), s.slots, p->batch,
+                              p->q_heads, p->groups, d_coef_a, d_coef_b, d_coef_c, st); }
       if (e != cudaSuccess) return fail_cuda(e, "coefficient reduction kernel");
     }
   }
@@ -423,13 +439,21 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
                             nb, 1.f, status, st); }
       if (e != cudaSuccess) return fail_cuda(e, "key cross read kernel");
     }
-    a.dq = nullptr; a.dq_init = nullptr; a.coef_partial = nullptr;
-    a.dk = want_k ? dk : nullptr;
-    a.dv = want_v ? dv : nullptr;
-    a.dk_init = want_k ? s.dk_cross : nullptr;
-    a.dv_init = want_v ? s.dv_cross : nullptr;
-    { LaunchScope scope("pairs_backward_kv", st); e = oal::pairs_backward_kv(a, st); }
-    if (e != cudaSuccess) return fail_cuda(e, "backward key/value-side pair kernel");
+    if (tc_intra) {
+      { LaunchScope scope("intra_backward_kv", st);
+        e = oal::intra_backward_kv(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_k ? dk : nullptr,
+                                   want_v ? dv : nullptr, want_k ? s.dk_cross : nullptr, want_v ? s.dv_cross : nullptr,
+                                   status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->scale, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward key/value-side kernel");
+    } else {
+      a.dq = nullptr; a.dq_init = nullptr; a.coef_partial = nullptr;
+      a.dk = want_k ? dk : nullptr;
+      a.dv = want_v ? dv : nullptr;
+      a.dk_init = want_k ? s.dk_cross : nullptr;
+      a.dv_init = want_v ? s.dv_cross : nullptr;
+      { LaunchScope scope("pairs_backward_kv", st); e = oal::pairs_backward_kv(a, st); }
+      if (e != cudaSuccess) return fail_cuda(e, "backward key/value-side pair kernel");
+    }
   }
   return OAL_OK;
 
@@ -555,6 +579,13 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
     e = oal::cross_read(true, q, saved_state, coef_table, num, den, p->batch, p->q_heads, p->q_heads / p->kv_heads,
                         p->seq_len, nb, p->scale, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
+  if (p->groups <= 8) {
+    { LaunchScope scope("intra_forward", st);
+      e = oal::intra_forward(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
+                             p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor, st); }
+    if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
+    return OAL_OK;
+  }
   oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
   a.window = kChunk;
   a.out = out; a.num = num; a.den = den; a.accumulate = 1;

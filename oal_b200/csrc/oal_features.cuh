@@ -72,22 +72,43 @@ __device__ __forceinline__ uint4 feature_chunk(const float (&x)[HD], const float
                     umma::pack_bf16(f[6], f[7]));
 }
 
-template <int S, int HALF, bool QUERY, int... J>
-__device__ __forceinline__ void half_slab_impl(const float (&x)[HD], const float* coef, uint4* tile, int token,
+// Threads per CTA of the kernels that generate feature slabs: 128 tokens x GEN_PARTS threads per
+// token, each thread writing 16 / GEN_PARTS chunks of a slab.
+constexpr int GEN_THREADS = 256;
+constexpr int GEN_PARTS = GEN_THREADS / CT;
+constexpr int GEN_CHUNKS = 16 / GEN_PARTS;
+
+template <int S, int PART, bool QUERY, int... J>
+__device__ __forceinline__ void part_slab_impl(const float (&x)[HD], const float* coef, uint4* tile, int token,
                                                std::integer_sequence<int, J...>) {
-  ((tile[(HALF * 8 + J) * CT + token] = feature_chunk<S * 16 + HALF * 8 + J, QUERY>(x, coef)), ...);
+  ((tile[(PART * GEN_CHUNKS + J) * CT + token] = feature_chunk<S * 16 + PART * GEN_CHUNKS + J, QUERY>(x, coef)), ...);
 }
 
-// Write chunks [8*half, 8*half+8) of slab s of this thread's token into the slab tile
-// ([16 chunks][128 tokens] x 16 bytes).  s and half are runtime values; the bodies are static.
+template <int S, bool QUERY>
+__device__ __forceinline__ void part_slab_select(int part, const float (&x)[HD], const float* coef, uint4* tile,
+                                                 int token) {
+  using Seq = std::make_integer_sequence<int, GEN_CHUNKS>;
+  if constexpr (GEN_PARTS == 2) {
+    if (part == 0) part_slab_impl<S, 0, QUERY>(x, coef, tile, token, Seq{});
+    else part_slab_impl<S, 1, QUERY>(x, coef, tile, token, Seq{});
+  } else {
+    switch (part) {
+      case 0: part_slab_impl<S, 0, QUERY>(x, coef, tile, token, Seq{}); break;
+      case 1: part_slab_impl<S, 1, QUERY>(x, coef, tile, token, Seq{}); break;
+      case 2: part_slab_impl<S, 2 % GEN_PARTS, QUERY>(x, coef, tile, token, Seq{}); break;
+      default: part_slab_impl<S, 3 % GEN_PARTS, QUERY>(x, coef, tile, token, Seq{}); break;
+    }
+  }
+}
+
+// Write this thread's chunks of slab s of its token into the slab tile ([16 chunks][128 tokens] x
+// 16 bytes).  s and part are runtime values; the bodies are static.
 template <bool QUERY>
-__device__ __forceinline__ void write_half_slab(int s, int half, const float (&x)[HD], const float* coef,
+__device__ __forceinline__ void write_half_slab(int s, int part, const float (&x)[HD], const float* coef,
                                                 uint4* tile, int token) {
-  using Seq = std::make_integer_sequence<int, 8>;
-#define OAL_SLAB_CASE(S)                                                        \
-  case S:                                                                       \
-    if (half == 0) half_slab_impl<S, 0, QUERY>(x, coef, tile, token, Seq{});    \
-    else half_slab_impl<S, 1, QUERY>(x, coef, tile, token, Seq{});              \
+#define OAL_SLAB_CASE(S)                                      \
+  case S:                                                     \
+    part_slab_select<S, QUERY>(part, x, coef, tile, token);   \
     break;
   switch (s) {
     OAL_SLAB_CASE(0) OAL_SLAB_CASE(1) OAL_SLAB_CASE(2) OAL_SLAB_CASE(3) OAL_SLAB_CASE(4) OAL_SLAB_CASE(5)
@@ -122,10 +143,15 @@ __device__ __forceinline__ void load_row_bf16(float (&x)[HD], const __nv_bfloat1
 // Bounded mbarrier waits for one CTA: the first wait that expires raises a shared flag and every
 // later wait returns at once, so a kernel always terminates; the flag ends up in the status word.
 struct Waiter {
-  int* dead;          // shared flag: a wait expired somewhere in this CTA
-  __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity) {
+  int* dead;          // shared flag: a wait expired somewhere in this CTA (holds the site id, >= 1)
+  __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int site = 1) {
     if (*reinterpret_cast<volatile int*>(dead)) return;
-    if (!umma::mbar_wait(bar, parity)) *reinterpret_cast<volatile int*>(dead) = 1;
+    if (!umma::mbar_wait(bar, parity)) *reinterpret_cast<volatile int*>(dead) = site;
+  }
+  // status bits to OR into the caller's word: the timeout flag plus the site id in bits 8..15
+  __device__ __forceinline__ int status_bits() const {
+    const int d = *reinterpret_cast<volatile int*>(dead);
+    return d ? (OAL_STATUS_WAIT_TIMEOUT | ((d & 0xFF) << 8)) : 0;
   }
 };
 

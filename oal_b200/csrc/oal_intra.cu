@@ -1,0 +1,224 @@
+// Intra-chunk term of the chunked scan on the tensor cores (tcgen05 / TMEM), forward.
+//
+// For one (batch, query head, 128-token chunk) the kernel forms, 16 keys at a time,
+//   S_g = Q_g K_g^T              one small MMA chain per dimension group (groups padded to 16 dims)
+//   W   = A + sum_g s_g (B_g + sum_g' C_gg' s_g')   in registers, causal mask, bf16
+//   Y  += W [v | 1]              second MMA, accumulator shared by all key tiles
+// then adds the cross-chunk part left in num/den by cross_read, normalises and writes out / num /
+// den and the status flags.  It replaces, per chunk, the reference's F-wide local score GEMM,
+// tril, bf16 cast, score x U GEMM, merge and normalise stages
+// (oal_attention/hd_block_gemm_runtime.py:530-597, hd_block_gemm_normalization_ops.py:113).
+#include "oal_intra.cuh"
+#include "oal_kernels.h"
+
+namespace oal {
+namespace {
+
+using namespace umma;
+
+struct IntraFwdArgs {
+  const __nv_bfloat16 *q, *k, *v;
+  const int32_t *dim_perm, *group_start;
+  const float *A, *Bc, *Cc;
+  void* out;
+  float *num, *den;
+  int32_t* status;
+  int N, Hq, Hkv, G, out_dt;
+  int slabs;            // upper bound on the padded 16-dim slabs of any head (image size)
+  float scale, floor;
+};
+
+constexpr int W_BYTES = (KT / 8) * CT * 16;              // 4096: one bf16 weight tile [2][128 rows][8 keys]
+__host__ __device__ constexpr int fwd_smem_bytes(int slabs) {
+  return 2 * slabs * 4096 + SLAB_S_BYTES + 2 * W_BYTES + STAGE_BYTES;
+}
+
+__global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int img_bytes = a.slabs * 4096;                  // padded q / k operand image [slabs*2][128][8]
+  unsigned char* Qimg = smem;
+  unsigned char* Kimg = Qimg + img_bytes;
+  unsigned char* Uimg = Kimg + img_bytes;
+  unsigned char* Wbuf = Uimg + SLAB_S_BYTES;
+  uint32_t* stage = reinterpret_cast<uint32_t*>(Wbuf + 2 * W_BYTES);
+  __shared__ PaddedGroups pg;
+  __shared__ uint64_t s_done, w_done[2];
+  __shared__ uint32_t tmem_base;
+  __shared__ int dead;
+  __shared__ float den_s[CT];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (a.Hq / a.Hkv);
+  const int half = warp >> 2, row = 32 * (warp & 3) + lane;
+  if (warp == 0) tmem_alloc(&tmem_base, 256);
+  if (tid == 0) {
+    mbar_init(&s_done, 1);
+    mbar_init(&w_done[0], 1);
+    mbar_init(&w_done[1], 1);
+    mbar_fence_init();
+    dead = 0;
+  }
+  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, a.scale, a.scale * a.scale, tid, 256);
+  const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
+  // a head with more padded slabs than the caller announced would not fit the images: refuse it
+  const bool bad = pg.k16_start[IG] > a.slabs;
+  if (!bad) {
+    build_padded_image(Qimg, stage, a.q + qoff * HD, c * CT, a.N, pg, tid, 256);
+    build_padded_image(Kimg, stage, a.k + koff * HD, c * CT, a.N, pg, tid, 256);
+  } else if (tid == 0) {
+    atomicOr(a.status, OAL_STATUS_BAD_LAYOUT);
+  }
+  for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
+    const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
+    reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
+  }
+  fence_async_smem();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  Waiter w{&dead};
+  const uint32_t tS = tmem_base, tY = tmem_base + IG * KT;
+  const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+  const uint32_t q_addr = smem_u32(Qimg), k_addr = smem_u32(Kimg), u_addr = smem_u32(Uimg);
+  const uint32_t idesc_y = instr_desc_bf16(128, EP, 0, 1);
+  const int tiles = bad ? 0 : min(CT / KT, (a.N - c * CT + KT - 1) / KT);
+  if (tid == 0 && !bad) {
+    issue_group_scores(tS, q_addr, k_addr, 0, pg);
+    mma_commit(&s_done);
+  }
+  for (int kt = 0; kt < tiles; ++kt) {
+    const int buf = kt & 1;
+    float s[IG][8];
+    w.wait(&s_done, kt & 1, 0x11);
+    fence_after_sync();
+#pragma unroll
+    for (int g = 0; g < IG; ++g) {
+      if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld8(tS + lane_off + g * KT + 8 * half, s[g]);
+      else {
+#pragma unroll
+        for (int x = 0; x < 8; ++x) s[g][x] = 0.f;
+      }
+    }
+    tmem_ld_wait();
+    fence_before_sync();
+    __syncthreads();                       // every thread holds its scores: S may be overwritten
+    if (tid == 0 && kt + 1 < tiles) {
+      fence_after_sync();
+      issue_group_scores(tS, q_addr, k_addr, (kt + 1) * KT, pg);
+      mma_commit(&s_done);
+    }
+    // combine (rows whose whole warp lies above the tile's keys are masked out entirely)
+    float wv[8];
+    const bool warp_active = 32 * (warp & 3) + 31 >= kt * KT;
+    if (warp_active) {
+#pragma unroll
+      for (int x = 0; x < 8; ++x) wv[x] = pg.A;
+#pragma unroll
+      for (int g = 0; g < IG; ++g) {
+        float t[8];
+        const float bg = pg.B[g], cgg = pg.C[g * IG + g];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) t[x] = fmaf(cgg, s[g][x], bg);
+#pragma unroll
+        for (int g2 = 0; g2 < g; ++g2) {
+          const float c2 = 2.f * pg.C[g * IG + g2];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+        }
+#pragma unroll
+        for (int x = 0; x < 8; ++x) wv[x] = fmaf(s[g][x], t[x], wv[x]);
+      }
+#pragma unroll
+      for (int x = 0; x < 8; ++x)
+        if (kt * KT + 8 * half + x > row) wv[x] = 0.f;
+    } else {
+#pragma unroll
+      for (int x = 0; x < 8; ++x) wv[x] = 0.f;
+    }
+    if (kt >= 2) w.wait(&w_done[buf], ((kt - 2) >> 1) & 1, 0x12);     // the MMA that read W[buf] two tiles ago
+    reinterpret_cast<uint4*>(Wbuf + buf * W_BYTES)[half * CT + row] =
+        make_uint4(pack_bf16(wv[0], wv[1]), pack_bf16(wv[2], wv[3]), pack_bf16(wv[4], wv[5]), pack_bf16(wv[6], wv[7]));
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      fence_after_sync();
+      mma_bf16_ss(tY, smem_desc(smem_u32(Wbuf + buf * W_BYTES), CT * 16, 128),
+                  smem_desc(u_addr + kt * KT * 16, 128, CT * 16), idesc_y, kt > 0);
+      mma_commit(&w_done[buf]);
+    }
+  }
+  // all weight MMAs done
+  if (tiles >= 2) w.wait(&w_done[(tiles - 2) & 1], ((tiles - 2) >> 1) & 1, 0x13);
+  if (tiles >= 1) w.wait(&w_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, 0x14);
+  fence_after_sync();
+  // epilogue: add the cross-chunk part, normalise, status
+  const int i = c * CT + row;
+  const size_t orow = qoff + i;
+  const int col0 = half == 0 ? 0 : 48, ncol = half == 0 ? 48 : 32;
+  float y[48];
+#pragma unroll
+  for (int cc = 0; cc < 48; cc += 16) {
+    if (cc < ncol) {
+      float vv[16];
+      tmem_ld16(tY + lane_off + col0 + cc, vv);
+      tmem_ld_wait();
+#pragma unroll
+      for (int x = 0; x < 16; ++x) y[cc + x] = vv[x];
+    }
+  }
+  int flags = 0;
+  if (half == 1) {
+    float den = y[16];                      // column 64
+    if (i < a.N && !bad) {
+      den += a.den[orow];
+      a.den[orow] = den;
+      if (!finite_f(den)) flags |= OAL_STATUS_NONFINITE;
+      else if (!(den > 0.f)) flags |= OAL_STATUS_DENOMINATOR;
+    }
+    den_s[row] = den;
+  }
+  __syncthreads();
+  if (i < a.N && !dead && !bad) {
+    const float dn = fmaxf(den_s[row], a.floor);
+    const int nval = half == 0 ? 48 : 16;
+#pragma unroll
+    for (int x4 = 0; x4 < 48; x4 += 4) {
+      if (x4 < nval) {
+        float* np = a.num + orow * VD + col0 + x4;
+        const float4 o = *reinterpret_cast<const float4*>(np);
+        const float n0 = y[x4] + o.x, n1 = y[x4 + 1] + o.y, n2 = y[x4 + 2] + o.z, n3 = y[x4 + 3] + o.w;
+        *reinterpret_cast<float4*>(np) = make_float4(n0, n1, n2, n3);
+        if (!(finite_f(n0) && finite_f(n1) && finite_f(n2) && finite_f(n3))) flags |= OAL_STATUS_NONFINITE;
+        store_elem(a.out, orow * VD + col0 + x4, a.out_dt, n0 / dn);
+        store_elem(a.out, orow * VD + col0 + x4 + 1, a.out_dt, n1 / dn);
+        store_elem(a.out, orow * VD + col0 + x4 + 2, a.out_dt, n2 / dn);
+        store_elem(a.out, orow * VD + col0 + x4 + 3, a.out_dt, n3 / dn);
+      }
+    }
+  }
+  if (flags) atomicOr(a.status, flags);
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 256);
+  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
+}
+
+}  // namespace
+
+cudaError_t intra_forward(const void* q, const void* k, const void* v, const int32_t* dim_perm,
+                          const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* out,
+                          float* num, float* den, int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G,
+                          int out_dt, int slabs, float scale, float floor_v, cudaStream_t st) {
+  if (slabs < 1 || slabs > DP_MAX / 16) slabs = DP_MAX / 16;
+  const int smem = fwd_smem_bytes(slabs);
+  cudaError_t e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       fwd_smem_bytes(DP_MAX / 16));
+  if (e != cudaSuccess) return e;
+  IntraFwdArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+                 static_cast<const __nv_bfloat16*>(v), dim_perm, group_start, A, Bc, Cc, out, num, den, status,
+                 N, Hq, Hkv, G, out_dt, slabs, scale, floor_v};
+  intra_fwd_kernel<<<dim3(NB, Hq, B), 256, smem, st>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace oal

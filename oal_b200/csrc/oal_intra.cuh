@@ -1,0 +1,109 @@
+// Shared pieces of the tensor-core intra-chunk kernels: per-head padded group layout, operand
+// images of q / k with every group padded to a multiple of 16 dimensions, and the per-pair
+// combine  w = A + sum_g s_g (B_g + sum_g' C_gg' s_g').
+#pragma once
+
+#include "oal_features.cuh"
+
+namespace oal {
+
+constexpr int KT = 16;            // keys (or queries) per tile of the intra-chunk kernels
+constexpr int DP_MAX = 176;       // padded dims: 64 + 7 * 16 rounded to 16 (at most 8 groups)
+constexpr int IG = 8;             // groups handled by the tensor-core intra-chunk kernels
+
+// Padded, group-sorted dimension layout of one head.
+struct PaddedGroups {
+  int k16_start[IG + 1];     // first 16-dim slab of group g; k16_start[IG] = number of slabs
+  short src[DP_MAX];         // original dimension of padded position p, or -1 for zero padding
+  float A, B[IG], C[IG * IG];   // coefficients; B pre-multiplied by `bscale`, C by `cscale`
+};
+
+__device__ __forceinline__ void load_padded_groups(PaddedGroups& pg, const int32_t* dim_perm,
+                                                   const int32_t* group_start, const float* A, const float* Bc,
+                                                   const float* Cc, int G, int h, float bscale, float cscale,
+                                                   int tid, int nthreads) {
+  if (tid == 0) {
+    int acc = 0;
+    for (int g = 0; g < IG; ++g) {
+      pg.k16_start[g] = acc;
+      const int n = group_start[h * (GMAX + 1) + g + 1] - group_start[h * (GMAX + 1) + g];
+      acc += (n + 15) >> 4;
+    }
+    pg.k16_start[IG] = acc;
+    pg.A = A[h];
+  }
+  for (int x = tid; x < IG; x += nthreads) pg.B[x] = x < G ? bscale * Bc[h * G + x] : 0.f;
+  for (int x = tid; x < IG * IG; x += nthreads) {
+    const int g = x / IG, g2 = x % IG;
+    pg.C[x] = (g < G && g2 < G) ? cscale * Cc[((size_t)h * G + g) * G + g2] : 0.f;
+  }
+  __syncthreads();
+  for (int p = tid; p < DP_MAX; p += nthreads) {
+    int g = 0;
+    while (g < IG - 1 && p >= 16 * pg.k16_start[g + 1]) ++g;
+    const int t = p - 16 * pg.k16_start[g];
+    const int s0 = group_start[h * (GMAX + 1) + g], n = group_start[h * (GMAX + 1) + g + 1] - s0;
+    pg.src[p] = (p < 16 * pg.k16_start[IG] && t < n) ? (short)dim_perm[h * HD + s0 + t] : (short)-1;
+  }
+  __syncthreads();
+}
+
+constexpr int STAGE_WORDS = CT * 33;      // raw 128 x 64 bf16 tile, row pitch 33 words (conflict-free column walks)
+constexpr int STAGE_BYTES = STAGE_WORDS * 4;
+
+// Rows [row0, row0+128) of a bf16 [.., N, 64] tensor -> operand image [slabs*2][128 rows][8] with the
+// padded group layout (rows beyond N are zero).  The tile is first copied row-major into `stage`
+// with coalesced 16-byte loads, then gathered column by column from shared memory.
+// Contains two block-wide barriers; `stage` is free again when it returns.
+__device__ __forceinline__ void build_padded_image(unsigned char* img, uint32_t* stage, const __nv_bfloat16* base,
+                                                   int row0, int N, const PaddedGroups& pg, int tid, int nthreads) {
+  for (int x = tid; x < CT * 8; x += nthreads) {
+    const int r = x >> 3, seg = x & 7, i = row0 + r;
+    uint4 t = make_uint4(0u, 0u, 0u, 0u);
+    if (i < N) t = *reinterpret_cast<const uint4*>(base + (size_t)i * HD + seg * 8);
+    uint32_t* d = stage + r * 33 + seg * 4;
+    d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+  }
+  __syncthreads();
+  const int chunks = 2 * pg.k16_start[IG];
+  const unsigned short* raw = reinterpret_cast<const unsigned short*>(stage);
+  for (int x = tid; x < chunks * CT; x += nthreads) {
+    const int c8 = x >> 7, r = x & 127;
+    unsigned short e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int s = pg.src[c8 * 8 + j];
+      e[j] = s >= 0 ? raw[r * 66 + s] : (unsigned short)0;
+    }
+    reinterpret_cast<uint4*>(img)[x] = make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16),
+                                                  e[4] | ((uint32_t)e[5] << 16), e[6] | ((uint32_t)e[7] << 16));
+  }
+  __syncthreads();
+}
+
+// 32 lanes x 32-bit, 8 consecutive columns per thread.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Issue the per-group score MMAs  S_g[128 x KT] = X_g (128 rows) . Y_g (KT rows)^T  for one tile.
+//   x_addr: image whose 128 rows are the MMA M dimension; y_addr: image, rows [yrow0, yrow0+KT) are N
+__device__ __forceinline__ void issue_group_scores(uint32_t tmem_s, uint32_t x_addr, uint32_t y_addr, int yrow0,
+                                                   const PaddedGroups& pg) {
+  const uint32_t idesc = umma::instr_desc_bf16(128, KT, 0, 0);
+#pragma unroll 1
+  for (int g = 0; g < IG; ++g) {
+    const int k0 = pg.k16_start[g], k1 = pg.k16_start[g + 1];
+    for (int k16 = k0; k16 < k1; ++k16)
+      umma::mma_bf16_ss(tmem_s + g * KT, umma::smem_desc(x_addr + k16 * 4096, CT * 16, 128),
+                        umma::smem_desc(y_addr + k16 * 4096 + yrow0 * 16, CT * 16, 128), idesc, k16 > k0);
+  }
+}
+
+}  // namespace oal

@@ -1,0 +1,534 @@
+// Intra-chunk term of the chunked scan on the tensor cores (tcgen05 / TMEM), backward.
+//
+// Per 16-key (query side) or 16-query (key/value side) tile of a 128-token chunk:
+//   S_g  = Q_g K_g^T,  dW = G [v|1]^T                          MMAs into tensor memory
+//   ds_g = dW (B_g + 2 sum_g' C_gg' s_g'),  w = A + ...        registers, causal mask, bf16 tiles
+//   dq~ += ds_g K_g          (query side)                      MMAs, accumulators in tensor memory
+//   dk~ += ds_g^T Q_g, dU += W^T G   (key/value side, summed over the query heads of the KV head)
+// plus the coefficient partial sums dA, dB_g, dC_gg' (query side, per-thread accumulators and a
+// fixed-order block reduction).  The cross-chunk parts computed by the state kernels arrive as
+// fp32 buffers and are added before the final cast.  Reference stages replaced:
+// oal_attention/hd_block_gemm_backward_wave.py:253-476 (dS, local dphi_q / dphi_k / dU GEMMs) and the
+// folds / coefficient partials of oal_attention/hd_block_gemm_feature_backward.py:59-474.
+#include "oal_intra.cuh"
+#include "oal_kernels.h"
+
+namespace oal {
+namespace {
+
+using namespace umma;
+
+constexpr int IMG_BYTES = (DP_MAX / 8) * CT * 16;        // 45056
+constexpr int TILE_BYTES = (KT / 8) * CT * 16;           // 4096: bf16 [2][128 rows][8]
+constexpr int NTRI = IG * (IG + 1) / 2;
+
+__device__ __forceinline__ int tri8(int g, int g2) { return g * GMAX - (g * (g - 1)) / 2 + (g2 - g); }
+
+struct IntraBwdArgs {
+  const __nv_bfloat16 *q, *k, *v;
+  const __nv_bfloat16* gimg;        // [2][B*Hq, NB, 10, 128, 8]: bf16(g) image, then the image of g - bf16(g)
+  size_t gimg_lo_offset;            // bytes from the hi image to the lo image
+  const int32_t *dim_perm, *group_start;
+  const float *A, *Bc, *Cc;
+  void *dq, *dk, *dv;               // io dtype outputs (bf16), may be null
+  const float* dq_init;             // fp32 cross part (already scaled), or null
+  float* dk_acc;                    // fp32 [B,Hkv,N,64]: holds the cross part, used as accumulator
+  const float* dv_init;             // fp32 cross part, or null
+  float* coef_partial;              // [B][Hq][NB][NCOEF] or null
+  int32_t* status;
+  int N, NB, Hq, Hkv, G;
+  float scale;
+};
+
+// scores -> (ds_g tiles, w) for 8 columns of one row.  ss = scale * s.
+struct PairOut {
+  float w[8];
+};
+
+// ---------------------------------------------------------------------------
+// query side
+// ---------------------------------------------------------------------------
+constexpr int BQ_SMEM = 2 * IMG_BYTES + 3 * SLAB_S_BYTES + 2 * IG * TILE_BYTES;
+
+__global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* Qimg = smem;
+  unsigned char* Kimg = Qimg + IMG_BYTES;
+  unsigned char* Uimg = Kimg + IMG_BYTES;
+  unsigned char* Gimg = Uimg + SLAB_S_BYTES;               // hi image, lo image
+  unsigned char* DS = Gimg + 2 * SLAB_S_BYTES;            // [2][IG][TILE_BYTES]
+  __shared__ PaddedGroups pg;
+  __shared__ uint64_t s_done, ds_done[2], gfull;
+  __shared__ uint32_t tmem_base;
+  __shared__ int dead;
+  __shared__ float red[8 * NCOEF];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (a.Hq / a.Hkv);
+  const int half = warp >> 2, row = 32 * (warp & 3) + lane;
+  if (warp == 0) tmem_alloc(&tmem_base, 512);
+  if (tid == 0) {
+    mbar_init(&s_done, 1);
+    mbar_init(&ds_done[0], 1);
+    mbar_init(&ds_done[1], 1);
+    mbar_init(&gfull, 1);
+    mbar_fence_init();
+    dead = 0;
+  }
+  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, 256);
+  const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
+  if (tid == 0) {
+    const unsigned char* gsrc =
+        reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.Hq + h) * a.NB + c) * SLAB_S_BYTES;
+    mbar_arrive_expect_tx(&gfull, 2 * SLAB_S_BYTES);
+    bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, &gfull);
+    bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
+  }
+  // the ds tile buffers are idle during set-up: use them as the staging area of the image builds
+  build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, 256);
+  build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, 256);
+  for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
+    const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
+    reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
+  }
+  fence_async_smem();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  Waiter w{&dead};
+  const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tQ = tmem_base + IG * KT + KT;
+  const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+  const uint32_t q_addr = smem_u32(Qimg), k_addr = smem_u32(Kimg), u_addr = smem_u32(Uimg), g_addr = smem_u32(Gimg);
+  const uint32_t idesc16 = instr_desc_bf16(128, KT, 0, 0);
+  const uint32_t idesc_dq = instr_desc_bf16(128, 16, 0, 1);
+  const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
+
+  auto issue_scores = [&](int kt) {
+    issue_group_scores(tS, q_addr, k_addr, kt * KT, pg);
+#pragma unroll
+    for (int ks = 0; ks < 2 * (EP / 16); ++ks) {       // G = hi + lo: the K extent is walked twice
+      const int part = ks / (EP / 16), kk = ks % (EP / 16);
+      mma_bf16_ss(tW, smem_desc(g_addr + part * SLAB_S_BYTES + kk * 4096, CT * 16, 128),
+                  smem_desc(u_addr + kk * 4096 + kt * KT * 16, CT * 16, 128), idesc16, ks > 0);
+    }
+    mma_commit(&s_done);
+  };
+  if (tid == 0) {
+    w.wait(&gfull, 0, 0x20);
+    fence_after_sync();
+    issue_scores(0);
+  }
+  float cA = 0.f, cB[IG], cC[NTRI];
+#pragma unroll
+  for (int g = 0; g < IG; ++g) cB[g] = 0.f;
+#pragma unroll
+  for (int x = 0; x < NTRI; ++x) cC[x] = 0.f;
+
+  for (int kt = 0; kt < tiles; ++kt) {
+    const int buf = kt & 1;
+    float s[IG][8], dw[8];
+    w.wait(&s_done, kt & 1, 0x21);
+    fence_after_sync();
+#pragma unroll
+    for (int g = 0; g < IG; ++g) {
+      if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld8(tS + lane_off + g * KT + 8 * half, s[g]);
+      else {
+#pragma unroll
+        for (int x = 0; x < 8; ++x) s[g][x] = 0.f;
+      }
+    }
+    tmem_ld8(tW + lane_off + 8 * half, dw);
+    tmem_ld_wait();
+    fence_before_sync();
+    __syncthreads();
+    if (tid == 0 && kt + 1 < tiles) {
+      fence_after_sync();
+      issue_scores(kt + 1);
+    }
+    const bool warp_active = 32 * (warp & 3) + 31 >= kt * KT;
+    if (kt >= 2) w.wait(&ds_done[buf], ((kt - 2) >> 1) & 1, 0x22);
+    unsigned char* dsb = DS + buf * IG * TILE_BYTES;
+    if (warp_active) {
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        if (kt * KT + 8 * half + x > row) dw[x] = 0.f;
+        cA += dw[x];
+      }
+#pragma unroll
+      for (int g = 0; g < IG; ++g)
+#pragma unroll
+        for (int x = 0; x < 8; ++x) s[g][x] *= a.scale;
+#pragma unroll
+      for (int g = 0; g < IG; ++g) {
+        float t[8];
+        const float bg = pg.B[g];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) t[x] = bg;
+#pragma unroll
+        for (int g2 = 0; g2 < IG; ++g2) {
+          const float c2 = 2.f * pg.C[g * IG + g2];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+        }
+#pragma unroll
+        for (int x = 0; x < 8; ++x) t[x] *= dw[x];
+        reinterpret_cast<uint4*>(dsb + g * TILE_BYTES)[half * CT + row] =
+            make_uint4(pack_bf16(t[0], t[1]), pack_bf16(t[2], t[3]), pack_bf16(t[4], t[5]), pack_bf16(t[6], t[7]));
+      }
+      int idx = 0;
+#pragma unroll
+      for (int g = 0; g < IG; ++g) {
+        float ws[8];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          ws[x] = dw[x] * s[g][x];
+          cB[g] += ws[x];
+        }
+#pragma unroll
+        for (int g2 = g; g2 < IG; ++g2) {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) cC[idx] = fmaf(ws[x], s[g2][x], cC[idx]);
+          ++idx;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < IG; ++g)
+        reinterpret_cast<uint4*>(dsb + g * TILE_BYTES)[half * CT + row] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      fence_after_sync();
+      const uint32_t ds_addr = smem_u32(dsb);
+#pragma unroll 1
+      for (int g = 0; g < IG; ++g)
+        for (int k16 = pg.k16_start[g]; k16 < pg.k16_start[g + 1]; ++k16)
+          mma_bf16_ss(tQ + k16 * 16, smem_desc(ds_addr + g * TILE_BYTES, CT * 16, 128),
+                      smem_desc(k_addr + k16 * 4096 + kt * KT * 16, 128, CT * 16), idesc_dq, kt > 0);
+      mma_commit(&ds_done[buf]);
+    }
+  }
+  if (tiles >= 2) w.wait(&ds_done[(tiles - 2) & 1], ((tiles - 2) >> 1) & 1, 0x23);
+  w.wait(&ds_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, 0x24);
+  fence_after_sync();
+  // dq~ (padded, group-sorted columns) -> dq
+  if (a.dq) {
+    const int i = c * CT + row;
+    const int nslab = pg.k16_start[IG];
+    for (int k16 = half; k16 < nslab; k16 += 2) {
+      float vv[16];
+      tmem_ld16(tQ + lane_off + k16 * 16, vv);
+      tmem_ld_wait();
+      if (i < a.N && !dead) {
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const int src = pg.src[k16 * 16 + x];
+          if (src >= 0) {
+            const size_t o = (qoff + i) * HD + src;
+            float val = a.scale * vv[x];
+            if (a.dq_init) val += a.dq_init[o];
+            reinterpret_cast<__nv_bfloat16*>(a.dq)[o] = __float2bfloat16_rn(val);
+          }
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (a.coef_partial) {
+    auto wsum = [](float v) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      return v;
+    };
+    for (int x = lane; x < NCOEF; x += 32) red[warp * NCOEF + x] = 0.f;
+    __syncwarp();
+    float v = wsum(cA);
+    if (lane == 0) red[warp * NCOEF + 0] = v;
+#pragma unroll
+    for (int g = 0; g < IG; ++g) {
+      v = wsum(cB[g]);
+      if (lane == 0) red[warp * NCOEF + 1 + g] = v;
+    }
+    int idx = 0;
+#pragma unroll
+    for (int g = 0; g < IG; ++g)
+#pragma unroll
+      for (int g2 = g; g2 < IG; ++g2) {
+        v = wsum(cC[idx]);
+        if (lane == 0) red[warp * NCOEF + 1 + GMAX + tri8(g, g2)] = v;
+        ++idx;
+      }
+    __syncthreads();
+    float* dst = a.coef_partial + ((size_t)(b * a.Hq + h) * a.NB + c) * NCOEF;
+    for (int x = tid; x < NCOEF; x += 256) {
+      float t = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < 8; ++ww) t += red[ww * NCOEF + x];
+      dst[x] = t;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
+  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
+}
+
+// ---------------------------------------------------------------------------
+// key / value side
+// ---------------------------------------------------------------------------
+constexpr int BKV_SMEM = 2 * IMG_BYTES + 3 * SLAB_S_BYTES + 2 * IG * TILE_BYTES + 2 * TILE_BYTES;
+
+__global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* Kimg = smem;
+  unsigned char* Qimg = Kimg + IMG_BYTES;
+  unsigned char* Uimg = Qimg + IMG_BYTES;
+  unsigned char* Gimg = Uimg + SLAB_S_BYTES;               // hi image, lo image
+  unsigned char* DS = Gimg + 2 * SLAB_S_BYTES;             // [2][IG][TILE_BYTES]
+  unsigned char* WT = DS + 2 * IG * TILE_BYTES;            // [2][TILE_BYTES]
+  __shared__ PaddedGroups pg;
+  __shared__ uint64_t s_done, ds_done[2], gfull;
+  __shared__ uint32_t tmem_base;
+  __shared__ int dead;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int rep = a.Hq / a.Hkv;
+  const int half = warp >> 2, row = 32 * (warp & 3) + lane;     // row = key index inside the chunk
+  if (warp == 0) tmem_alloc(&tmem_base, 512);
+  if (tid == 0) {
+    mbar_init(&s_done, 1);
+    mbar_init(&ds_done[0], 1);
+    mbar_init(&ds_done[1], 1);
+    mbar_init(&gfull, 1);
+    mbar_fence_init();
+    dead = 0;
+  }
+  const size_t koff = (size_t)(b * a.Hkv + kvh) * a.N;
+  for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
+    const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
+    reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
+  }
+  fence_async_smem();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  Waiter w{&dead};
+  const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tK = tmem_base + IG * KT + KT, tU = tK + DP_MAX;
+  const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+  const uint32_t q_addr = smem_u32(Qimg), k_addr = smem_u32(Kimg), u_addr = smem_u32(Uimg), g_addr = smem_u32(Gimg);
+  const uint32_t idesc16 = instr_desc_bf16(128, KT, 0, 0);
+  const uint32_t idesc_dk = instr_desc_bf16(128, 16, 0, 1);
+  const uint32_t idesc_du = instr_desc_bf16(128, EP, 0, 1);
+  const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
+  const int jglob = c * CT + row;
+  int nt = 0;                                   // tiles issued so far over all heads
+
+  for (int hh = 0; hh < rep; ++hh) {
+    const int h = kvh * rep + hh;
+    const size_t qoff = (size_t)(b * a.Hq + h) * a.N;
+    // every MMA of the previous head has completed (waited at its end): the images may be rebuilt
+    if (tid == 0) {
+      const unsigned char* gsrc =
+          reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.Hq + h) * a.NB + c) * SLAB_S_BYTES;
+      mbar_arrive_expect_tx(&gfull, 2 * SLAB_S_BYTES);
+      bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, &gfull);
+      bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
+    }
+    load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, 256);
+    // every MMA that read the ds tiles has completed: they double as staging area of the image builds
+    build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, 256);
+    build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, 256);
+    fence_async_smem();
+    __syncthreads();
+
+    auto issue_scores = [&](int qt) {
+      issue_group_scores(tS, k_addr, q_addr, qt * KT, pg);         // S^T: key rows x 16 queries
+#pragma unroll
+      for (int ks = 0; ks < 2 * (EP / 16); ++ks) {     // G = hi + lo
+        const int part = ks / (EP / 16), kk = ks % (EP / 16);
+        mma_bf16_ss(tW, smem_desc(u_addr + kk * 4096, CT * 16, 128),
+                    smem_desc(g_addr + part * SLAB_S_BYTES + kk * 4096 + qt * KT * 16, CT * 16, 128), idesc16, ks > 0);
+      }
+      mma_commit(&s_done);
+    };
+    if (tid == 0) {
+      w.wait(&gfull, hh & 1, 0x30);
+      fence_after_sync();
+      issue_scores(0);
+    }
+    for (int qt = 0; qt < tiles; ++qt, ++nt) {
+      const int buf = nt & 1;
+      float s[IG][8], dw[8];
+      w.wait(&s_done, nt & 1, 0x31);
+      fence_after_sync();
+#pragma unroll
+      for (int g = 0; g < IG; ++g) {
+        if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld8(tS + lane_off + g * KT + 8 * half, s[g]);
+        else {
+#pragma unroll
+          for (int x = 0; x < 8; ++x) s[g][x] = 0.f;
+        }
+      }
+      tmem_ld8(tW + lane_off + 8 * half, dw);
+      tmem_ld_wait();
+      fence_before_sync();
+      __syncthreads();
+      if (tid == 0 && qt + 1 < tiles) {
+        fence_after_sync();
+        issue_scores(qt + 1);
+      }
+      // keys of this warp are all later than the tile's queries -> nothing survives the mask
+      const bool warp_active = 32 * (warp & 3) <= qt * KT + KT - 1;
+      if (nt >= 2) w.wait(&ds_done[buf], ((nt - 2) >> 1) & 1, 0x32);
+      unsigned char* dsb = DS + buf * IG * TILE_BYTES;
+      float wv[8];
+      if (warp_active) {
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          wv[x] = pg.A;
+          if (qt * KT + 8 * half + x < row) dw[x] = 0.f;          // query earlier than the key
+        }
+#pragma unroll
+        for (int g = 0; g < IG; ++g)
+#pragma unroll
+          for (int x = 0; x < 8; ++x) s[g][x] *= a.scale;
+#pragma unroll
+        for (int g = 0; g < IG; ++g) {
+          float t[8];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) t[x] = 0.f;
+#pragma unroll
+          for (int g2 = 0; g2 < IG; ++g2) {
+            const float c2 = pg.C[g * IG + g2];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+          }
+          const float bg = pg.B[g];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            wv[x] = fmaf(s[g][x], bg + t[x], wv[x]);
+            t[x] = dw[x] * (bg + 2.f * t[x]);
+          }
+          reinterpret_cast<uint4*>(dsb + g * TILE_BYTES)[half * CT + row] =
+              make_uint4(pack_bf16(t[0], t[1]), pack_bf16(t[2], t[3]), pack_bf16(t[4], t[5]), pack_bf16(t[6], t[7]));
+        }
+#pragma unroll
+        for (int x = 0; x < 8; ++x)
+          if (qt * KT + 8 * half + x < row) wv[x] = 0.f;
+      } else {
+#pragma unroll
+        for (int x = 0; x < 8; ++x) wv[x] = 0.f;
+#pragma unroll
+        for (int g = 0; g < IG; ++g)
+          reinterpret_cast<uint4*>(dsb + g * TILE_BYTES)[half * CT + row] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      reinterpret_cast<uint4*>(WT + buf * TILE_BYTES)[half * CT + row] =
+          make_uint4(pack_bf16(wv[0], wv[1]), pack_bf16(wv[2], wv[3]), pack_bf16(wv[4], wv[5]), pack_bf16(wv[6], wv[7]));
+      fence_async_smem();
+      __syncthreads();
+      if (tid == 0) {
+        fence_after_sync();
+        const uint32_t ds_addr = smem_u32(dsb);
+#pragma unroll 1
+        for (int g = 0; g < IG; ++g)
+          for (int k16 = pg.k16_start[g]; k16 < pg.k16_start[g + 1]; ++k16)
+            mma_bf16_ss(tK + k16 * 16, smem_desc(ds_addr + g * TILE_BYTES, CT * 16, 128),
+                        smem_desc(q_addr + k16 * 4096 + qt * KT * 16, 128, CT * 16), idesc_dk, qt > 0);
+        mma_bf16_ss(tU, smem_desc(smem_u32(WT + buf * TILE_BYTES), CT * 16, 128),
+                    smem_desc(g_addr + qt * KT * 16, 128, CT * 16), idesc_du, nt > 0);
+        mma_commit(&ds_done[buf]);
+      }
+    }
+    // end of head: wait for its last MMAs, fold dk~ into the fp32 accumulator (original dim order)
+    if (nt >= 2) w.wait(&ds_done[(nt - 2) & 1], ((nt - 2) >> 1) & 1, 0x33);
+    w.wait(&ds_done[(nt - 1) & 1], ((nt - 1) >> 1) & 1, 0x34);
+    fence_after_sync();
+    if (a.dk_acc) {
+      const int nslab = pg.k16_start[IG];
+      for (int k16 = half; k16 < nslab; k16 += 2) {
+        float vv[16];
+        tmem_ld16(tK + lane_off + k16 * 16, vv);
+        tmem_ld_wait();
+        if (jglob < a.N && !dead) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            const int src = pg.src[k16 * 16 + x];
+            if (src >= 0) a.dk_acc[(koff + jglob) * HD + src] += a.scale * vv[x];   // Q image holds unscaled q
+          }
+        }
+      }
+    }
+    fence_before_sync();
+    __syncthreads();
+  }
+  // outputs
+  fence_after_sync();
+  {
+    // tensor-memory loads are warp-collective: every thread executes them, only the stores are guarded
+    const bool valid = jglob < a.N && !dead;
+    const int col0 = half == 0 ? 0 : 32;
+#pragma unroll
+    for (int cc = 0; cc < 32; cc += 16) {
+      float vv[16];
+      tmem_ld16(tU + lane_off + col0 + cc, vv);
+      tmem_ld_wait();
+      if (valid && a.dv) {
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+          const size_t o = (koff + jglob) * VD + col0 + cc + x;
+          float val = vv[x];
+          if (a.dv_init) val += a.dv_init[o];
+          reinterpret_cast<__nv_bfloat16*>(a.dv)[o] = __float2bfloat16_rn(val);
+        }
+      }
+    }
+    if (valid && a.dk && a.dk_acc) {
+      const size_t o = (koff + jglob) * HD + 32 * half;
+#pragma unroll
+      for (int x = 0; x < 32; ++x) reinterpret_cast<__nv_bfloat16*>(a.dk)[o + x] = __float2bfloat16_rn(a.dk_acc[o + x]);
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
+  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
+}
+
+}  // namespace
+
+cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
+                             const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dq,
+                             const float* dq_init, float* coef_partial, int32_t* status, int B, int Hq, int Hkv,
+                             int N, int NB, int G, float scale, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(intra_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BQ_SMEM);
+  if (e != cudaSuccess) return e;
+  IntraBwdArgs a{};
+  a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
+  a.v = static_cast<const __nv_bfloat16*>(v); a.gimg = static_cast<const __nv_bfloat16*>(gimg);
+  a.dim_perm = dim_perm; a.group_start = group_start; a.A = A; a.Bc = Bc; a.Cc = Cc;
+  a.dq = dq; a.dq_init = dq_init; a.coef_partial = coef_partial; a.status = status;
+  a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv; a.G = G; a.scale = scale;
+  a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
+  intra_bwd_q_kernel<<<dim3(NB, Hq, B), 256, BQ_SMEM, st>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t intra_backward_kv(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
+                              const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dk,
+                              void* dv, float* dk_acc, const float* dv_init, int32_t* status, int B, int Hq, int Hkv,
+                              int N, int NB, int G, float scale, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(intra_bwd_kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BKV_SMEM);
+  if (e != cudaSuccess) return e;
+  IntraBwdArgs a{};
+  a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
+  a.v = static_cast<const __nv_bfloat16*>(v); a.gimg = static_cast<const __nv_bfloat16*>(gimg);
+  a.dim_perm = dim_perm; a.group_start = group_start; a.A = A; a.Bc = Bc; a.Cc = Cc;
+  a.dk = dk; a.dv = dv; a.dk_acc = dk_acc; a.dv_init = dv_init; a.status = status;
+  a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv; a.G = G; a.scale = scale;
+  a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
+  intra_bwd_kv_kernel<<<dim3(NB, Hkv, B), 256, BKV_SMEM, st>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace oal

@@ -69,4 +69,19 @@ cudaError_t norm_vjp_image(const void* grad_out, int out_dt, const float* grad_n
                            const float* num, const float* den, float floor_v, float* g, void* gimg, int heads,
                            int N, int NB, cudaStream_t st);
 
+
+// ---- tensor-core intra-chunk kernels (oal_intra.cu, oal_intra_bwd.cu); at most 8 groups per head ----
+cudaError_t intra_forward(const void* q, const void* k, const void* v, const int32_t* dim_perm,
+                          const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* out,
+                          float* num, float* den, int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G,
+                          int out_dt, int slabs, float scale, float floor_v, cudaStream_t st);
+cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
+                             const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dq,
+                             const float* dq_init, float* coef_partial, int32_t* status, int B, int Hq, int Hkv,
+                             int N, int NB, int G, float scale, cudaStream_t st);
+cudaError_t intra_backward_kv(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
+                              const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dk,
+                              void* dv, float* dk_acc, const float* dv_init, int32_t* status, int B, int Hq, int Hkv,
+                              int N, int NB, int G, float scale, cudaStream_t st);
+
 }  // namespace oal

@@ -65,7 +65,7 @@ struct StateUpdateArgs {
   int32_t* status;
 };
 
-__global__ void __launch_bounds__(256, 1) state_update_kernel(const StateUpdateArgs a) {
+__global__ void __launch_bounds__(GEN_THREADS, 1) state_update_kernel(const StateUpdateArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Abuf = smem;                          // 2 x SLAB_A_BYTES
   unsigned char* Uimg = smem + 2 * SLAB_A_BYTES;       // [10][128 tokens][8 e]
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256, 1) state_update_kernel(const StateUpdateA
   const __nv_bfloat16* vbase = a.v + (size_t)u * a.N * VD;
   float x[HD];
   load_row_bf16(x, kbase, i, a.N, 1.f);
-  for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
+  for (int idx = tid; idx < (EP / 8) * CT; idx += GEN_THREADS) {
     const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
     reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(vbase + (size_t)j * VD, ec, j < a.N);
   }
@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(256, 1) state_update_kernel(const StateUpdateA
   auto epilogue = [&](int it) {
     w.wait(&mma_done[it & 1], (it >> 1) & 1);
     fence_after_sync();
+    if (warp >= 8) return;          // warps 0-7 cover the 128 lanes x 80 columns
     const int row = (s0 + it) * 128 + 32 * (warp & 3) + lane;
     const int col0 = warp < 4 ? 0 : 48, ncol = warp < 4 ? 48 : 32;
     float* dst = ds_base + (size_t)row * EP + col0;
@@ -140,7 +141,7 @@ __global__ void __launch_bounds__(256, 1) state_update_kernel(const StateUpdateA
   epilogue(ns - 1);
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, 256);
-  if (tid == 0 && dead) atomicOr(a.status, OAL_STATUS_WAIT_TIMEOUT);
+  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
 // ---------------------------------------------------------------------------
@@ -205,7 +206,7 @@ struct CrossReadArgs {
 constexpr int CR_STAGES = 4;
 
 template <bool QUERY>
-__global__ void __launch_bounds__(256, 1) cross_read_kernel(const CrossReadArgs a) {
+__global__ void __launch_bounds__(GEN_THREADS, 1) cross_read_kernel(const CrossReadArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Abuf = smem;                                   // 2 x SLAB_A_BYTES
   unsigned char* Sbuf = smem + 2 * SLAB_A_BYTES;                // CR_STAGES x SLAB_S_BYTES
@@ -227,7 +228,7 @@ __global__ void __launch_bounds__(256, 1) cross_read_kernel(const CrossReadArgs 
     dead = 0;
   }
   if (QUERY)
-    for (int f = tid; f < F_ROWS; f += 256) coef[f] = a.coef_table[(size_t)h * F_ROWS + f];
+    for (int f = tid; f < F_ROWS; f += GEN_THREADS) coef[f] = a.coef_table[(size_t)h * F_ROWS + f];
   const int i = c * CT + token;
   float x[HD];
   load_row_bf16(x, a.x + (size_t)(b * a.H + h) * a.N * HD, i, a.N, a.mul);
@@ -273,7 +274,7 @@ __global__ void __launch_bounds__(256, 1) cross_read_kernel(const CrossReadArgs 
   w.wait(&mma_done[1], ((F_SLABS - 2) >> 1) & 1);    // slab 15
   w.wait(&mma_done[0], ((F_SLABS - 1) >> 1) & 1);    // slab 16
   fence_after_sync();
-  {
+  if (warp < 8) {
     const int row = c * CT + 32 * (warp & 3) + lane;
     const int col0 = warp < 4 ? 0 : 48, ncol = warp < 4 ? 48 : 32;
     const uint32_t t = tacc + ((uint32_t)(32 * (warp & 3)) << 16) + col0;
@@ -298,7 +299,7 @@ __global__ void __launch_bounds__(256, 1) cross_read_kernel(const CrossReadArgs 
   fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, 128);
-  if (tid == 0 && dead) atomicOr(a.status, OAL_STATUS_WAIT_TIMEOUT);
+  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
 }  // namespace
@@ -318,7 +319,7 @@ cudaError_t state_update(const void* k, const void* v, float* ds, int units, int
   cudaError_t e = cudaFuncSetAttribute(state_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   StateUpdateArgs a{static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ds, N, NB, status};
-  state_update_kernel<<<dim3(4, NB, units), 256, smem, st>>>(a);
+  state_update_kernel<<<dim3(4, NB, units), GEN_THREADS, smem, st>>>(a);
   return cudaGetLastError();
 }
 
@@ -339,11 +340,11 @@ cudaError_t cross_read(bool query, const void* x, const void* image, const float
   if (query) {
     e = cudaFuncSetAttribute(cross_read_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    cross_read_kernel<true><<<dim3(NB, H, B), 256, smem, st>>>(a);
+    cross_read_kernel<true><<<dim3(NB, H, B), GEN_THREADS, smem, st>>>(a);
   } else {
     e = cudaFuncSetAttribute(cross_read_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    cross_read_kernel<false><<<dim3(NB, H, B), 256, smem, st>>>(a);
+    cross_read_kernel<false><<<dim3(NB, H, B), GEN_THREADS, smem, st>>>(a);
   }
   return cudaGetLastError();
 }

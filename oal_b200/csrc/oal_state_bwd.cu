@@ -48,7 +48,7 @@ struct DStateArgs {
   int32_t* status;
 };
 
-__global__ void __launch_bounds__(256, 1) dstate_heads_kernel(const DStateArgs a) {
+__global__ void __launch_bounds__(GEN_THREADS, 1) dstate_heads_kernel(const DStateArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Abuf = smem;                        // 2 x SLAB_A_BYTES
   unsigned char* Gbuf = smem + 2 * SLAB_A_BYTES;     // 2 x SLAB_S_BYTES  ([10][128 tokens][8 e])
@@ -98,33 +98,35 @@ __global__ void __launch_bounds__(256, 1) dstate_heads_kernel(const DStateArgs a
     w.wait(&mma_done[m & 1], (m >> 1) & 1);
     fence_after_sync();
     const int f = (s0 + im) * 128 + fr;
-    const float cf = a.coef_table[(size_t)h * F_ROWS + f];
-    float dot = 0.f;
-    for (int cc = 0; cc < ncol; cc += 16) {
-      float z[16];
-      tmem_ld16(tz + (m & 1) * EP + lane_off + col0 + cc, z);
-      float acc[16];
-      if (hm > 0) tmem_ld16(tacc + im * EP + lane_off + col0 + cc, acc);
-      tmem_ld_wait();
-      if (carry_base) {
-        const uint4* cp = reinterpret_cast<const uint4*>(carry_base + (size_t)(s0 + im) * SLAB_S_BYTES);
-        const int ec = (col0 + cc) >> 3;
-        float c0[8], c1[8];
-        unpack_bf16x8(cp[ec * 128 + fr], c0);
-        unpack_bf16x8(cp[(ec + 1) * 128 + fr], c1);
+    if (warp < 8) {                 // warps 0-7 cover the 128 lanes x 80 columns
+      const float cf = a.coef_table[(size_t)h * F_ROWS + f];
+      float dot = 0.f;
+      for (int cc = 0; cc < ncol; cc += 16) {
+        float z[16];
+        tmem_ld16(tz + (m & 1) * EP + lane_off + col0 + cc, z);
+        float acc[16];
+        if (hm > 0) tmem_ld16(tacc + im * EP + lane_off + col0 + cc, acc);
+        tmem_ld_wait();
+        if (carry_base) {
+          const uint4* cp = reinterpret_cast<const uint4*>(carry_base + (size_t)(s0 + im) * SLAB_S_BYTES);
+          const int ec = (col0 + cc) >> 3;
+          float c0[8], c1[8];
+          unpack_bf16x8(cp[ec * 128 + fr], c0);
+          unpack_bf16x8(cp[(ec + 1) * 128 + fr], c1);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dot = fmaf(z[j], c0[j], fmaf(z[8 + j], c1[j], dot));
+          for (int j = 0; j < 8; ++j) dot = fmaf(z[j], c0[j], fmaf(z[8 + j], c1[j], dot));
+        }
+        uint32_t o[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(hm > 0 ? fmaf(cf, z[j], acc[j]) : cf * z[j]);
+        tmem_st16(tacc + im * EP + lane_off + col0 + cc, o);
       }
-      uint32_t o[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(hm > 0 ? fmaf(cf, z[j], acc[j]) : cf * z[j]);
-      tmem_st16(tacc + im * EP + lane_off + col0 + cc, o);
+      tmem_st_wait();
+      if (a.dcoef_partial) dsum[m & 1][wg][fr] = dot;
     }
-    tmem_st_wait();
     if (a.dcoef_partial) {
-      dsum[m & 1][wg][fr] = dot;
       __syncthreads();
-      if (wg == 0)
+      if (warp < 4)
         a.dcoef_partial[(((size_t)b * a.NB + c) * a.Hq + h) * F_ROWS + f] = dsum[m & 1][0][fr] + dsum[m & 1][1][fr];
     }
     fence_before_sync();
@@ -163,7 +165,7 @@ __global__ void __launch_bounds__(256, 1) dstate_heads_kernel(const DStateArgs a
   fence_after_sync();
   // dCarry rows of this slab group: tensor memory -> HBM
   float* dbase = a.dcarry + ((size_t)u * a.NB + c) * F_ROWS * EP;
-  for (int it = 0; it < ns; ++it) {
+  for (int it = 0; it < ns && warp < 8; ++it) {
     float* dst = dbase + (size_t)((s0 + it) * 128 + fr) * EP + col0;
     for (int cc = 0; cc < ncol; cc += 16) {
       float vv[16];
@@ -178,7 +180,7 @@ __global__ void __launch_bounds__(256, 1) dstate_heads_kernel(const DStateArgs a
   fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
-  if (tid == 0 && dead) atomicOr(a.status, OAL_STATUS_WAIT_TIMEOUT);
+  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
 // ---------------------------------------------------------------------------
@@ -379,7 +381,7 @@ __global__ void __launch_bounds__(256, 1) feature_grad_kernel(const FeatGradArgs
   fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, 256);
-  if (tid == 0 && dead) atomicOr(a.status, OAL_STATUS_WAIT_TIMEOUT);
+  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
 // ---------------------------------------------------------------------------
@@ -474,15 +476,23 @@ __global__ void __launch_bounds__(256) norm_vjp_image_kernel(const void* grad_ou
     if (grad_den) gd += grad_den[row];
     if (lane < EP - VD) g[row * EP + VD + lane] = lane == 0 ? gd : 0.f;
   }
+  // hi image = bf16(g); lo image = bf16(g - hi): dW = g . [v|1] is formed from both, because its two
+  // large terms (dout.v / den and dout.num / den^2) nearly cancel
   __nv_bfloat16* img = gimg + (bh * NB + cidx) * (size_t)(SLAB_S_BYTES / 2);
+  __nv_bfloat16* img_lo = img + (size_t)heads * NB * (SLAB_S_BYTES / 2);
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     const int e = lane + 32 * c;
-    img[((e >> 3) * CT + tl) * 8 + (e & 7)] = __float2bfloat16_rn(gv[c]);
+    const __nv_bfloat16 hi = __float2bfloat16_rn(gv[c]);
+    img[((e >> 3) * CT + tl) * 8 + (e & 7)] = hi;
+    img_lo[((e >> 3) * CT + tl) * 8 + (e & 7)] = __float2bfloat16_rn(gv[c] - __bfloat162float(hi));
   }
   if (lane < EP - VD) {
     const int e = VD + lane;
-    img[((e >> 3) * CT + tl) * 8 + (e & 7)] = __float2bfloat16_rn(lane == 0 ? gd : 0.f);
+    const float val = lane == 0 ? gd : 0.f;
+    const __nv_bfloat16 hi = __float2bfloat16_rn(val);
+    img[((e >> 3) * CT + tl) * 8 + (e & 7)] = hi;
+    img_lo[((e >> 3) * CT + tl) * 8 + (e & 7)] = __float2bfloat16_rn(val - __bfloat162float(hi));
   }
 }
 
@@ -497,7 +507,7 @@ cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img,
   DStateArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(gimg),
                static_cast<const __nv_bfloat16*>(carry_img), coef_table, dcarry, dcoef_partial, N, NB, Hq, Hkv,
                scale, status};
-  dstate_heads_kernel<<<dim3(5, NB, B * Hkv), 256, smem, st>>>(a);
+  dstate_heads_kernel<<<dim3(5, NB, B * Hkv), GEN_THREADS, smem, st>>>(a);
   return cudaGetLastError();
 }
 

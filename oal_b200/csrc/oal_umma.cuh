@@ -144,8 +144,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Wait for the phase with the given parity.  The wait is bounded (about a second of
-// SM clocks): on expiry it returns false and the caller records
+// Wait for the phase with the given parity.  The wait is bounded (about 25 ms of
+// SM clocks, far longer than any kernel of this library runs): on expiry it returns false and the caller records
 // OAL_STATUS_WAIT_TIMEOUT and leaves its loops; it never spins forever.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t addr = smem_u32(bar);
@@ -162,7 +162,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
-    if (clock64() - t0 > 2000000000LL) return false;
+    if (clock64() - t0 > 50000000LL) return false;
   }
 }
 

@@ -34,6 +34,7 @@ class GroupTables:
     dim_perm: torch.Tensor      # int32 [Hq, 64]: dims sorted by group id (padded dims first, group 0)
     group_start: torch.Tensor   # int32 [Hq, 17]: group g owns dim_perm[h, start[g]:start[g+1]]
     group_count: int            # G = extent of B / C
+    padded_slabs: int = 0       # max over heads of sum_g ceil(|g| / 16) (0 = unknown)
 
 
 def build_group_tables(groups: torch.Tensor, group_count: int) -> GroupTables:
@@ -47,7 +48,8 @@ def build_group_tables(groups: torch.Tensor, group_count: int) -> GroupTables:
     counts.scatter_add_(1, g64, torch.ones_like(g64))
     start = torch.zeros(hq, _lib.MAX_GROUPS + 1, dtype=torch.int64, device=groups.device)
     start[:, 1:] = counts.cumsum(1)
-    return GroupTables(perm.contiguous(), start.to(torch.int32).contiguous(), int(group_count))
+    slabs = int(((counts + 15) // 16).sum(1).max().item())
+    return GroupTables(perm.contiguous(), start.to(torch.int32).contiguous(), int(group_count), slabs)
 
 
 def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
@@ -77,7 +79,9 @@ def raise_on_status(status: torch.Tensor) -> None:
     (oal_attention/hd_block_gemm_runtime.py:392-408)."""
     bits = int(status.item())
     if bits & _lib.STATUS_WAIT_TIMEOUT:
-        raise RuntimeError("oal_b200 kernel gave up on a bounded wait (device status word)")
+        raise RuntimeError(f"oal_b200 kernel gave up on a bounded wait (device status word {bits:#x})")
+    if bits & _lib.STATUS_BAD_LAYOUT:
+        raise ValueError("problem.padded_slabs is smaller than a head's padded group layout")
     if bits & (_lib.STATUS_NONFINITE | _lib.STATUS_DENOMINATOR):
         raise RuntimeError(f"{_DENOMINATOR_ERROR} (device status {bits})")
 
@@ -95,7 +99,7 @@ def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: flo
     dev = q.device
     problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=q.dtype, out_dtype=kernel_out,
                            precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
-                           floor=float(floor))
+                           floor=float(floor), padded_slabs=tables.padded_slabs)
     out = torch.empty(B, Hq, N, _lib.HEAD_DIM, dtype=kernel_out, device=dev)
     num = torch.empty(B, Hq, N, _lib.HEAD_DIM, dtype=torch.float32, device=dev)
     den = torch.empty(B, Hq, N, dtype=torch.float32, device=dev)
@@ -167,6 +171,8 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
                           _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dA), _lib.ptr(dB), _lib.ptr(dC),
                           _lib.ptr(dstate_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status), _stream_ptr(dev))
     _lib.check(rc)
+    if plan.precision == "bf16_tensorcore":
+        raise_on_status(status)      # only a bounded wait that gave up can set it here
     if D != _lib.HEAD_DIM:
         dq = None if dq is None else dq[..., :D].contiguous()
         dk = None if dk is None else dk[..., :D].contiguous()

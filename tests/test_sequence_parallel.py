@@ -109,7 +109,7 @@ def test_rank_emulation_matches_single_call(splits):
             parts[key].append(val)
     for key, vals in parts.items():
         got = torch.cat(vals, dim=2)
-        assert ERR(got, full[key]) < 5e-3, key
+        assert ERR(got, full[key]) < 1e-2, key      # bf16 outputs: one ulp near the maximum is 4e-3
 
 
 def _nccl_script():
