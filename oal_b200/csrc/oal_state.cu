@@ -203,14 +203,15 @@ struct CrossReadArgs {
   int32_t* status;
 };
 
-constexpr int CR_STAGES = 4;
+constexpr int CR_STAGES = 2;      // two CTAs share an SM: the other CTA hides this one's copy latency
 
 template <bool QUERY>
-__global__ void __launch_bounds__(GEN_THREADS, 1) cross_read_kernel(const CrossReadArgs a) {
+__global__ void __launch_bounds__(GEN_THREADS, 2) cross_read_kernel(const CrossReadArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Abuf = smem;                                   // 2 x SLAB_A_BYTES
   unsigned char* Sbuf = smem + 2 * SLAB_A_BYTES;                // CR_STAGES x SLAB_S_BYTES
-  float* coef = reinterpret_cast<float*>(Sbuf + CR_STAGES * SLAB_S_BYTES);   // F_ROWS floats (QUERY)
+  // per-head coefficient table, read straight from global memory (warp-uniform, L1-resident)
+  const float* coef = QUERY ? a.coef_table + (size_t)blockIdx.y * F_ROWS : nullptr;
   __shared__ uint64_t full[CR_STAGES];
   __shared__ uint64_t mma_done[2];
   __shared__ uint32_t tmem_base;
@@ -227,8 +228,6 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) cross_read_kernel(const CrossR
     mbar_fence_init();
     dead = 0;
   }
-  if (QUERY)
-    for (int f = tid; f < F_ROWS; f += GEN_THREADS) coef[f] = a.coef_table[(size_t)h * F_ROWS + f];
   const int i = c * CT + token;
   float x[HD];
   load_row_bf16(x, a.x + (size_t)(b * a.H + h) * a.N * HD, i, a.N, a.mul);
@@ -250,10 +249,10 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) cross_read_kernel(const CrossR
     const int buf = s & 1;
     if (s >= 2) {
       w.wait(&mma_done[buf], ((s - 2) >> 1) & 1);      // slab s-2 finished: A[buf] and its state stage are free
-      if (tid == 0 && s + 2 < F_SLABS) {
-        const int st = (s + 2) % CR_STAGES;
+      if (tid == 0 && s + CR_STAGES - 2 < F_SLABS) {
+        const int nxt = s + CR_STAGES - 2, st = nxt % CR_STAGES;
         mbar_arrive_expect_tx(&full[st], SLAB_S_BYTES);
-        bulk_g2s(Sbuf + st * SLAB_S_BYTES, img + (size_t)(s + 2) * SLAB_S_BYTES, SLAB_S_BYTES, &full[st]);
+        bulk_g2s(Sbuf + st * SLAB_S_BYTES, img + (size_t)nxt * SLAB_S_BYTES, SLAB_S_BYTES, &full[st]);
       }
     }
     write_half_slab<QUERY>(s, half, x, coef, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES), token);
@@ -333,7 +332,7 @@ cudaError_t state_scan(const float* ds, void* image, const float* state_in, floa
 cudaError_t cross_read(bool query, const void* x, const void* image, const float* coef_table, float* out64,
                        float* out1, int B, int H, int rep, int N, int NB, float mul, int32_t* status,
                        cudaStream_t st) {
-  const int smem = 2 * SLAB_A_BYTES + CR_STAGES * SLAB_S_BYTES + F_ROWS * (int)sizeof(float);
+  const int smem = 2 * SLAB_A_BYTES + CR_STAGES * SLAB_S_BYTES;
   CrossReadArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(image), coef_table,
                   out64, out1, N, NB, H, rep, mul, status};
   cudaError_t e;

@@ -213,6 +213,8 @@ def oal_attention(
     factor, gmax = _validate_factor(factor, query_heads=q.shape[1], q_device=q.device)
     working_dtype = _resolve_working_dtype(q.dtype, factor.dtype)
     _validate_kernel_eps(kernel_eps, working_dtype=working_dtype)
+    _canonicalize_dim_groups(dim_groups, query_heads=q.shape[1], head_dimension=q.shape[-1], gmax=gmax,
+                             q_device=q.device)
     _resolve_scale(scale, q.shape[-1])
     if execution == "reference":
         raise RuntimeError("execution='reference' (the pure-torch statement) is not part of oal_b200")
