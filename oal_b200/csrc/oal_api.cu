@@ -143,6 +143,7 @@ struct BackwardSpaceTC {
   float* dcoef;
   float* slots;
   float *dq_cross, *dk_cross, *dv_cross;
+  float *dk_part, *dv_part;      // per-query-head intra-chunk shares of dk / dv
   size_t bytes;
 };
 
@@ -165,6 +166,8 @@ BackwardSpaceTC carve_backward_tc(const OalProblem* p, void* ws) {
   s.dq_cross = c.take<float>(qrows * oal::HD);
   s.dk_cross = c.take<float>(krows * oal::HD);
   s.dv_cross = c.take<float>(krows * oal::VD);
+  s.dk_part = c.take<float>(qrows * oal::HD);
+  s.dv_part = c.take<float>(qrows * oal::VD);
   s.bytes = c.off;
   return s;
 }
@@ -440,10 +443,11 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
       if (e != cudaSuccess) return fail_cuda(e, "key cross read kernel");
     }
     if (tc_intra) {
-      { LaunchScope scope("intra_backward_kv", st);
+      { LaunchScope scope("intra_backward_kv", st, 1 + (want_k ? 1 : 0) + (want_v ? 1 : 0));
         e = oal::intra_backward_kv(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_k ? dk : nullptr,
                                    want_v ? dv : nullptr, want_k ? s.dk_cross : nullptr, want_v ? s.dv_cross : nullptr,
-                                   status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->scale, st); }
+                                   s.dk_part, s.dv_part, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
+                                   p->groups, p->scale, st); }
       if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward key/value-side kernel");
     } else {
       a.dq = nullptr; a.dq_init = nullptr; a.coef_partial = nullptr;

@@ -92,6 +92,17 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 lanes x 32-bit, 4 consecutive columns per thread.
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
+  uint32_t r[4];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // Issue the per-group score MMAs  S_g[128 x KT] = X_g (128 rows) . Y_g (KT rows)^T  for one tile.
 //   x_addr: image whose 128 rows are the MMA M dimension; y_addr: image, rows [yrow0, yrow0+KT) are N
 __device__ __forceinline__ void issue_group_scores(uint32_t tmem_s, uint32_t x_addr, uint32_t y_addr, int yrow0,

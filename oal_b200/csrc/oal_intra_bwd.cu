@@ -21,6 +21,14 @@ using namespace umma;
 constexpr int IMG_BYTES = (DP_MAX / 8) * CT * 16;        // 45056
 constexpr int TILE_BYTES = (KT / 8) * CT * 16;           // 4096: bf16 [2][128 rows][8]
 constexpr int NTRI = IG * (IG + 1) / 2;
+constexpr int BT = 512;                 // threads per CTA: 128 rows x 4 column parts
+constexpr int CW = KT / (BT / CT);      // columns of a tile handled by one thread (4)
+
+// 8 bytes (4 bf16) of a [2][128 rows][8] tile image: columns 4*part .. 4*part+3 of `row`
+__device__ __forceinline__ void store_tile4(unsigned char* tile, int part, int row, const float (&t)[4]) {
+  *reinterpret_cast<uint2*>(tile + ((part >> 1) * CT + row) * 16 + (part & 1) * 8) =
+      make_uint2(pack_bf16(t[0], t[1]), pack_bf16(t[2], t[3]));
+}
 
 __device__ __forceinline__ int tri8(int g, int g2) { return g * GMAX - (g * (g - 1)) / 2 + (g2 - g); }
 
@@ -32,8 +40,8 @@ struct IntraBwdArgs {
   const float *A, *Bc, *Cc;
   void *dq, *dk, *dv;               // io dtype outputs (bf16), may be null
   const float* dq_init;             // fp32 cross part (already scaled), or null
-  float* dk_acc;                    // fp32 [B,Hkv,N,64]: holds the cross part, used as accumulator
-  const float* dv_init;             // fp32 cross part, or null
+  float* dk_part;                   // fp32 [B,Hq,N,64]: this query head's intra-chunk share of dk
+  float* dv_part;                   // fp32 [B,Hq,N,64]: this query head's intra-chunk share of dv
   float* coef_partial;              // [B][Hq][NB][NCOEF] or null
   int32_t* status;
   int N, NB, Hq, Hkv, G;
@@ -50,7 +58,7 @@ struct PairOut {
 // ---------------------------------------------------------------------------
 constexpr int BQ_SMEM = 2 * IMG_BYTES + 3 * SLAB_S_BYTES + 2 * IG * TILE_BYTES;
 
-__global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs a) {
+__global__ void __launch_bounds__(BT, 1) intra_bwd_q_kernel(const IntraBwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Qimg = smem;
   unsigned char* Kimg = Qimg + IMG_BYTES;
@@ -61,11 +69,10 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
   __shared__ uint64_t s_done, ds_done[2], gfull;
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
-  __shared__ float red[8 * NCOEF];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (a.Hq / a.Hkv);
-  const int half = warp >> 2, row = 32 * (warp & 3) + lane;
+  const int part = warp >> 2, row = 32 * (warp & 3) + lane;
   if (warp == 0) tmem_alloc(&tmem_base, 512);
   if (tid == 0) {
     mbar_init(&s_done, 1);
@@ -75,7 +82,7 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
     mbar_fence_init();
     dead = 0;
   }
-  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, 256);
+  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, BT);
   const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
   if (tid == 0) {
     const unsigned char* gsrc =
@@ -85,9 +92,9 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
     bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
   }
   // the ds tile buffers are idle during set-up: use them as the staging area of the image builds
-  build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, 256);
-  build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, 256);
-  for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
+  build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, BT);
+  build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, BT);
+  for (int idx = tid; idx < (EP / 8) * CT; idx += BT) {
     const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
     reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
   }
@@ -126,18 +133,18 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
 
   for (int kt = 0; kt < tiles; ++kt) {
     const int buf = kt & 1;
-    float s[IG][8], dw[8];
+    float s[IG][CW], dw[CW];
     w.wait(&s_done, kt & 1, 0x21);
     fence_after_sync();
 #pragma unroll
     for (int g = 0; g < IG; ++g) {
-      if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld8(tS + lane_off + g * KT + 8 * half, s[g]);
+      if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld4(tS + lane_off + g * KT + CW * part, s[g]);
       else {
 #pragma unroll
-        for (int x = 0; x < 8; ++x) s[g][x] = 0.f;
+        for (int x = 0; x < CW; ++x) s[g][x] = 0.f;
       }
     }
-    tmem_ld8(tW + lane_off + 8 * half, dw);
+    tmem_ld4(tW + lane_off + CW * part, dw);
     tmem_ld_wait();
     fence_before_sync();
     __syncthreads();
@@ -150,51 +157,50 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
     unsigned char* dsb = DS + buf * IG * TILE_BYTES;
     if (warp_active) {
 #pragma unroll
-      for (int x = 0; x < 8; ++x) {
-        if (kt * KT + 8 * half + x > row) dw[x] = 0.f;
+      for (int x = 0; x < CW; ++x) {
+        if (kt * KT + CW * part + x > row) dw[x] = 0.f;
         cA += dw[x];
       }
 #pragma unroll
       for (int g = 0; g < IG; ++g)
 #pragma unroll
-        for (int x = 0; x < 8; ++x) s[g][x] *= a.scale;
+        for (int x = 0; x < CW; ++x) s[g][x] *= a.scale;
 #pragma unroll
       for (int g = 0; g < IG; ++g) {
-        float t[8];
+        float t[CW];
         const float bg = pg.B[g];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) t[x] = bg;
+        for (int x = 0; x < CW; ++x) t[x] = bg;
 #pragma unroll
         for (int g2 = 0; g2 < IG; ++g2) {
           const float c2 = 2.f * pg.C[g * IG + g2];
 #pragma unroll
-          for (int x = 0; x < 8; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+          for (int x = 0; x < CW; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
         }
 #pragma unroll
-        for (int x = 0; x < 8; ++x) t[x] *= dw[x];
-        reinterpret_cast<uint4*>(dsb + g * TILE_BYTES)[half * CT + row] =
-            make_uint4(pack_bf16(t[0], t[1]), pack_bf16(t[2], t[3]), pack_bf16(t[4], t[5]), pack_bf16(t[6], t[7]));
+        for (int x = 0; x < CW; ++x) t[x] *= dw[x];
+        store_tile4(dsb + g * TILE_BYTES, part, row, t);
       }
       int idx = 0;
 #pragma unroll
       for (int g = 0; g < IG; ++g) {
-        float ws[8];
+        float ws[CW];
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
+        for (int x = 0; x < CW; ++x) {
           ws[x] = dw[x] * s[g][x];
           cB[g] += ws[x];
         }
 #pragma unroll
         for (int g2 = g; g2 < IG; ++g2) {
 #pragma unroll
-          for (int x = 0; x < 8; ++x) cC[idx] = fmaf(ws[x], s[g2][x], cC[idx]);
+          for (int x = 0; x < CW; ++x) cC[idx] = fmaf(ws[x], s[g2][x], cC[idx]);
           ++idx;
         }
       }
     } else {
+      const float zero[CW] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int g = 0; g < IG; ++g)
-        reinterpret_cast<uint4*>(dsb + g * TILE_BYTES)[half * CT + row] = make_uint4(0u, 0u, 0u, 0u);
+      for (int g = 0; g < IG; ++g) store_tile4(dsb + g * TILE_BYTES, part, row, zero);
     }
     fence_async_smem();
     __syncthreads();
@@ -216,7 +222,7 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
   if (a.dq) {
     const int i = c * CT + row;
     const int nslab = pg.k16_start[IG];
-    for (int k16 = half; k16 < nslab; k16 += 2) {
+    for (int k16 = part; k16 < nslab; k16 += BT / CT) {
       float vv[16];
       tmem_ld16(tQ + lane_off + k16 * 16, vv);
       tmem_ld_wait();
@@ -237,6 +243,7 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
   fence_before_sync();
   __syncthreads();
   if (a.coef_partial) {
+    float* red = reinterpret_cast<float*>(DS);      // the ds tiles are idle now: [16 warps][NCOEF]
     auto wsum = [](float v) {
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -262,10 +269,10 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
       }
     __syncthreads();
     float* dst = a.coef_partial + ((size_t)(b * a.Hq + h) * a.NB + c) * NCOEF;
-    for (int x = tid; x < NCOEF; x += 256) {
+    for (int x = tid; x < NCOEF; x += BT) {
       float t = 0.f;
 #pragma unroll
-      for (int ww = 0; ww < 8; ++ww) t += red[ww * NCOEF + x];
+      for (int ww = 0; ww < BT / 32; ++ww) t += red[ww * NCOEF + x];
       dst[x] = t;
     }
   }
@@ -279,7 +286,7 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_q_kernel(const IntraBwdArgs 
 // ---------------------------------------------------------------------------
 constexpr int BKV_SMEM = 2 * IMG_BYTES + 3 * SLAB_S_BYTES + 2 * IG * TILE_BYTES + 2 * TILE_BYTES;
 
-__global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs a) {
+__global__ void __launch_bounds__(BT, 1) intra_bwd_kv_kernel(const IntraBwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Kimg = smem;
   unsigned char* Qimg = Kimg + IMG_BYTES;
@@ -292,9 +299,11 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int rep = a.Hq / a.Hkv;
-  const int half = warp >> 2, row = 32 * (warp & 3) + lane;     // row = key index inside the chunk
+  // one CTA per (chunk, query head, batch row): the per-head shares are summed over the query heads
+  // of a KV head afterwards, in fixed order, by kv_head_reduce_kernel
+  const int c = blockIdx.x, b = blockIdx.z;
+  const int rep = 1, kvh = blockIdx.y / (a.Hq / a.Hkv);
+  const int part = warp >> 2, row = 32 * (warp & 3) + lane;     // row = key index inside the chunk
   if (warp == 0) tmem_alloc(&tmem_base, 512);
   if (tid == 0) {
     mbar_init(&s_done, 1);
@@ -305,7 +314,7 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
     dead = 0;
   }
   const size_t koff = (size_t)(b * a.Hkv + kvh) * a.N;
-  for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
+  for (int idx = tid; idx < (EP / 8) * CT; idx += BT) {
     const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
     reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
   }
@@ -325,7 +334,7 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
   int nt = 0;                                   // tiles issued so far over all heads
 
   for (int hh = 0; hh < rep; ++hh) {
-    const int h = kvh * rep + hh;
+    const int h = blockIdx.y + hh;
     const size_t qoff = (size_t)(b * a.Hq + h) * a.N;
     // every MMA of the previous head has completed (waited at its end): the images may be rebuilt
     if (tid == 0) {
@@ -335,10 +344,21 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
       bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, &gfull);
       bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
     }
-    load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, 256);
+    // the K image depends only on the head's group layout: keep it when the layout repeats
+    bool same_layout = hh > 0;
+    if (hh > 0) {
+      for (int x = tid; x < HD + GMAX + 1; x += BT) {
+        const bool eq = x < HD ? a.dim_perm[h * HD + x] == a.dim_perm[(h - 1) * HD + x]
+                               : a.group_start[h * (GMAX + 1) + x - HD] == a.group_start[(h - 1) * (GMAX + 1) + x - HD];
+        if (!eq) same_layout = false;
+      }
+    }
+    same_layout = __syncthreads_and(same_layout);
+    load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, BT);
     // every MMA that read the ds tiles has completed: they double as staging area of the image builds
-    build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, 256);
-    build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, 256);
+    if (!same_layout)
+      build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, BT);
+    build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, BT);
     fence_async_smem();
     __syncthreads();
 
@@ -359,18 +379,18 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
     }
     for (int qt = 0; qt < tiles; ++qt, ++nt) {
       const int buf = nt & 1;
-      float s[IG][8], dw[8];
+      float s[IG][CW], dw[CW];
       w.wait(&s_done, nt & 1, 0x31);
       fence_after_sync();
 #pragma unroll
       for (int g = 0; g < IG; ++g) {
-        if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld8(tS + lane_off + g * KT + 8 * half, s[g]);
+        if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld4(tS + lane_off + g * KT + CW * part, s[g]);
         else {
 #pragma unroll
-          for (int x = 0; x < 8; ++x) s[g][x] = 0.f;
+          for (int x = 0; x < CW; ++x) s[g][x] = 0.f;
         }
       }
-      tmem_ld8(tW + lane_off + 8 * half, dw);
+      tmem_ld4(tW + lane_off + CW * part, dw);
       tmem_ld_wait();
       fence_before_sync();
       __syncthreads();
@@ -382,49 +402,46 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
       const bool warp_active = 32 * (warp & 3) <= qt * KT + KT - 1;
       if (nt >= 2) w.wait(&ds_done[buf], ((nt - 2) >> 1) & 1, 0x32);
       unsigned char* dsb = DS + buf * IG * TILE_BYTES;
-      float wv[8];
+      float wv[CW];
       if (warp_active) {
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
+        for (int x = 0; x < CW; ++x) {
           wv[x] = pg.A;
-          if (qt * KT + 8 * half + x < row) dw[x] = 0.f;          // query earlier than the key
+          if (qt * KT + CW * part + x < row) dw[x] = 0.f;          // query earlier than the key
         }
 #pragma unroll
         for (int g = 0; g < IG; ++g)
 #pragma unroll
-          for (int x = 0; x < 8; ++x) s[g][x] *= a.scale;
+          for (int x = 0; x < CW; ++x) s[g][x] *= a.scale;
 #pragma unroll
         for (int g = 0; g < IG; ++g) {
-          float t[8];
+          float t[CW];
 #pragma unroll
-          for (int x = 0; x < 8; ++x) t[x] = 0.f;
+          for (int x = 0; x < CW; ++x) t[x] = 0.f;
 #pragma unroll
           for (int g2 = 0; g2 < IG; ++g2) {
             const float c2 = pg.C[g * IG + g2];
 #pragma unroll
-            for (int x = 0; x < 8; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+            for (int x = 0; x < CW; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
           }
           const float bg = pg.B[g];
 #pragma unroll
-          for (int x = 0; x < 8; ++x) {
+          for (int x = 0; x < CW; ++x) {
             wv[x] = fmaf(s[g][x], bg + t[x], wv[x]);
             t[x] = dw[x] * (bg + 2.f * t[x]);
           }
-          reinterpret_cast<uint4*>(dsb + g * TILE_BYTES)[half * CT + row] =
-              make_uint4(pack_bf16(t[0], t[1]), pack_bf16(t[2], t[3]), pack_bf16(t[4], t[5]), pack_bf16(t[6], t[7]));
+          store_tile4(dsb + g * TILE_BYTES, part, row, t);
         }
 #pragma unroll
-        for (int x = 0; x < 8; ++x)
-          if (qt * KT + 8 * half + x < row) wv[x] = 0.f;
+        for (int x = 0; x < CW; ++x)
+          if (qt * KT + CW * part + x < row) wv[x] = 0.f;
       } else {
 #pragma unroll
-        for (int x = 0; x < 8; ++x) wv[x] = 0.f;
+        for (int x = 0; x < CW; ++x) wv[x] = 0.f;
 #pragma unroll
-        for (int g = 0; g < IG; ++g)
-          reinterpret_cast<uint4*>(dsb + g * TILE_BYTES)[half * CT + row] = make_uint4(0u, 0u, 0u, 0u);
+        for (int g = 0; g < IG; ++g) store_tile4(dsb + g * TILE_BYTES, part, row, wv);
       }
-      reinterpret_cast<uint4*>(WT + buf * TILE_BYTES)[half * CT + row] =
-          make_uint4(pack_bf16(wv[0], wv[1]), pack_bf16(wv[2], wv[3]), pack_bf16(wv[4], wv[5]), pack_bf16(wv[6], wv[7]));
+      store_tile4(WT + buf * TILE_BYTES, part, row, wv);
       fence_async_smem();
       __syncthreads();
       if (tid == 0) {
@@ -444,9 +461,9 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
     if (nt >= 2) w.wait(&ds_done[(nt - 2) & 1], ((nt - 2) >> 1) & 1, 0x33);
     w.wait(&ds_done[(nt - 1) & 1], ((nt - 1) >> 1) & 1, 0x34);
     fence_after_sync();
-    if (a.dk_acc) {
+    if (a.dk_part) {
       const int nslab = pg.k16_start[IG];
-      for (int k16 = half; k16 < nslab; k16 += 2) {
+      for (int k16 = part; k16 < nslab; k16 += BT / CT) {
         float vv[16];
         tmem_ld16(tK + lane_off + k16 * 16, vv);
         tmem_ld_wait();
@@ -454,7 +471,7 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
 #pragma unroll
           for (int x = 0; x < 16; ++x) {
             const int src = pg.src[k16 * 16 + x];
-            if (src >= 0) a.dk_acc[(koff + jglob) * HD + src] += a.scale * vv[x];   // Q image holds unscaled q
+            if (src >= 0) a.dk_part[(qoff + jglob) * HD + src] = a.scale * vv[x];   // Q image holds unscaled q
           }
         }
       }
@@ -467,32 +484,43 @@ __global__ void __launch_bounds__(256, 1) intra_bwd_kv_kernel(const IntraBwdArgs
   {
     // tensor-memory loads are warp-collective: every thread executes them, only the stores are guarded
     const bool valid = jglob < a.N && !dead;
-    const int col0 = half == 0 ? 0 : 32;
-#pragma unroll
-    for (int cc = 0; cc < 32; cc += 16) {
+    const int col0 = 16 * part;
+    {
       float vv[16];
-      tmem_ld16(tU + lane_off + col0 + cc, vv);
+      tmem_ld16(tU + lane_off + col0, vv);
       tmem_ld_wait();
-      if (valid && a.dv) {
+      if (valid && a.dv_part) {
+        float* dst = a.dv_part + ((size_t)(b * a.Hq + blockIdx.y) * a.N + jglob) * VD + col0;
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const size_t o = (koff + jglob) * VD + col0 + cc + x;
-          float val = vv[x];
-          if (a.dv_init) val += a.dv_init[o];
-          reinterpret_cast<__nv_bfloat16*>(a.dv)[o] = __float2bfloat16_rn(val);
-        }
+        for (int x4 = 0; x4 < 16; x4 += 4)
+          *reinterpret_cast<float4*>(dst + x4) = make_float4(vv[x4], vv[x4 + 1], vv[x4 + 2], vv[x4 + 3]);
       }
-    }
-    if (valid && a.dk && a.dk_acc) {
-      const size_t o = (koff + jglob) * HD + 32 * half;
-#pragma unroll
-      for (int x = 0; x < 32; ++x) reinterpret_cast<__nv_bfloat16*>(a.dk)[o + x] = __float2bfloat16_rn(a.dk_acc[o + x]);
     }
   }
   fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
   if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
+}
+
+// dk / dv = cross-chunk part + sum over the query heads of the KV head of the per-head shares,
+// fixed order, cast to bf16.  One thread per 4 consecutive dims of one key token.
+__global__ void __launch_bounds__(256) kv_head_reduce_kernel(const float* part, const float* cross,
+                                                            __nv_bfloat16* out, int B, int Hq, int Hkv, int N) {
+  const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;       // over B*Hkv*N*16
+  const size_t total = (size_t)B * Hkv * N * 16;
+  if (idx >= total) return;
+  const int d4 = (int)(idx & 15);
+  const size_t tok = idx >> 4;                                     // (b*Hkv + kvh)*N + n
+  const int n = (int)(tok % N);
+  const size_t bk = tok / N;
+  const int kvh = (int)(bk % Hkv), b = (int)(bk / Hkv), rep = Hq / Hkv;
+  float4 acc = cross ? *reinterpret_cast<const float4*>(cross + tok * HD + 4 * d4) : make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < rep; ++r) {
+    const float4 t = *reinterpret_cast<const float4*>(part + (((size_t)b * Hq + kvh * rep + r) * N + n) * HD + 4 * d4);
+    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+  }
+  *reinterpret_cast<uint2*>(out + tok * HD + 4 * d4) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
 }
 
 }  // namespace
@@ -510,24 +538,31 @@ cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const 
   a.dq = dq; a.dq_init = dq_init; a.coef_partial = coef_partial; a.status = status;
   a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv; a.G = G; a.scale = scale;
   a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
-  intra_bwd_q_kernel<<<dim3(NB, Hq, B), 256, BQ_SMEM, st>>>(a);
+  intra_bwd_q_kernel<<<dim3(NB, Hq, B), BT, BQ_SMEM, st>>>(a);
   return cudaGetLastError();
 }
 
 cudaError_t intra_backward_kv(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
                               const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dk,
-                              void* dv, float* dk_acc, const float* dv_init, int32_t* status, int B, int Hq, int Hkv,
-                              int N, int NB, int G, float scale, cudaStream_t st) {
+                              void* dv, const float* dk_cross, const float* dv_cross, float* dk_part, float* dv_part,
+                              int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G, float scale,
+                              cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(intra_bwd_kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BKV_SMEM);
   if (e != cudaSuccess) return e;
   IntraBwdArgs a{};
   a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
   a.v = static_cast<const __nv_bfloat16*>(v); a.gimg = static_cast<const __nv_bfloat16*>(gimg);
   a.dim_perm = dim_perm; a.group_start = group_start; a.A = A; a.Bc = Bc; a.Cc = Cc;
-  a.dk = dk; a.dv = dv; a.dk_acc = dk_acc; a.dv_init = dv_init; a.status = status;
+  a.dk_part = dk ? dk_part : nullptr; a.dv_part = dv ? dv_part : nullptr; a.status = status;
   a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv; a.G = G; a.scale = scale;
   a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
-  intra_bwd_kv_kernel<<<dim3(NB, Hkv, B), 256, BKV_SMEM, st>>>(a);
+  intra_bwd_kv_kernel<<<dim3(NB, Hq, B), BT, BKV_SMEM, st>>>(a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const size_t total = (size_t)B * Hkv * N * 16;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dk) kv_head_reduce_kernel<<<blocks, 256, 0, st>>>(dk_part, dk_cross, static_cast<__nv_bfloat16*>(dk), B, Hq, Hkv, N);
+  if (dv) kv_head_reduce_kernel<<<blocks, 256, 0, st>>>(dv_part, dv_cross, static_cast<__nv_bfloat16*>(dv), B, Hq, Hkv, N);
   return cudaGetLastError();
 }
 

@@ -81,7 +81,8 @@ cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const 
                              int N, int NB, int G, float scale, cudaStream_t st);
 cudaError_t intra_backward_kv(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
                               const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dk,
-                              void* dv, float* dk_acc, const float* dv_init, int32_t* status, int B, int Hq, int Hkv,
-                              int N, int NB, int G, float scale, cudaStream_t st);
+                              void* dv, const float* dk_cross, const float* dv_cross, float* dk_part, float* dv_part,
+                              int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G, float scale,
+                              cudaStream_t st);
 
 }  // namespace oal

@@ -65,7 +65,7 @@ struct StateUpdateArgs {
   int32_t* status;
 };
 
-__global__ void __launch_bounds__(GEN_THREADS, 1) state_update_kernel(const StateUpdateArgs a) {
+__global__ void __launch_bounds__(GEN_THREADS, 2) state_update_kernel(const StateUpdateArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Abuf = smem;                          // 2 x SLAB_A_BYTES
   unsigned char* Uimg = smem + 2 * SLAB_A_BYTES;       // [10][128 tokens][8 e]
