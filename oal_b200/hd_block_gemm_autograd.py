@@ -74,10 +74,7 @@ def _pad_last(t: torch.Tensor) -> torch.Tensor:
     return t if d == _lib.HEAD_DIM else F.pad(t, (0, _lib.HEAD_DIM - d)).contiguous()
 
 
-def raise_on_status(status: torch.Tensor) -> None:
-    """One host synchronisation at the point where the reference synchronises
-    (oal_attention/hd_block_gemm_runtime.py:392-408)."""
-    bits = int(status.item())
+def _raise_for_bits(bits: int) -> None:
     if bits & _lib.STATUS_WAIT_TIMEOUT:
         raise RuntimeError(f"oal_b200 kernel gave up on a bounded wait (device status word {bits:#x})")
     if bits & _lib.STATUS_BAD_LAYOUT:
@@ -86,11 +83,49 @@ def raise_on_status(status: torch.Tensor) -> None:
         raise RuntimeError(f"{_DENOMINATOR_ERROR} (device status {bits})")
 
 
+def raise_on_status(status: torch.Tensor) -> None:
+    """One host synchronisation at the point where the reference synchronises
+    (oal_attention/hd_block_gemm_runtime.py:392-408)."""
+    _raise_for_bits(int(status.item()))
+
+
+# Deferred status words.  The reference synchronises after every forward because "a device-side
+# assertion can poison a CUDA context ... until a safe asynchronous status mechanism is available"
+# (hd_block_gemm_runtime.py:395-398).  The status word is that mechanism: when autograd will run a
+# backward anyway, the forward only queues an asynchronous copy of its status word to pinned host
+# memory; it is examined (without blocking unless asked) when the backward starts, at the next call
+# of the operator, or by ``check_pending_status(block=True)``.  Forward-only calls stay eager.
+_PENDING: list = []
+
+
+def defer_status(status: torch.Tensor) -> None:
+    host = torch.empty(1, dtype=torch.int32, pin_memory=True)
+    host.copy_(status, non_blocking=True)
+    event = torch.cuda.Event()
+    event.record(torch.cuda.current_stream(status.device))
+    _PENDING.append((host, event))
+
+
+def check_pending_status(block: bool = False) -> None:
+    """Raise for any finished call whose device status word reported a problem."""
+    while _PENDING:
+        host, event = _PENDING[0]
+        if not block and not event.query():
+            return
+        if block:
+            event.synchronize()
+        _PENDING.pop(0)
+        _raise_for_bits(int(host[0]))
+
+
 def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: float,
                  plan: HDParallelBlockPlan, *, state_in=None, check=True):
-    """Launch the forward kernels.  Returns (out, num, den[B,Hq,N,1], saved_state, padded q,k,v)."""
+    """Launch the forward kernels.  Returns (out, num, den[B,Hq,N,1], saved_state, padded q,k,v).
+
+    ``check``: True = synchronise and raise on the status word now; "defer" = queue it."""
     if q.device.type != "cuda":
         raise RuntimeError("oal_b200 runs on CUDA tensors only (there is no CPU path)")
+    check_pending_status()
     lib = _lib.load()
     B, Hq, Hkv, N, D, Dv = plan.geometry
     qp, kp, vp = _pad_last(q), _pad_last(k), _pad_last(v)
@@ -114,7 +149,9 @@ def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: flo
                          _lib.ptr(saved), _lib.ptr(state_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status),
                          _stream_ptr(dev))
     _lib.check(rc)
-    if check:
+    if check == "defer":
+        defer_status(status)
+    elif check:
         raise_on_status(status)
     if Dv != _lib.HEAD_DIM:
         out, num = out[..., :Dv].contiguous(), num[..., :Dv].contiguous()
@@ -131,6 +168,7 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
     ``workspace`` / ``reuse_state_stage``: sequence parallelism passes the workspace that
     ``oal_backward_local_state`` has just filled so that stage is not computed twice."""
     lib = _lib.load()
+    check_pending_status()
     qp, kp, vp, a32, b32, c32 = saved_inputs
     B, Hq, Hkv, N, D, Dv = plan.geometry
     dev = qp.device
@@ -172,7 +210,7 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
                           _lib.ptr(dstate_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status), _stream_ptr(dev))
     _lib.check(rc)
     if plan.precision == "bf16_tensorcore":
-        raise_on_status(status)      # only a bounded wait that gave up can set it here
+        defer_status(status)         # only a bounded wait that gave up can set it here
     if D != _lib.HEAD_DIM:
         dq = None if dq is None else dq[..., :D].contiguous()
         dk = None if dk is None else dk[..., :D].contiguous()
@@ -191,7 +229,8 @@ class _HDParallelBlockGemmFunction(torch.autograd.Function):
         if plan.requested_gradient_mask != mask:
             raise ValueError("plan gradient mask must exactly match the six tensor inputs")
         ctx.set_materialize_grads(False)
-        out, num, den, saved_state, padded = forward_impl(q, k, v, a, b, c, tables, scale, eps, plan)
+        out, num, den, saved_state, padded = forward_impl(q, k, v, a, b, c, tables, scale, eps, plan,
+                                                          check="defer" if any(mask) else True)
         ctx.tables, ctx.scale, ctx.eps, ctx.plan, ctx.mask = tables, float(scale), float(eps), plan, mask
         ctx.input_dtypes = tuple(t.dtype for t in (q, k, v, a, b, c))
         ctx.has_state = saved_state is not None

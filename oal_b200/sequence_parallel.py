@@ -99,7 +99,8 @@ class _SequenceParallelFunction(torch.autograd.Function):
         ctx.set_materialize_grads(False)
         state_in = exclusive_prefix_over_ranks(local_state_total(k, v, plan), group)
         out, num, den, saved_state, padded = forward_impl(q, k, v, a, b, c, prepared.tables, prepared.scale,
-                                                          prepared.normalization_floor, plan, state_in=state_in)
+                                                          prepared.normalization_floor, plan, state_in=state_in,
+                                                          check="defer" if any(mask) else True)
         ctx.prepared, ctx.group, ctx.mask, ctx.reduce_coef = prepared, group, mask, reduce_coef
         ctx.input_dtypes = tuple(t.dtype for t in (q, k, v, a, b, c))
         if any(mask):

@@ -180,3 +180,20 @@ def test_qwen_n4096_rows_against_reference_golden(golden, precision, tol):
     ((fa * ref["dA"]).sum() + (fb * ref["dB"]).sum() + (fc * ref["dC"]).sum()).backward()
     ref["dfactor"] = factor.grad
     assert_close(rows, ref, tol, keys=["out", "num", "den", "dq", "dk", "dv", "dfactor"], label=precision)
+
+
+def test_deferred_status_surfaces_at_backward_or_explicit_check():
+    """With autograd active the forward does not synchronise: a bad denominator is reported when the
+    status word is examined (explicit blocking check here)."""
+    import oal_b200
+
+    case = synthetic.qwen_head_case(2, batch=1, n=40, hq=2, hkv=1, g=4, bf16=False)
+    q, k, v, groups = (t.cuda() for t in (case.q, case.k, case.v, case.dim_groups))
+    q.requires_grad_()
+    a = torch.full((2,), -1e6, device="cuda")
+    zb, zc = torch.zeros(2, 4, device="cuda"), torch.zeros(2, 4, 4, device="cuda")
+    oal_b200.check_pending_status(block=True)
+    oal_b200.grouped_coefficient_attention(q, k, v, groups, a, zb, zc, scale=case.scale)   # queued, no raise
+    with pytest.raises(RuntimeError, match="denominator must be finite and strictly positive"):
+        oal_b200.check_pending_status(block=True)
+    oal_b200.check_pending_status(block=True)        # queue is drained: nothing left to report
