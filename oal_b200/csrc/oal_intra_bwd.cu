@@ -6,7 +6,9 @@
 //   dq~ += ds_g K_g          (query side)                      MMAs, accumulators in tensor memory
 //   dk~ += ds_g^T Q_g, dU += W^T G   (key/value side, summed over the query heads of the KV head)
 // plus the coefficient partial sums dA, dB_g, dC_gg' (query side, per-thread accumulators and a
-// fixed-order block reduction).  The cross-chunk parts computed by the state kernels arrive as
+// fixed-order block reduction).  Sixteen compute warps (128 rows x 4 column parts) never meet at a
+// block-wide barrier inside the tile loop: a seventeenth warp issues all MMAs and is driven by
+// warp-granular mbarrier arrivals (scores read, ds tiles written); tcgen05.commit signals back.  The cross-chunk parts computed by the state kernels arrive as
 // fp32 buffers and are added before the final cast.  Reference stages replaced:
 // oal_attention/hd_block_gemm_backward_wave.py:253-476 (dS, local dphi_q / dphi_k / dU GEMMs) and the
 // folds / coefficient partials of oal_attention/hd_block_gemm_feature_backward.py:59-474.
@@ -21,8 +23,17 @@ using namespace umma;
 constexpr int IMG_BYTES = (DP_MAX / 8) * CT * 16;        // 45056
 constexpr int TILE_BYTES = (KT / 8) * CT * 16;           // 4096: bf16 [2][128 rows][8]
 constexpr int NTRI = IG * (IG + 1) / 2;
-constexpr int BT = 512;                 // threads per CTA: 128 rows x 4 column parts
+constexpr int BT = 512;                 // compute threads per CTA: 128 rows x 4 column parts
+constexpr int BT_ALL = BT + 32;         // plus one warp whose lane 0 issues every MMA
+constexpr int CWARPS = BT / 32;         // compute warps: arrival count of the warp-level barriers
 constexpr int CW = KT / (BT / CT);      // columns of a tile handled by one thread (4)
+
+// One arrival per warp on an mbarrier after every lane has finished what precedes (shared-memory
+// stores made visible to the async proxy, or tensor-memory loads).
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
 
 // 8 bytes (4 bf16) of a [2][128 rows][8] tile image: columns 4*part .. 4*part+3 of `row`
 __device__ __forceinline__ void store_tile4(unsigned char* tile, int part, int row, const float (&t)[4]) {
@@ -58,7 +69,7 @@ struct PairOut {
 // ---------------------------------------------------------------------------
 constexpr int BQ_SMEM = 2 * IMG_BYTES + 3 * SLAB_S_BYTES + 2 * IG * TILE_BYTES;
 
-__global__ void __launch_bounds__(BT, 1) intra_bwd_q_kernel(const IntraBwdArgs a) {
+__global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Qimg = smem;
   unsigned char* Kimg = Qimg + IMG_BYTES;
@@ -66,23 +77,27 @@ __global__ void __launch_bounds__(BT, 1) intra_bwd_q_kernel(const IntraBwdArgs a
   unsigned char* Gimg = Uimg + SLAB_S_BYTES;               // hi image, lo image
   unsigned char* DS = Gimg + 2 * SLAB_S_BYTES;            // [2][IG][TILE_BYTES]
   __shared__ PaddedGroups pg;
-  __shared__ uint64_t s_done, ds_done[2], gfull;
+  __shared__ uint64_t s_done, s_free, ds_ready[2], ds_done[2], gfull;
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (a.Hq / a.Hkv);
-  const int part = warp >> 2, row = 32 * (warp & 3) + lane;
+  const int part = (warp >> 2) & 3, row = 32 * (warp & 3) + lane;
+  const bool issuer = warp == CWARPS;
   if (warp == 0) tmem_alloc(&tmem_base, 512);
   if (tid == 0) {
     mbar_init(&s_done, 1);
+    mbar_init(&s_free, CWARPS);
+    mbar_init(&ds_ready[0], CWARPS);
+    mbar_init(&ds_ready[1], CWARPS);
     mbar_init(&ds_done[0], 1);
     mbar_init(&ds_done[1], 1);
     mbar_init(&gfull, 1);
     mbar_fence_init();
     dead = 0;
   }
-  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, BT);
+  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, BT_ALL);
   const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
   if (tid == 0) {
     const unsigned char* gsrc =
@@ -92,9 +107,9 @@ __global__ void __launch_bounds__(BT, 1) intra_bwd_q_kernel(const IntraBwdArgs a
     bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
   }
   // the ds tile buffers are idle during set-up: use them as the staging area of the image builds
-  build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, BT);
-  build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, BT);
-  for (int idx = tid; idx < (EP / 8) * CT; idx += BT) {
+  build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, BT_ALL);
+  build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, BT_ALL);
+  for (int idx = tid; idx < (EP / 8) * CT; idx += BT_ALL) {
     const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
     reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
   }
@@ -105,282 +120,55 @@ __global__ void __launch_bounds__(BT, 1) intra_bwd_q_kernel(const IntraBwdArgs a
   Waiter w{&dead};
   const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tQ = tmem_base + IG * KT + KT;
   const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
-  const uint32_t q_addr = smem_u32(Qimg), k_addr = smem_u32(Kimg), u_addr = smem_u32(Uimg), g_addr = smem_u32(Gimg);
-  const uint32_t idesc16 = instr_desc_bf16(128, KT, 0, 0);
-  const uint32_t idesc_dq = instr_desc_bf16(128, 16, 0, 1);
   const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
-
-  auto issue_scores = [&](int kt) {
-    issue_group_scores(tS, q_addr, k_addr, kt * KT, pg);
-#pragma unroll
-    for (int ks = 0; ks < 2 * (EP / 16); ++ks) {       // G = hi + lo: the K extent is walked twice
-      const int part = ks / (EP / 16), kk = ks % (EP / 16);
-      mma_bf16_ss(tW, smem_desc(g_addr + part * SLAB_S_BYTES + kk * 4096, CT * 16, 128),
-                  smem_desc(u_addr + kk * 4096 + kt * KT * 16, CT * 16, 128), idesc16, ks > 0);
-    }
-    mma_commit(&s_done);
-  };
-  if (tid == 0) {
-    w.wait(&gfull, 0, 0x20);
-    fence_after_sync();
-    issue_scores(0);
-  }
   float cA = 0.f, cB[IG], cC[NTRI];
 #pragma unroll
   for (int g = 0; g < IG; ++g) cB[g] = 0.f;
 #pragma unroll
   for (int x = 0; x < NTRI; ++x) cC[x] = 0.f;
 
-  for (int kt = 0; kt < tiles; ++kt) {
-    const int buf = kt & 1;
-    float s[IG][CW], dw[CW];
-    w.wait(&s_done, kt & 1, 0x21);
-    fence_after_sync();
+  if (issuer) {
+    if (lane == 0) {
+      const uint32_t q_addr = smem_u32(Qimg), k_addr = smem_u32(Kimg), u_addr = smem_u32(Uimg), g_addr = smem_u32(Gimg);
+      const uint32_t idesc16 = instr_desc_bf16(128, KT, 0, 0);
+      const uint32_t idesc_dq = instr_desc_bf16(128, 16, 0, 1);
+      auto issue_scores = [&](int kt) {
+        issue_group_scores(tS, q_addr, k_addr, kt * KT, pg);
 #pragma unroll
-    for (int g = 0; g < IG; ++g) {
-      if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld4(tS + lane_off + g * KT + CW * part, s[g]);
-      else {
-#pragma unroll
-        for (int x = 0; x < CW; ++x) s[g][x] = 0.f;
-      }
-    }
-    tmem_ld4(tW + lane_off + CW * part, dw);
-    tmem_ld_wait();
-    fence_before_sync();
-    __syncthreads();
-    if (tid == 0 && kt + 1 < tiles) {
-      fence_after_sync();
-      issue_scores(kt + 1);
-    }
-    const bool warp_active = 32 * (warp & 3) + 31 >= kt * KT;
-    if (kt >= 2) w.wait(&ds_done[buf], ((kt - 2) >> 1) & 1, 0x22);
-    unsigned char* dsb = DS + buf * IG * TILE_BYTES;
-    if (warp_active) {
-#pragma unroll
-      for (int x = 0; x < CW; ++x) {
-        if (kt * KT + CW * part + x > row) dw[x] = 0.f;
-        cA += dw[x];
-      }
-#pragma unroll
-      for (int g = 0; g < IG; ++g)
-#pragma unroll
-        for (int x = 0; x < CW; ++x) s[g][x] *= a.scale;
-#pragma unroll
-      for (int g = 0; g < IG; ++g) {
-        float t[CW];
-        const float bg = pg.B[g];
-#pragma unroll
-        for (int x = 0; x < CW; ++x) t[x] = bg;
-#pragma unroll
-        for (int g2 = 0; g2 < IG; ++g2) {
-          const float c2 = 2.f * pg.C[g * IG + g2];
-#pragma unroll
-          for (int x = 0; x < CW; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+        for (int ks = 0; ks < 2 * (EP / 16); ++ks) {       // G = hi + lo: the K extent is walked twice
+          const int gp = ks / (EP / 16), kk = ks % (EP / 16);
+          mma_bf16_ss(tW, smem_desc(g_addr + gp * SLAB_S_BYTES + kk * 4096, CT * 16, 128),
+                      smem_desc(u_addr + kk * 4096 + kt * KT * 16, CT * 16, 128), idesc16, ks > 0);
         }
-#pragma unroll
-        for (int x = 0; x < CW; ++x) t[x] *= dw[x];
-        store_tile4(dsb + g * TILE_BYTES, part, row, t);
-      }
-      int idx = 0;
-#pragma unroll
-      for (int g = 0; g < IG; ++g) {
-        float ws[CW];
-#pragma unroll
-        for (int x = 0; x < CW; ++x) {
-          ws[x] = dw[x] * s[g][x];
-          cB[g] += ws[x];
-        }
-#pragma unroll
-        for (int g2 = g; g2 < IG; ++g2) {
-#pragma unroll
-          for (int x = 0; x < CW; ++x) cC[idx] = fmaf(ws[x], s[g2][x], cC[idx]);
-          ++idx;
-        }
-      }
-    } else {
-      const float zero[CW] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int g = 0; g < IG; ++g) store_tile4(dsb + g * TILE_BYTES, part, row, zero);
-    }
-    fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      fence_after_sync();
-      const uint32_t ds_addr = smem_u32(dsb);
-#pragma unroll 1
-      for (int g = 0; g < IG; ++g)
-        for (int k16 = pg.k16_start[g]; k16 < pg.k16_start[g + 1]; ++k16)
-          mma_bf16_ss(tQ + k16 * 16, smem_desc(ds_addr + g * TILE_BYTES, CT * 16, 128),
-                      smem_desc(k_addr + k16 * 4096 + kt * KT * 16, 128, CT * 16), idesc_dq, kt > 0);
-      mma_commit(&ds_done[buf]);
-    }
-  }
-  if (tiles >= 2) w.wait(&ds_done[(tiles - 2) & 1], ((tiles - 2) >> 1) & 1, 0x23);
-  w.wait(&ds_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, 0x24);
-  fence_after_sync();
-  // dq~ (padded, group-sorted columns) -> dq
-  if (a.dq) {
-    const int i = c * CT + row;
-    const int nslab = pg.k16_start[IG];
-    for (int k16 = part; k16 < nslab; k16 += BT / CT) {
-      float vv[16];
-      tmem_ld16(tQ + lane_off + k16 * 16, vv);
-      tmem_ld_wait();
-      if (i < a.N && !dead) {
-#pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const int src = pg.src[k16 * 16 + x];
-          if (src >= 0) {
-            const size_t o = (qoff + i) * HD + src;
-            float val = a.scale * vv[x];
-            if (a.dq_init) val += a.dq_init[o];
-            reinterpret_cast<__nv_bfloat16*>(a.dq)[o] = __float2bfloat16_rn(val);
-          }
-        }
-      }
-    }
-  }
-  fence_before_sync();
-  __syncthreads();
-  if (a.coef_partial) {
-    float* red = reinterpret_cast<float*>(DS);      // the ds tiles are idle now: [16 warps][NCOEF]
-    auto wsum = [](float v) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      return v;
-    };
-    for (int x = lane; x < NCOEF; x += 32) red[warp * NCOEF + x] = 0.f;
-    __syncwarp();
-    float v = wsum(cA);
-    if (lane == 0) red[warp * NCOEF + 0] = v;
-#pragma unroll
-    for (int g = 0; g < IG; ++g) {
-      v = wsum(cB[g]);
-      if (lane == 0) red[warp * NCOEF + 1 + g] = v;
-    }
-    int idx = 0;
-#pragma unroll
-    for (int g = 0; g < IG; ++g)
-#pragma unroll
-      for (int g2 = g; g2 < IG; ++g2) {
-        v = wsum(cC[idx]);
-        if (lane == 0) red[warp * NCOEF + 1 + GMAX + tri8(g, g2)] = v;
-        ++idx;
-      }
-    __syncthreads();
-    float* dst = a.coef_partial + ((size_t)(b * a.Hq + h) * a.NB + c) * NCOEF;
-    for (int x = tid; x < NCOEF; x += BT) {
-      float t = 0.f;
-#pragma unroll
-      for (int ww = 0; ww < BT / 32; ++ww) t += red[ww * NCOEF + x];
-      dst[x] = t;
-    }
-  }
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, 512);
-  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
-}
-
-// ---------------------------------------------------------------------------
-// key / value side
-// ---------------------------------------------------------------------------
-constexpr int BKV_SMEM = 2 * IMG_BYTES + 3 * SLAB_S_BYTES + 2 * IG * TILE_BYTES + 2 * TILE_BYTES;
-
-__global__ void __launch_bounds__(BT, 1) intra_bwd_kv_kernel(const IntraBwdArgs a) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* Kimg = smem;
-  unsigned char* Qimg = Kimg + IMG_BYTES;
-  unsigned char* Uimg = Qimg + IMG_BYTES;
-  unsigned char* Gimg = Uimg + SLAB_S_BYTES;               // hi image, lo image
-  unsigned char* DS = Gimg + 2 * SLAB_S_BYTES;             // [2][IG][TILE_BYTES]
-  unsigned char* WT = DS + 2 * IG * TILE_BYTES;            // [2][TILE_BYTES]
-  __shared__ PaddedGroups pg;
-  __shared__ uint64_t s_done, ds_done[2], gfull;
-  __shared__ uint32_t tmem_base;
-  __shared__ int dead;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // one CTA per (chunk, query head, batch row): the per-head shares are summed over the query heads
-  // of a KV head afterwards, in fixed order, by kv_head_reduce_kernel
-  const int c = blockIdx.x, b = blockIdx.z;
-  const int rep = 1, kvh = blockIdx.y / (a.Hq / a.Hkv);
-  const int part = warp >> 2, row = 32 * (warp & 3) + lane;     // row = key index inside the chunk
-  if (warp == 0) tmem_alloc(&tmem_base, 512);
-  if (tid == 0) {
-    mbar_init(&s_done, 1);
-    mbar_init(&ds_done[0], 1);
-    mbar_init(&ds_done[1], 1);
-    mbar_init(&gfull, 1);
-    mbar_fence_init();
-    dead = 0;
-  }
-  const size_t koff = (size_t)(b * a.Hkv + kvh) * a.N;
-  for (int idx = tid; idx < (EP / 8) * CT; idx += BT) {
-    const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
-    reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
-  }
-  fence_async_smem();
-  fence_before_sync();
-  __syncthreads();
-  fence_after_sync();
-  Waiter w{&dead};
-  const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tK = tmem_base + IG * KT + KT, tU = tK + DP_MAX;
-  const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
-  const uint32_t q_addr = smem_u32(Qimg), k_addr = smem_u32(Kimg), u_addr = smem_u32(Uimg), g_addr = smem_u32(Gimg);
-  const uint32_t idesc16 = instr_desc_bf16(128, KT, 0, 0);
-  const uint32_t idesc_dk = instr_desc_bf16(128, 16, 0, 1);
-  const uint32_t idesc_du = instr_desc_bf16(128, EP, 0, 1);
-  const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
-  const int jglob = c * CT + row;
-  int nt = 0;                                   // tiles issued so far over all heads
-
-  for (int hh = 0; hh < rep; ++hh) {
-    const int h = blockIdx.y + hh;
-    const size_t qoff = (size_t)(b * a.Hq + h) * a.N;
-    // every MMA of the previous head has completed (waited at its end): the images may be rebuilt
-    if (tid == 0) {
-      const unsigned char* gsrc =
-          reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.Hq + h) * a.NB + c) * SLAB_S_BYTES;
-      mbar_arrive_expect_tx(&gfull, 2 * SLAB_S_BYTES);
-      bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, &gfull);
-      bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
-    }
-    // the K image depends only on the head's group layout: keep it when the layout repeats
-    bool same_layout = hh > 0;
-    if (hh > 0) {
-      for (int x = tid; x < HD + GMAX + 1; x += BT) {
-        const bool eq = x < HD ? a.dim_perm[h * HD + x] == a.dim_perm[(h - 1) * HD + x]
-                               : a.group_start[h * (GMAX + 1) + x - HD] == a.group_start[(h - 1) * (GMAX + 1) + x - HD];
-        if (!eq) same_layout = false;
-      }
-    }
-    same_layout = __syncthreads_and(same_layout);
-    load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, BT);
-    // every MMA that read the ds tiles has completed: they double as staging area of the image builds
-    if (!same_layout)
-      build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, BT);
-    build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, BT);
-    fence_async_smem();
-    __syncthreads();
-
-    auto issue_scores = [&](int qt) {
-      issue_group_scores(tS, k_addr, q_addr, qt * KT, pg);         // S^T: key rows x 16 queries
-#pragma unroll
-      for (int ks = 0; ks < 2 * (EP / 16); ++ks) {     // G = hi + lo
-        const int part = ks / (EP / 16), kk = ks % (EP / 16);
-        mma_bf16_ss(tW, smem_desc(u_addr + kk * 4096, CT * 16, 128),
-                    smem_desc(g_addr + part * SLAB_S_BYTES + kk * 4096 + qt * KT * 16, CT * 16, 128), idesc16, ks > 0);
-      }
-      mma_commit(&s_done);
-    };
-    if (tid == 0) {
-      w.wait(&gfull, hh & 1, 0x30);
+        mma_commit(&s_done);
+      };
+      w.wait(&gfull, 0, 0x20);
       fence_after_sync();
       issue_scores(0);
+      for (int kt = 0; kt < tiles; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < tiles) {
+          w.wait(&s_free, kt & 1, 0x25);            // every compute warp holds the scores of tile kt
+          fence_after_sync();
+          issue_scores(kt + 1);
+        }
+        w.wait(&ds_ready[buf], (kt >> 1) & 1, 0x26);  // ds tiles of tile kt are in shared memory
+        fence_after_sync();
+        const uint32_t ds_addr = smem_u32(DS + buf * IG * TILE_BYTES);
+#pragma unroll 1
+        for (int g = 0; g < IG; ++g)
+          for (int k16 = pg.k16_start[g]; k16 < pg.k16_start[g + 1]; ++k16)
+            mma_bf16_ss(tQ + k16 * 16, smem_desc(ds_addr + g * TILE_BYTES, CT * 16, 128),
+                        smem_desc(k_addr + k16 * 4096 + kt * KT * 16, 128, CT * 16), idesc_dq, kt > 0);
+        mma_commit(&ds_done[buf]);
+      }
     }
-    for (int qt = 0; qt < tiles; ++qt, ++nt) {
-      const int buf = nt & 1;
+    __syncwarp();
+  } else {
+    for (int kt = 0; kt < tiles; ++kt) {
+      const int buf = kt & 1;
       float s[IG][CW], dw[CW];
-      w.wait(&s_done, nt & 1, 0x31);
+      w.wait(&s_done, kt & 1, 0x21);
       fence_after_sync();
 #pragma unroll
       for (int g = 0; g < IG; ++g) {
@@ -393,14 +181,250 @@ __global__ void __launch_bounds__(BT, 1) intra_bwd_kv_kernel(const IntraBwdArgs 
       tmem_ld4(tW + lane_off + CW * part, dw);
       tmem_ld_wait();
       fence_before_sync();
-      __syncthreads();
-      if (tid == 0 && qt + 1 < tiles) {
-        fence_after_sync();
-        issue_scores(qt + 1);
+      warp_arrive(&s_free, lane);
+      const bool warp_active = 32 * (warp & 3) + 31 >= kt * KT;
+      if (kt >= 2) w.wait(&ds_done[buf], ((kt - 2) >> 1) & 1, 0x22);
+      unsigned char* dsb = DS + buf * IG * TILE_BYTES;
+      if (warp_active) {
+#pragma unroll
+        for (int x = 0; x < CW; ++x) {
+          if (kt * KT + CW * part + x > row) dw[x] = 0.f;
+          cA += dw[x];
+        }
+#pragma unroll
+        for (int g = 0; g < IG; ++g)
+#pragma unroll
+          for (int x = 0; x < CW; ++x) s[g][x] *= a.scale;
+#pragma unroll
+        for (int g = 0; g < IG; ++g) {
+          float t[CW];
+          const float bg = pg.B[g];
+#pragma unroll
+          for (int x = 0; x < CW; ++x) t[x] = bg;
+#pragma unroll
+          for (int g2 = 0; g2 < IG; ++g2) {
+            const float c2 = 2.f * pg.C[g * IG + g2];
+#pragma unroll
+            for (int x = 0; x < CW; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+          }
+#pragma unroll
+          for (int x = 0; x < CW; ++x) t[x] *= dw[x];
+          store_tile4(dsb + g * TILE_BYTES, part, row, t);
+        }
+        int idx = 0;
+#pragma unroll
+        for (int g = 0; g < IG; ++g) {
+          float ws[CW];
+#pragma unroll
+          for (int x = 0; x < CW; ++x) {
+            ws[x] = dw[x] * s[g][x];
+            cB[g] += ws[x];
+          }
+#pragma unroll
+          for (int g2 = g; g2 < IG; ++g2) {
+#pragma unroll
+            for (int x = 0; x < CW; ++x) cC[idx] = fmaf(ws[x], s[g2][x], cC[idx]);
+            ++idx;
+          }
+        }
+      } else {
+        const float zero[CW] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int g = 0; g < IG; ++g) store_tile4(dsb + g * TILE_BYTES, part, row, zero);
       }
+      fence_async_smem();
+      warp_arrive(&ds_ready[buf], lane);
+    }
+    if (tiles >= 2) w.wait(&ds_done[(tiles - 2) & 1], ((tiles - 2) >> 1) & 1, 0x23);
+    w.wait(&ds_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, 0x24);
+    fence_after_sync();
+    // dq~ (padded, group-sorted columns) -> dq
+    if (a.dq) {
+      const int i = c * CT + row;
+      const int nslab = pg.k16_start[IG];
+      for (int k16 = part; k16 < nslab; k16 += BT / CT) {
+        float vv[16];
+        tmem_ld16(tQ + lane_off + k16 * 16, vv);
+        tmem_ld_wait();
+        if (i < a.N && !dead) {
+#pragma unroll
+          for (int x = 0; x < 16; ++x) {
+            const int src = pg.src[k16 * 16 + x];
+            if (src >= 0) {
+              const size_t o = (qoff + i) * HD + src;
+              float val = a.scale * vv[x];
+              if (a.dq_init) val += a.dq_init[o];
+              reinterpret_cast<__nv_bfloat16*>(a.dq)[o] = __float2bfloat16_rn(val);
+            }
+          }
+        }
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (a.coef_partial) {
+    float* red = reinterpret_cast<float*>(DS);      // the ds tiles are idle now: [16 warps][NCOEF]
+    if (!issuer) {
+      auto wsum = [](float v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        return v;
+      };
+      for (int x = lane; x < NCOEF; x += 32) red[warp * NCOEF + x] = 0.f;
+      __syncwarp();
+      float v = wsum(cA);
+      if (lane == 0) red[warp * NCOEF + 0] = v;
+#pragma unroll
+      for (int g = 0; g < IG; ++g) {
+        v = wsum(cB[g]);
+        if (lane == 0) red[warp * NCOEF + 1 + g] = v;
+      }
+      int idx = 0;
+#pragma unroll
+      for (int g = 0; g < IG; ++g)
+#pragma unroll
+        for (int g2 = g; g2 < IG; ++g2) {
+          v = wsum(cC[idx]);
+          if (lane == 0) red[warp * NCOEF + 1 + GMAX + tri8(g, g2)] = v;
+          ++idx;
+        }
+    }
+    __syncthreads();
+    float* dst = a.coef_partial + ((size_t)(b * a.Hq + h) * a.NB + c) * NCOEF;
+    for (int x = tid; x < NCOEF; x += BT_ALL) {
+      float t = 0.f;
+#pragma unroll
+      for (int ww = 0; ww < CWARPS; ++ww) t += red[ww * NCOEF + x];
+      dst[x] = t;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 512);
+  if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
+}
+
+// ---------------------------------------------------------------------------
+// key / value side: one CTA per (chunk, query head, batch row); the per-head shares of dk and dv are
+// summed over the query heads of a KV head afterwards, in fixed order, by kv_head_reduce_kernel
+// ---------------------------------------------------------------------------
+constexpr int BKV_SMEM = 2 * IMG_BYTES + 3 * SLAB_S_BYTES + 2 * IG * TILE_BYTES + 2 * TILE_BYTES;
+
+__global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* Kimg = smem;
+  unsigned char* Qimg = Kimg + IMG_BYTES;
+  unsigned char* Uimg = Qimg + IMG_BYTES;
+  unsigned char* Gimg = Uimg + SLAB_S_BYTES;               // hi image, lo image
+  unsigned char* DS = Gimg + 2 * SLAB_S_BYTES;             // [2][IG][TILE_BYTES]
+  unsigned char* WT = DS + 2 * IG * TILE_BYTES;            // [2][TILE_BYTES]
+  __shared__ PaddedGroups pg;
+  __shared__ uint64_t s_done, s_free, ds_ready[2], ds_done[2], gfull;
+  __shared__ uint32_t tmem_base;
+  __shared__ int dead;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (a.Hq / a.Hkv);
+  const int part = (warp >> 2) & 3, row = 32 * (warp & 3) + lane;     // row = key index inside the chunk
+  const bool issuer = warp == CWARPS;
+  if (warp == 0) tmem_alloc(&tmem_base, 512);
+  if (tid == 0) {
+    mbar_init(&s_done, 1);
+    mbar_init(&s_free, CWARPS);
+    mbar_init(&ds_ready[0], CWARPS);
+    mbar_init(&ds_ready[1], CWARPS);
+    mbar_init(&ds_done[0], 1);
+    mbar_init(&ds_done[1], 1);
+    mbar_init(&gfull, 1);
+    mbar_fence_init();
+    dead = 0;
+  }
+  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, BT_ALL);
+  const size_t koff = (size_t)(b * a.Hkv + kvh) * a.N, qoff = (size_t)(b * a.Hq + h) * a.N;
+  if (tid == 0) {
+    const unsigned char* gsrc =
+        reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.Hq + h) * a.NB + c) * SLAB_S_BYTES;
+    mbar_arrive_expect_tx(&gfull, 2 * SLAB_S_BYTES);
+    bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, &gfull);
+    bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
+  }
+  build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, BT_ALL);
+  build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, BT_ALL);
+  for (int idx = tid; idx < (EP / 8) * CT; idx += BT_ALL) {
+    const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
+    reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
+  }
+  fence_async_smem();
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  Waiter w{&dead};
+  const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tK = tmem_base + IG * KT + KT, tU = tK + DP_MAX;
+  const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+  const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
+  const int jglob = c * CT + row;
+
+  if (issuer) {
+    if (lane == 0) {
+      const uint32_t q_addr = smem_u32(Qimg), k_addr = smem_u32(Kimg), u_addr = smem_u32(Uimg), g_addr = smem_u32(Gimg);
+      const uint32_t idesc16 = instr_desc_bf16(128, KT, 0, 0);
+      const uint32_t idesc_dk = instr_desc_bf16(128, 16, 0, 1);
+      const uint32_t idesc_du = instr_desc_bf16(128, EP, 0, 1);
+      auto issue_scores = [&](int qt) {
+        issue_group_scores(tS, k_addr, q_addr, qt * KT, pg);         // S^T: key rows x 16 queries
+#pragma unroll
+        for (int ks = 0; ks < 2 * (EP / 16); ++ks) {     // G = hi + lo
+          const int gp = ks / (EP / 16), kk = ks % (EP / 16);
+          mma_bf16_ss(tW, smem_desc(u_addr + kk * 4096, CT * 16, 128),
+                      smem_desc(g_addr + gp * SLAB_S_BYTES + kk * 4096 + qt * KT * 16, CT * 16, 128), idesc16, ks > 0);
+        }
+        mma_commit(&s_done);
+      };
+      w.wait(&gfull, 0, 0x30);
+      fence_after_sync();
+      issue_scores(0);
+      for (int qt = 0; qt < tiles; ++qt) {
+        const int buf = qt & 1;
+        if (qt + 1 < tiles) {
+          w.wait(&s_free, qt & 1, 0x35);
+          fence_after_sync();
+          issue_scores(qt + 1);
+        }
+        w.wait(&ds_ready[buf], (qt >> 1) & 1, 0x36);
+        fence_after_sync();
+        const uint32_t ds_addr = smem_u32(DS + buf * IG * TILE_BYTES);
+#pragma unroll 1
+        for (int g = 0; g < IG; ++g)
+          for (int k16 = pg.k16_start[g]; k16 < pg.k16_start[g + 1]; ++k16)
+            mma_bf16_ss(tK + k16 * 16, smem_desc(ds_addr + g * TILE_BYTES, CT * 16, 128),
+                        smem_desc(q_addr + k16 * 4096 + qt * KT * 16, 128, CT * 16), idesc_dk, qt > 0);
+        mma_bf16_ss(tU, smem_desc(smem_u32(WT + buf * TILE_BYTES), CT * 16, 128),
+                    smem_desc(g_addr + qt * KT * 16, 128, CT * 16), idesc_du, qt > 0);
+        mma_commit(&ds_done[buf]);
+      }
+    }
+    __syncwarp();
+  } else {
+    for (int qt = 0; qt < tiles; ++qt) {
+      const int buf = qt & 1;
+      float s[IG][CW], dw[CW];
+      w.wait(&s_done, qt & 1, 0x31);
+      fence_after_sync();
+#pragma unroll
+      for (int g = 0; g < IG; ++g) {
+        if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld4(tS + lane_off + g * KT + CW * part, s[g]);
+        else {
+#pragma unroll
+          for (int x = 0; x < CW; ++x) s[g][x] = 0.f;
+        }
+      }
+      tmem_ld4(tW + lane_off + CW * part, dw);
+      tmem_ld_wait();
+      fence_before_sync();
+      warp_arrive(&s_free, lane);
       // keys of this warp are all later than the tile's queries -> nothing survives the mask
       const bool warp_active = 32 * (warp & 3) <= qt * KT + KT - 1;
-      if (nt >= 2) w.wait(&ds_done[buf], ((nt - 2) >> 1) & 1, 0x32);
+      if (qt >= 2) w.wait(&ds_done[buf], ((qt - 2) >> 1) & 1, 0x32);
       unsigned char* dsb = DS + buf * IG * TILE_BYTES;
       float wv[CW];
       if (warp_active) {
@@ -443,54 +467,33 @@ __global__ void __launch_bounds__(BT, 1) intra_bwd_kv_kernel(const IntraBwdArgs 
       }
       store_tile4(WT + buf * TILE_BYTES, part, row, wv);
       fence_async_smem();
-      __syncthreads();
-      if (tid == 0) {
-        fence_after_sync();
-        const uint32_t ds_addr = smem_u32(dsb);
-#pragma unroll 1
-        for (int g = 0; g < IG; ++g)
-          for (int k16 = pg.k16_start[g]; k16 < pg.k16_start[g + 1]; ++k16)
-            mma_bf16_ss(tK + k16 * 16, smem_desc(ds_addr + g * TILE_BYTES, CT * 16, 128),
-                        smem_desc(q_addr + k16 * 4096 + qt * KT * 16, 128, CT * 16), idesc_dk, qt > 0);
-        mma_bf16_ss(tU, smem_desc(smem_u32(WT + buf * TILE_BYTES), CT * 16, 128),
-                    smem_desc(g_addr + qt * KT * 16, 128, CT * 16), idesc_du, nt > 0);
-        mma_commit(&ds_done[buf]);
-      }
+      warp_arrive(&ds_ready[buf], lane);
     }
-    // end of head: wait for its last MMAs, fold dk~ into the fp32 accumulator (original dim order)
-    if (nt >= 2) w.wait(&ds_done[(nt - 2) & 1], ((nt - 2) >> 1) & 1, 0x33);
-    w.wait(&ds_done[(nt - 1) & 1], ((nt - 1) >> 1) & 1, 0x34);
+    if (tiles >= 2) w.wait(&ds_done[(tiles - 2) & 1], ((tiles - 2) >> 1) & 1, 0x33);
+    w.wait(&ds_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, 0x34);
     fence_after_sync();
-    if (a.dk_part) {
-      const int nslab = pg.k16_start[IG];
-      for (int k16 = part; k16 < nslab; k16 += BT / CT) {
-        float vv[16];
-        tmem_ld16(tK + lane_off + k16 * 16, vv);
-        tmem_ld_wait();
-        if (jglob < a.N && !dead) {
+    // tensor-memory loads are warp-collective: every thread executes them, only the stores are guarded
+    const bool valid = jglob < a.N && !dead;
+    const int nslab = pg.k16_start[IG];
+    for (int k16 = part; k16 < nslab; k16 += BT / CT) {
+      float vv[16];
+      tmem_ld16(tK + lane_off + k16 * 16, vv);
+      tmem_ld_wait();
+      if (valid && a.dk_part) {
 #pragma unroll
-          for (int x = 0; x < 16; ++x) {
-            const int src = pg.src[k16 * 16 + x];
-            if (src >= 0) a.dk_part[(qoff + jglob) * HD + src] = a.scale * vv[x];   // Q image holds unscaled q
-          }
+        for (int x = 0; x < 16; ++x) {
+          const int src = pg.src[k16 * 16 + x];
+          if (src >= 0) a.dk_part[(qoff + jglob) * HD + src] = a.scale * vv[x];   // Q image holds unscaled q
         }
       }
     }
-    fence_before_sync();
-    __syncthreads();
-  }
-  // outputs
-  fence_after_sync();
-  {
-    // tensor-memory loads are warp-collective: every thread executes them, only the stores are guarded
-    const bool valid = jglob < a.N && !dead;
-    const int col0 = 16 * part;
     {
+      const int col0 = 16 * part;
       float vv[16];
       tmem_ld16(tU + lane_off + col0, vv);
       tmem_ld_wait();
       if (valid && a.dv_part) {
-        float* dst = a.dv_part + ((size_t)(b * a.Hq + blockIdx.y) * a.N + jglob) * VD + col0;
+        float* dst = a.dv_part + (qoff + jglob) * VD + col0;
 #pragma unroll
         for (int x4 = 0; x4 < 16; x4 += 4)
           *reinterpret_cast<float4*>(dst + x4) = make_float4(vv[x4], vv[x4 + 1], vv[x4 + 2], vv[x4 + 3]);
@@ -538,7 +541,7 @@ cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const 
   a.dq = dq; a.dq_init = dq_init; a.coef_partial = coef_partial; a.status = status;
   a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv; a.G = G; a.scale = scale;
   a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
-  intra_bwd_q_kernel<<<dim3(NB, Hq, B), BT, BQ_SMEM, st>>>(a);
+  intra_bwd_q_kernel<<<dim3(NB, Hq, B), BT_ALL, BQ_SMEM, st>>>(a);
   return cudaGetLastError();
 }
 
@@ -556,7 +559,7 @@ cudaError_t intra_backward_kv(const void* q, const void* k, const void* v, const
   a.dk_part = dk ? dk_part : nullptr; a.dv_part = dv ? dv_part : nullptr; a.status = status;
   a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv; a.G = G; a.scale = scale;
   a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
-  intra_bwd_kv_kernel<<<dim3(NB, Hq, B), BT, BKV_SMEM, st>>>(a);
+  intra_bwd_kv_kernel<<<dim3(NB, Hq, B), BT_ALL, BKV_SMEM, st>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const size_t total = (size_t)B * Hkv * N * 16;
