@@ -19,9 +19,11 @@ namespace {
 
 using namespace umma;
 
-// five slab groups (4,4,3,3,3): four 80-column accumulators plus two Z buffers fit in 512 columns
-__device__ __forceinline__ int hgroup_first(int g) { return g < 2 ? 4 * g : 8 + 3 * (g - 2); }   // 0,4,8,11,14
-__device__ __forceinline__ int hgroup_count(int g) { return g < 2 ? 4 : 3; }
+// nine slab groups (2,...,2,1): two 80-column accumulators plus one Z buffer fit in 256 columns, so two
+// CTAs share an SM and fill each other's gaps
+constexpr int HGROUPS = 9;
+__device__ __forceinline__ int hgroup_first(int g) { return 2 * g; }
+__device__ __forceinline__ int hgroup_count(int g) { return g < 8 ? 2 : 1; }
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4 t, float (&o)[8]) {
   const uint32_t w[4] = {t.x, t.y, t.z, t.w};
@@ -48,7 +50,7 @@ struct DStateArgs {
   int32_t* status;
 };
 
-__global__ void __launch_bounds__(GEN_THREADS, 1) dstate_heads_kernel(const DStateArgs a) {
+__global__ void __launch_bounds__(GEN_THREADS, 2) dstate_heads_kernel(const DStateArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Abuf = smem;                        // 2 x SLAB_A_BYTES
   unsigned char* Gbuf = smem + 2 * SLAB_A_BYTES;     // 2 x SLAB_S_BYTES  ([10][128 tokens][8 e])
@@ -60,7 +62,7 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) dstate_heads_kernel(const DSta
   const int grp = blockIdx.x, c = blockIdx.y, u = blockIdx.z;
   const int b = u / a.Hkv, kvh = u % a.Hkv, rep = a.Hq / a.Hkv;
   const int token = tid & 127, half = tid >> 7, wg = warp >> 2;
-  if (warp == 0) tmem_alloc(&tmem_base, 512);
+  if (warp == 0) tmem_alloc(&tmem_base, 256);
   if (tid == 0) {
     mbar_init(&mma_done[0], 1);
     mbar_init(&mma_done[1], 1);
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) dstate_heads_kernel(const DSta
   Waiter w{&dead};
   const int s0 = hgroup_first(grp), ns = hgroup_count(grp);
   const uint32_t tacc = tmem_base;                 // ns x 80 columns
-  const uint32_t tz = tmem_base + 320;             // 2 x 80 columns
+  const uint32_t tz = tmem_base + 160;             // 80 columns
   const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
   const uint32_t idesc = instr_desc_bf16(128, EP, 1, 1);
   const int fr = 32 * (warp & 3) + lane;
@@ -103,7 +105,7 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) dstate_heads_kernel(const DSta
       float dot = 0.f;
       for (int cc = 0; cc < ncol; cc += 16) {
         float z[16];
-        tmem_ld16(tz + (m & 1) * EP + lane_off + col0 + cc, z);
+        tmem_ld16(tz + lane_off + col0 + cc, z);
         float acc[16];
         if (hm > 0) tmem_ld16(tacc + im * EP + lane_off + col0 + cc, acc);
         tmem_ld_wait();
@@ -140,6 +142,13 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) dstate_heads_kernel(const DSta
     for (int it = 0; it < ns; ++it, ++n) {
       const int buf = n & 1;
       write_half_slab<false>(s0 + it, half, x, nullptr, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES), token);
+      // the single Z buffer must be drained before the next MMA is issued
+      if (n >= 1) epilogue(n - 1);
+      // every MMA of the previous head has completed: its G buffer can take the next head's image
+      if (it == 0 && tid == 0 && hh + 1 < rep) {
+        mbar_arrive_expect_tx(&gfull[(hh + 1) & 1], SLAB_S_BYTES);
+        bulk_g2s(Gbuf + ((hh + 1) & 1) * SLAB_S_BYTES, gimg_ptr(h + 1), SLAB_S_BYTES, &gfull[(hh + 1) & 1]);
+      }
       fence_async_smem();
       __syncthreads();
       if (tid == 0) {
@@ -149,15 +158,9 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) dstate_heads_kernel(const DSta
         const uint32_t g_addr = smem_u32(Gbuf + (hh & 1) * SLAB_S_BYTES);
 #pragma unroll
         for (int ks = 0; ks < CT / 16; ++ks)
-          mma_bf16_ss(tz + buf * EP, smem_desc(a_addr + ks * 256, 128, CT * 16),
-                      smem_desc(g_addr + ks * 256, 128, CT * 16), idesc, ks > 0);
+          mma_bf16_ss(tz, smem_desc(a_addr + ks * 256, 128, CT * 16), smem_desc(g_addr + ks * 256, 128, CT * 16),
+                      idesc, ks > 0);
         mma_commit(&mma_done[buf]);
-      }
-      if (n >= 1) epilogue(n - 1);
-      // every MMA of the previous head has completed: its G buffer can take the next head's image
-      if (it == 0 && tid == 0 && hh + 1 < rep) {
-        mbar_arrive_expect_tx(&gfull[(hh + 1) & 1], SLAB_S_BYTES);
-        bulk_g2s(Gbuf + ((hh + 1) & 1) * SLAB_S_BYTES, gimg_ptr(h + 1), SLAB_S_BYTES, &gfull[(hh + 1) & 1]);
       }
     }
   }
@@ -179,7 +182,7 @@ __global__ void __launch_bounds__(GEN_THREADS, 1) dstate_heads_kernel(const DSta
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, 512);
+  if (warp == 0) tmem_dealloc(tmem_base, 256);
   if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
@@ -507,7 +510,7 @@ cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img,
   DStateArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(gimg),
                static_cast<const __nv_bfloat16*>(carry_img), coef_table, dcarry, dcoef_partial, N, NB, Hq, Hkv,
                scale, status};
-  dstate_heads_kernel<<<dim3(5, NB, B * Hkv), GEN_THREADS, smem, st>>>(a);
+  dstate_heads_kernel<<<dim3(HGROUPS, NB, B * Hkv), GEN_THREADS, smem, st>>>(a);
   return cudaGetLastError();
 }
 

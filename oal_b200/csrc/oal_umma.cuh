@@ -149,8 +149,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // OAL_STATUS_WAIT_TIMEOUT and leaves its loops; it never spins forever.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   const uint32_t addr = smem_u32(bar);
-  const long long t0 = clock64();
-  for (;;) {
+  long long t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
@@ -162,7 +162,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
-    if (clock64() - t0 > 50000000LL) return false;
+    // back off so that waiting warps do not take issue slots from working ones; look at the clock
+    // only now and then
+    __nanosleep(64);
+    if ((spin & 15) == 0) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > 50000000LL) return false;
+    }
   }
 }
 
