@@ -266,7 +266,9 @@ def run_gpu_arm(args) -> None:
         fpt = flop_per_token(w["hq"], w["hkv"], 64)
         f, e = 1 + D + D * (D + 1) // 2, D + 1
         tok = w["batch"] * w["n"]
-        # algorithmic FLOPs of each kernel per launch (unpadded F = 2145, E = 65)
+        # algorithmic FLOPs of each kernel per launch (unpadded F = 2145, E = 65; causal half, chunk 64
+        # in the intra-chunk terms, exactly the terms of flop_per_token)
+        intra = w["hq"] * (D + e) * 65 * tok
         kernel_flops = {
             "state_update": w["hkv"] * 2 * f * e * tok,
             "cross_read_q": w["hq"] * 2 * f * e * tok,
@@ -274,20 +276,30 @@ def run_gpu_arm(args) -> None:
             "feature_grad_q": w["hq"] * 2 * f * e * tok,
             "feature_grad_k": w["hkv"] * 2 * f * e * tok,
             "cross_read_k": w["hkv"] * 2 * f * e * tok,
+            "intra_forward": intra,            # s and W [v|1]
+            "intra_backward_q": intra,         # dW and dq
+            "intra_backward_kv": intra,        # dk and dv
         }
         kernels = {name: dict(launches=cnt, ms_per_launch=ms / max(cnt, 1), share=None)
                    for name, (cnt, ms) in report.items()}
         tot = sum(ms for _, ms in report.values()) or 1.0
         for name, (cnt, ms) in report.items():
             kernels[name]["share"] = round(ms / tot, 4)
+            if name in kernel_flops:
+                kernels[name]["tflops"] = round(kernel_flops[name] / (ms / max(cnt, 1) * 1e-3) / 1e12, 2)
         tc = {n_: k_ for n_, k_ in kernels.items() if n_ in kernel_flops}
         roofline = None
         if tc:
+            # the dominant kernel by device time
             top = max(tc, key=lambda n_: tc[n_]["ms_per_launch"] * tc[n_]["launches"])
             achieved = kernel_flops[top] / (tc[top]["ms_per_launch"] * 1e-3) / 1e12
+            best = max(tc, key=lambda n_: tc[n_]["tflops"])
             roofline = dict(bound="tensor", kernel=top, achieved=round(achieved, 2), peak=peaks["tflops"],
                             unit="TFLOP/s", frac=round(achieved / peaks["tflops"], 4), traffic=None,
                             peak_source=peaks["source"] + " (sustained bf16)",
+                            note="algorithmic MMA FLOPs of the kernel / its mean launch time; the intra-chunk "
+                                 "kernels spend their time in the fp32 combine on the CUDA cores",
+                            best_kernel=best, best_kernel_frac=round(tc[best]["tflops"] / peaks["tflops"], 4),
                             whole_step_frac=round(value * fpt / 1e12 / peaks["tflops"], 4))
         cpu = cpu_reference_run(2, 1) if world >= 1 and not args.no_cpu_baseline else None
         line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps,

@@ -1,0 +1,119 @@
+"""Secondary measurements of the operator (the headline number lives in bench.py at the repo root).
+
+    python -m oal_b200.benchmarks sweep [--seq 1024,4096,16384,65536] [--groups 1,4,8,16]
+        forward+backward time per token over sequence length and group count (B=1, 14 query /
+        2 KV heads, d=64, bf16): time per token must stay flat in N, and the G axis shows what the
+        per-group padding of the intra-chunk GEMMs costs.
+    torchrun --nproc-per-node P -m oal_b200.benchmarks sp [--seq 32768]
+        sequence-parallel forward+backward: the sequence is cut into P contiguous ranges, one
+        all-gather of the range-final states per direction (NCCL).
+
+Each measurement prints one JSON line (rank 0).  Inputs are the seeded synthetic tensors of
+``oal_b200.synthetic``.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import _lib, synthetic
+from .hd_block_gemm_adapters import prepare_grouped_hd_block_gemm, run_prepared_grouped_hd_block_gemm
+from .hd_block_gemm_autograd import check_pending_status
+
+
+def _time_steps(step, steps: int, warmup: int) -> float:
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    check_pending_status(block=True)
+    return e0.elapsed_time(e1) / steps
+
+
+def sweep(ns, gs, steps: int, warmup: int) -> None:
+    dev = torch.device("cuda", 0)
+    for g in gs:
+        for n in ns:
+            case = synthetic.qwen_head_case(7, batch=1, n=n, hq=14, hkv=2, g=g, bf16=True)
+            q, k, v, dout = (t.to(dev, torch.bfloat16) for t in (case.q, case.k, case.v, case.grad_out))
+            groups, factor = case.dim_groups.to(dev), case.factor.to(dev).requires_grad_()
+            q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+            prepared = prepare_grouped_hd_block_gemm(q, k, v, groups, factor, scale=case.scale,
+                                                     precision="bf16_tensorcore")
+
+            def step():
+                q.grad = k.grad = v.grad = factor.grad = None
+                out, _, _ = run_prepared_grouped_hd_block_gemm(prepared, q, k, v, factor)
+                out.backward(dout)
+
+            ms = _time_steps(step, steps, warmup)
+            print(json.dumps(dict(benchmark="sweep", n=n, groups=g, ms_per_step=ms, ns_per_token=ms * 1e6 / n,
+                                  tokens_per_s=n / (ms * 1e-3),
+                                  intra_chunk="tcgen05" if g <= 8 else "token-pair kernels")), flush=True)
+            del q, k, v, dout, prepared
+            torch.cuda.empty_cache()
+
+
+def sequence_parallel(n: int, steps: int, warmup: int) -> None:
+    import torch.distributed as dist
+
+    from .sequence_parallel import sequence_parallel_attention
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    case = synthetic.qwen_head_case(3, batch=1, n=n, hq=14, hkv=2, g=8, bf16=True)
+    sl = slice(rank * n // world, (rank + 1) * n // world)
+    q, k, v, dout = (t[:, :, sl].to(dev, torch.bfloat16).contiguous() for t in (case.q, case.k, case.v, case.grad_out))
+    groups, factor = case.dim_groups.to(dev), case.factor.to(dev).requires_grad_()
+    q.requires_grad_(), k.requires_grad_(), v.requires_grad_()
+    prepared = prepare_grouped_hd_block_gemm(q, k, v, groups, factor, scale=case.scale, precision="bf16_tensorcore")
+
+    def step():
+        q.grad = k.grad = v.grad = factor.grad = None
+        out, _, _ = sequence_parallel_attention(q, k, v, groups, factor, scale=case.scale, prepared=prepared)
+        out.backward(dout)
+
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([_time_steps(step, steps, warmup)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps(dict(benchmark="sequence_parallel", n=n, ranks=world, ms_per_step=ms.item(),
+                              tokens_per_s=n / (ms.item() * 1e-3),
+                              exchange_bytes_per_rank_per_direction=2 * _lib.STATE_ROWS * _lib.E_PAD * 4)), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("mode", choices=["sweep", "sp"])
+    ap.add_argument("--seq", default=None, help="sequence length(s), comma separated")
+    ap.add_argument("--groups", default="1,4,8,16")
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    if a.mode == "sweep":
+        ns = [int(x) for x in (a.seq or "1024,4096,16384,65536").split(",")]
+        sweep(ns, [int(x) for x in a.groups.split(",")], a.steps, a.warmup)
+    else:
+        sequence_parallel(int(a.seq or 32768), a.steps, a.warmup)
+
+
+if __name__ == "__main__":
+    main()

@@ -111,23 +111,31 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
     float wv[8];
     const bool warp_active = 32 * (warp & 3) + 31 >= kt * KT;
     if (warp_active) {
+      // packed pairs of columns (2j, 2j+1)
+      f32x2 s2[IG][4], w2[4];
 #pragma unroll
-      for (int x = 0; x < 8; ++x) wv[x] = pg.A;
+      for (int g = 0; g < IG; ++g)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s2[g][j] = f2_pack(s[g][2 * j], s[g][2 * j + 1]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w2[j] = f2_bcast(pg.A);
 #pragma unroll
       for (int g = 0; g < IG; ++g) {
-        float t[8];
-        const float bg = pg.B[g], cgg = pg.C[g * IG + g];
+        f32x2 t[4];
+        const f32x2 bg = f2_bcast(pg.B[g]), cgg = f2_bcast(pg.C[g * IG + g]);
 #pragma unroll
-        for (int x = 0; x < 8; ++x) t[x] = fmaf(cgg, s[g][x], bg);
+        for (int j = 0; j < 4; ++j) t[j] = f2_fma(cgg, s2[g][j], bg);
 #pragma unroll
         for (int g2 = 0; g2 < g; ++g2) {
-          const float c2 = 2.f * pg.C[g * IG + g2];
+          const f32x2 c2 = f2_bcast(2.f * pg.C[g * IG + g2]);
 #pragma unroll
-          for (int x = 0; x < 8; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+          for (int j = 0; j < 4; ++j) t[j] = f2_fma(c2, s2[g2][j], t[j]);
         }
 #pragma unroll
-        for (int x = 0; x < 8; ++x) wv[x] = fmaf(s[g][x], t[x], wv[x]);
+        for (int j = 0; j < 4; ++j) w2[j] = f2_fma(s2[g][j], t[j], w2[j]);
       }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) f2_unpack(w2[j], wv[2 * j], wv[2 * j + 1]);
 #pragma unroll
       for (int x = 0; x < 8; ++x)
         if (kt * KT + 8 * half + x > row) wv[x] = 0.f;

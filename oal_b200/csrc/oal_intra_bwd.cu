@@ -191,24 +191,31 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
           if (kt * KT + CW * part + x > row) dw[x] = 0.f;
           cA += dw[x];
         }
-#pragma unroll
-        for (int g = 0; g < IG; ++g)
-#pragma unroll
-          for (int x = 0; x < CW; ++x) s[g][x] *= a.scale;
+        // packed pairs of columns: (0,1) and (2,3)
+        f32x2 s2[IG][2];
+        const f32x2 sc2 = f2_bcast(a.scale);
+        const f32x2 dw2[2] = {f2_pack(dw[0], dw[1]), f2_pack(dw[2], dw[3])};
 #pragma unroll
         for (int g = 0; g < IG; ++g) {
-          float t[CW];
-          const float bg = pg.B[g];
+          s2[g][0] = f2_mul(f2_pack(s[g][0], s[g][1]), sc2);
+          s2[g][1] = f2_mul(f2_pack(s[g][2], s[g][3]), sc2);
+          f2_unpack(s2[g][0], s[g][0], s[g][1]);
+          f2_unpack(s2[g][1], s[g][2], s[g][3]);
+        }
 #pragma unroll
-          for (int x = 0; x < CW; ++x) t[x] = bg;
+        for (int g = 0; g < IG; ++g) {
+          f32x2 t0 = f2_bcast(pg.B[g]), t1 = t0;
 #pragma unroll
           for (int g2 = 0; g2 < IG; ++g2) {
-            const float c2 = 2.f * pg.C[g * IG + g2];
-#pragma unroll
-            for (int x = 0; x < CW; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+            const f32x2 c2 = f2_bcast(2.f * pg.C[g * IG + g2]);
+            t0 = f2_fma(c2, s2[g2][0], t0);
+            t1 = f2_fma(c2, s2[g2][1], t1);
           }
-#pragma unroll
-          for (int x = 0; x < CW; ++x) t[x] *= dw[x];
+          t0 = f2_mul(t0, dw2[0]);
+          t1 = f2_mul(t1, dw2[1]);
+          float t[CW];
+          f2_unpack(t0, t[0], t[1]);
+          f2_unpack(t1, t[2], t[3]);
           store_tile4(dsb + g * TILE_BYTES, part, row, t);
         }
         int idx = 0;
@@ -433,29 +440,38 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
           wv[x] = pg.A;
           if (qt * KT + CW * part + x < row) dw[x] = 0.f;          // query earlier than the key
         }
-#pragma unroll
-        for (int g = 0; g < IG; ++g)
-#pragma unroll
-          for (int x = 0; x < CW; ++x) s[g][x] *= a.scale;
+        // packed pairs of columns: (0,1) and (2,3)
+        f32x2 s2[IG][2];
+        const f32x2 sc2 = f2_bcast(a.scale), two2 = f2_bcast(2.f);
+        const f32x2 dw2[2] = {f2_pack(dw[0], dw[1]), f2_pack(dw[2], dw[3])};
+        f32x2 w0 = f2_bcast(pg.A), w1 = w0;
 #pragma unroll
         for (int g = 0; g < IG; ++g) {
-          float t[CW];
+          s2[g][0] = f2_mul(f2_pack(s[g][0], s[g][1]), sc2);
+          s2[g][1] = f2_mul(f2_pack(s[g][2], s[g][3]), sc2);
+        }
 #pragma unroll
-          for (int x = 0; x < CW; ++x) t[x] = 0.f;
+        for (int g = 0; g < IG; ++g) {
+          f32x2 t0 = f2_bcast(0.f), t1 = t0;
 #pragma unroll
           for (int g2 = 0; g2 < IG; ++g2) {
-            const float c2 = pg.C[g * IG + g2];
-#pragma unroll
-            for (int x = 0; x < CW; ++x) t[x] = fmaf(c2, s[g2][x], t[x]);
+            const f32x2 c2 = f2_bcast(pg.C[g * IG + g2]);
+            t0 = f2_fma(c2, s2[g2][0], t0);
+            t1 = f2_fma(c2, s2[g2][1], t1);
           }
-          const float bg = pg.B[g];
-#pragma unroll
-          for (int x = 0; x < CW; ++x) {
-            wv[x] = fmaf(s[g][x], bg + t[x], wv[x]);
-            t[x] = dw[x] * (bg + 2.f * t[x]);
-          }
+          const f32x2 bg = f2_bcast(pg.B[g]);
+          // w += s_g (B_g + t);  ds_g = dw (B_g + 2 t)
+          w0 = f2_fma(s2[g][0], f2_fma(t0, f2_bcast(1.f), bg), w0);
+          w1 = f2_fma(s2[g][1], f2_fma(t1, f2_bcast(1.f), bg), w1);
+          t0 = f2_mul(dw2[0], f2_fma(two2, t0, bg));
+          t1 = f2_mul(dw2[1], f2_fma(two2, t1, bg));
+          float t[CW];
+          f2_unpack(t0, t[0], t[1]);
+          f2_unpack(t1, t[2], t[3]);
           store_tile4(dsb + g * TILE_BYTES, part, row, t);
         }
+        f2_unpack(w0, wv[0], wv[1]);
+        f2_unpack(w1, wv[2], wv[3]);
 #pragma unroll
         for (int x = 0; x < CW; ++x)
           if (qt * KT + CW * part + x < row) wv[x] = 0.f;
