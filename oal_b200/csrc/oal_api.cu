@@ -315,7 +315,7 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
   if (p->groups <= 8) {
     { LaunchScope scope("intra_forward", st);
-      e = oal::intra_forward(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
+      e = (p->groups <= 4 ? oal::intra_forward_g4 : oal::intra_forward)(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
                              p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor, st); }
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
     return OAL_OK;
@@ -408,7 +408,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     }
     if (tc_intra) {
       { LaunchScope scope("intra_backward_q", st);
-        e = oal::intra_backward_q(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_q ? dq : nullptr,
+        e = (p->groups <= 4 ? oal::intra_backward_q_g4 : oal::intra_backward_q)(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_q ? dq : nullptr,
                                   want_q ? s.dq_cross : nullptr, want_c ? s.coef_pairs : nullptr, status, p->batch,
                                   p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->scale, st); }
       if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward query-side kernel");
@@ -444,7 +444,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     }
     if (tc_intra) {
       { LaunchScope scope("intra_backward_kv", st, 1 + (want_k ? 1 : 0) + (want_v ? 1 : 0));
-        e = oal::intra_backward_kv(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_k ? dk : nullptr,
+        e = (p->groups <= 4 ? oal::intra_backward_kv_g4 : oal::intra_backward_kv)(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_k ? dk : nullptr,
                                    want_v ? dv : nullptr, want_k ? s.dk_cross : nullptr, want_v ? s.dv_cross : nullptr,
                                    s.dk_part, s.dv_part, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
                                    p->groups, p->scale, st); }
@@ -585,7 +585,7 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
   if (p->groups <= 8) {
     { LaunchScope scope("intra_forward", st);
-      e = oal::intra_forward(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
+      e = (p->groups <= 4 ? oal::intra_forward_g4 : oal::intra_forward)(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
                              p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor, st); }
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
     return OAL_OK;

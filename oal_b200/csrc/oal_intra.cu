@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
 
 }  // namespace
 
-cudaError_t intra_forward(const void* q, const void* k, const void* v, const int32_t* dim_perm,
+cudaError_t OAL_INTRA_NAME(intra_forward)(const void* q, const void* k, const void* v, const int32_t* dim_perm,
                           const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* out,
                           float* num, float* den, int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G,
                           int out_dt, int slabs, float scale, float floor_v, cudaStream_t st) {

@@ -7,9 +7,17 @@
 
 namespace oal {
 
-constexpr int KT = 16;            // keys (or queries) per tile of the intra-chunk kernels
-constexpr int DP_MAX = 176;       // padded dims: 64 + 7 * 16 rounded to 16 (at most 8 groups)
-constexpr int IG = 8;             // groups handled by the tensor-core intra-chunk kernels
+// The intra-chunk kernels are compiled twice: for up to 8 groups per head (default) and, with
+// OAL_IG = 4, for up to 4 groups (the per-pair combine is quadratic in the compiled group bound).
+#ifndef OAL_IG
+#define OAL_IG 8
+#endif
+#ifndef OAL_INTRA_NAME
+#define OAL_INTRA_NAME(name) name
+#endif
+constexpr int KT = 16;                       // keys (or queries) per tile of the intra-chunk kernels
+constexpr int IG = OAL_IG;                   // groups handled by this build of the kernels
+constexpr int DP_MAX = 64 + (IG - 1) * 16;   // padded dims: every group rounded up to 16 (176 for 8 groups)
 
 // Padded, group-sorted dimension layout of one head.
 struct PaddedGroups {

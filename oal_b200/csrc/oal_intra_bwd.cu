@@ -544,7 +544,7 @@ __global__ void __launch_bounds__(256) kv_head_reduce_kernel(const float* part, 
 
 }  // namespace
 
-cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
+cudaError_t OAL_INTRA_NAME(intra_backward_q)(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
                              const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dq,
                              const float* dq_init, float* coef_partial, int32_t* status, int B, int Hq, int Hkv,
                              int N, int NB, int G, float scale, cudaStream_t st) {
@@ -561,7 +561,7 @@ cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const 
   return cudaGetLastError();
 }
 
-cudaError_t intra_backward_kv(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
+cudaError_t OAL_INTRA_NAME(intra_backward_kv)(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
                               const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dk,
                               void* dv, const float* dk_cross, const float* dv_cross, float* dk_part, float* dv_part,
                               int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G, float scale,

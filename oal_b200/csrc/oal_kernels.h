@@ -85,4 +85,19 @@ cudaError_t intra_backward_kv(const void* q, const void* k, const void* v, const
                               int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G, float scale,
                               cudaStream_t st);
 
+// the same kernels compiled for at most 4 groups per head
+cudaError_t intra_forward_g4(const void* q, const void* k, const void* v, const int32_t* dim_perm,
+                          const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* out,
+                          float* num, float* den, int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G,
+                          int out_dt, int slabs, float scale, float floor_v, cudaStream_t st);
+cudaError_t intra_backward_q_g4(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
+                             const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dq,
+                             const float* dq_init, float* coef_partial, int32_t* status, int B, int Hq, int Hkv,
+                             int N, int NB, int G, float scale, cudaStream_t st);
+cudaError_t intra_backward_kv_g4(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
+                              const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dk,
+                              void* dv, const float* dk_cross, const float* dv_cross, float* dk_part, float* dv_part,
+                              int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G, float scale,
+                              cudaStream_t st);
+
 }  // namespace oal
