@@ -132,6 +132,27 @@ def cpu_reference_run(steps: int, warmup: int) -> dict:
                        f"best of {steps} after {warmup} warm-up")
 
 
+def cpu_config1_run() -> dict:
+    """BASELINE config 1 exactly as specified, on the CPU: cumulative-state statement + autograd, fp32,
+    B=1, Hq=Hkv=2, N=256, d=64, G=4 (the reference oracle's algorithm)."""
+    from oal_b200 import synthetic
+    from oracle import oal_oracle as orc
+
+    case = synthetic.config1_case(0)
+    best = None
+    for it in range(3):
+        q, k, v = (t.clone().requires_grad_() for t in (case.q, case.k, case.v))
+        a, b, c = (t.clone().requires_grad_() for t in (case.A, case.B, case.C))
+        t0 = time.perf_counter()
+        out, _, _ = orc.state_forward(q, k, v, case.dim_groups, a, b, c, scale=case.scale)
+        out.backward(case.grad_out)
+        dt = time.perf_counter() - t0
+        if it > 0:
+            best = dt if best is None else min(best, dt)
+    return dict(value=256 / best, unit="tokens/s", seconds=best, cores=torch.get_num_threads(),
+                sample="config 1 (B=1, H=2, N=256, G=4), cumulative-state statement + autograd, fp32, best of 2 after 1 warm-up")
+
+
 def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -332,6 +353,7 @@ def run_gpu_arm(args) -> None:
         if cpu:
             line["cpu_baseline"] = dict(value=cpu["tokens_per_s"], unit="tokens/s", cores=cpu["threads"],
                                         kind="port", sample=cpu["sample"])
+            line["cpu_baseline_config1"] = cpu_config1_run()
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

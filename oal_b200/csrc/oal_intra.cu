@@ -197,10 +197,18 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
         const float n0 = y[x4] + o.x, n1 = y[x4 + 1] + o.y, n2 = y[x4 + 2] + o.z, n3 = y[x4 + 3] + o.w;
         *reinterpret_cast<float4*>(np) = make_float4(n0, n1, n2, n3);
         if (!(finite_f(n0) && finite_f(n1) && finite_f(n2) && finite_f(n3))) flags |= OAL_STATUS_NONFINITE;
-        store_elem(a.out, orow * VD + col0 + x4, a.out_dt, n0 / dn);
-        store_elem(a.out, orow * VD + col0 + x4 + 1, a.out_dt, n1 / dn);
-        store_elem(a.out, orow * VD + col0 + x4 + 2, a.out_dt, n2 / dn);
-        store_elem(a.out, orow * VD + col0 + x4 + 3, a.out_dt, n3 / dn);
+        const size_t oo = orow * VD + col0 + x4;          // four consecutive outputs, one vector store
+        if (a.out_dt == OAL_DTYPE_BF16) {
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + oo) =
+              make_uint2(pack_bf16(n0 / dn, n1 / dn), pack_bf16(n2 / dn, n3 / dn));
+        } else if (a.out_dt == OAL_DTYPE_F32) {
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + oo) = make_float4(n0 / dn, n1 / dn, n2 / dn, n3 / dn);
+        } else {
+          store_elem(a.out, oo, a.out_dt, n0 / dn);
+          store_elem(a.out, oo + 1, a.out_dt, n1 / dn);
+          store_elem(a.out, oo + 2, a.out_dt, n2 / dn);
+          store_elem(a.out, oo + 3, a.out_dt, n3 / dn);
+        }
       }
     }
   }

@@ -121,6 +121,10 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
   const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tQ = tmem_base + IG * KT + KT;
   const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
   const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
+  // every MMA has completed when the tile loop is left, so the q / k images are free by then:
+  // they hold the [128][65] fp32 staging tile of the coalesced dq write-out
+  static_assert(2 * IMG_BYTES >= CT * 65 * 4, "staging tile must fit in the two operand images");
+  float* stage_out = reinterpret_cast<float*>(smem);
   float cA = 0.f, cB[IG], cC[NTRI];
 #pragma unroll
   for (int g = 0; g < IG; ++g) cB[g] = 0.f;
@@ -245,31 +249,41 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
     if (tiles >= 2) w.wait(&ds_done[(tiles - 2) & 1], ((tiles - 2) >> 1) & 1, 0x23);
     w.wait(&ds_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, 0x24);
     fence_after_sync();
-    // dq~ (padded, group-sorted columns) -> dq
+    // dq~ (padded, group-sorted columns) -> row-major staging tile in shared memory (original dim order)
     if (a.dq) {
-      const int i = c * CT + row;
       const int nslab = pg.k16_start[IG];
       for (int k16 = part; k16 < nslab; k16 += BT / CT) {
         float vv[16];
         tmem_ld16(tQ + lane_off + k16 * 16, vv);
         tmem_ld_wait();
-        if (i < a.N && !dead) {
 #pragma unroll
-          for (int x = 0; x < 16; ++x) {
-            const int src = pg.src[k16 * 16 + x];
-            if (src >= 0) {
-              const size_t o = (qoff + i) * HD + src;
-              float val = a.scale * vv[x];
-              if (a.dq_init) val += a.dq_init[o];
-              reinterpret_cast<__nv_bfloat16*>(a.dq)[o] = __float2bfloat16_rn(val);
-            }
-          }
+        for (int x = 0; x < 16; ++x) {
+          const int src = pg.src[k16 * 16 + x];
+          if (src >= 0) stage_out[row * 65 + src] = a.scale * vv[x];
         }
       }
     }
   }
   fence_before_sync();
   __syncthreads();
+  if (a.dq && !dead) {
+    // coalesced write-out: 8 consecutive dims per thread, cross-chunk part added, one 16-byte store
+    for (int x = tid; x < CT * 8; x += BT_ALL) {
+      const int r = x >> 3, seg = x & 7, i = c * CT + r;
+      if (i >= a.N) continue;
+      const size_t o = (qoff + i) * HD + seg * 8;
+      float val[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) val[j] = stage_out[r * 65 + seg * 8 + j];
+      if (a.dq_init) {
+        const float4 i0 = *reinterpret_cast<const float4*>(a.dq_init + o), i1 = *reinterpret_cast<const float4*>(a.dq_init + o + 4);
+        val[0] += i0.x; val[1] += i0.y; val[2] += i0.z; val[3] += i0.w;
+        val[4] += i1.x; val[5] += i1.y; val[6] += i1.z; val[7] += i1.w;
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.dq) + o) =
+          make_uint4(pack_bf16(val[0], val[1]), pack_bf16(val[2], val[3]), pack_bf16(val[4], val[5]), pack_bf16(val[6], val[7]));
+    }
+  }
   if (a.coef_partial) {
     float* red = reinterpret_cast<float*>(DS);      // the ds tiles are idle now: [16 warps][NCOEF]
     if (!issuer) {
@@ -491,16 +505,15 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
     // tensor-memory loads are warp-collective: every thread executes them, only the stores are guarded
     const bool valid = jglob < a.N && !dead;
     const int nslab = pg.k16_start[IG];
+    float* stage_out = reinterpret_cast<float*>(smem);    // the k / q images are free: [128][65] fp32 staging tile
     for (int k16 = part; k16 < nslab; k16 += BT / CT) {
       float vv[16];
       tmem_ld16(tK + lane_off + k16 * 16, vv);
       tmem_ld_wait();
-      if (valid && a.dk_part) {
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const int src = pg.src[k16 * 16 + x];
-          if (src >= 0) a.dk_part[(qoff + jglob) * HD + src] = a.scale * vv[x];   // Q image holds unscaled q
-        }
+      for (int x = 0; x < 16; ++x) {
+        const int src = pg.src[k16 * 16 + x];
+        if (src >= 0) stage_out[row * 65 + src] = a.scale * vv[x];   // Q image holds unscaled q
       }
     }
     {
@@ -517,6 +530,17 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
     }
   }
   fence_before_sync();
+  __syncthreads();
+  if (a.dk_part && !dead) {
+    const float* stage_out = reinterpret_cast<const float*>(smem);
+    for (int x = tid; x < CT * 16; x += BT_ALL) {       // coalesced write-out, four dims per thread
+      const int r = x >> 4, seg = x & 15, j = c * CT + r;
+      if (j >= a.N) continue;
+      *reinterpret_cast<float4*>(a.dk_part + (qoff + j) * HD + seg * 4) =
+          make_float4(stage_out[r * 65 + seg * 4], stage_out[r * 65 + seg * 4 + 1], stage_out[r * 65 + seg * 4 + 2],
+                      stage_out[r * 65 + seg * 4 + 3]);
+    }
+  }
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, 512);
   if (tid == 0 && dead) atomicOr(a.status, w.status_bits());

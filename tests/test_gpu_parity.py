@@ -197,3 +197,19 @@ def test_deferred_status_surfaces_at_backward_or_explicit_check():
     with pytest.raises(RuntimeError, match="denominator must be finite and strictly positive"):
         oal_b200.check_pending_status(block=True)
     oal_b200.check_pending_status(block=True)        # queue is drained: nothing left to report
+
+
+def test_run_to_run_determinism_bf16_tensorcore():
+    """No float atomics anywhere: two runs of the tensor-core path agree bit for bit."""
+    case = synthetic.qwen_head_case(6, batch=2, n=700, hq=14, hkv=2, g=8, bf16=True)
+    a = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
+    b = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
+    for key in a:
+        assert torch.equal(a[key], b[key]), key
+
+
+def test_more_than_eight_groups_uses_pair_kernels_bf16_tensorcore():
+    """G = 16: the state path stays on the tensor cores, the intra-chunk term runs on the fp32 pair kernels."""
+    case = synthetic.qwen_head_case(8, batch=1, n=300, hq=2, hkv=1, g=16, bf16=True, outlier_scale=4.0)
+    res = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
+    assert_close(res, oracle_dense(case), TOL_BF16, label="bf16 G=16")
