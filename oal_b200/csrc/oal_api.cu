@@ -160,7 +160,7 @@ BackwardSpaceTC carve_backward_tc(const OalProblem* p, void* ws) {
   s.coef_table = c.take<float>((size_t)p->q_heads * oal::state_rows());
   s.dcarry = c.take<float>(units * nb * oal::state_rows() * oal::EP);
   s.dt_img = c.take<char>(units * nb * oal::state_image_bytes_per_chunk());
-  s.dcoef_partial = c.take<float>((size_t)p->batch * nb * p->q_heads * oal::state_rows());
+  s.dcoef_partial = c.take<float>(2 * (size_t)p->batch * nb * p->q_heads * oal::state_rows());   // two column halves
   s.dcoef = c.take<float>((size_t)p->q_heads * oal::state_rows());
   s.slots = c.take<float>((size_t)p->q_heads * oal::NCOEF);
   s.dq_cross = c.take<float>(qrows * oal::HD);
@@ -421,7 +421,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     }
     if (want_c) {
       { LaunchScope scope("dcoef_reduce", st, 2);
-        e = oal::dcoef_reduce(s.dcoef_partial, p->batch * nb, p->q_heads, dim_perm, group_start, s.dcoef, s.slots, st); }
+        e = oal::dcoef_reduce(s.dcoef_partial, 2 * p->batch * nb, p->q_heads, dim_perm, group_start, s.dcoef, s.slots, st); }
       if (e != cudaSuccess) return fail_cuda(e, "coefficient gradient reduction kernels");
       { LaunchScope scope("reduce_coefs", st);
         e = oal::reduce_coefs(s.coef_pairs, tc_intra ? nb : oal::pairs_tiles(p->seq_len), s.slots, p->batch,

@@ -72,6 +72,72 @@ __device__ __forceinline__ uint4 feature_chunk(const float (&x)[HD], const float
                     umma::pack_bf16(f[6], f[7]));
 }
 
+// ---- coefficient-free features straight from the packed bf16 row ------------------------------
+// xp[k] holds (x[2k], x[2k+1]).  The product of two bf16 values rounded once to bf16 is what the
+// fp32 multiply followed by a conversion gives, so the packed multiply yields the same bits at two
+// features per instruction and needs no unpacked copy of the row.
+template <int A, int B>
+__device__ __forceinline__ uint32_t pick2(const uint32_t (&xp)[HD / 2]) {   // (x[A], x[B])
+  if constexpr ((A & 1) == 0 && B == A + 1) {
+    return xp[A / 2];
+  } else {
+    constexpr uint32_t lo = (A & 1) * 2, hi = 4 + (B & 1) * 2;
+    return __byte_perm(xp[A / 2], xp[B / 2], lo | ((lo + 1) << 4) | (hi << 8) | ((hi + 1) << 12));
+  }
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+template <int CH>
+__device__ __forceinline__ uint4 feature_chunk_bf16(const uint32_t (&xp)[HD / 2]) {
+  if constexpr (CH < F_PAIR_CHUNKS) {
+    constexpr RC p0 = pair_rc(8 * CH + 0), p1 = pair_rc(8 * CH + 1), p2 = pair_rc(8 * CH + 2),
+                 p3 = pair_rc(8 * CH + 3), p4 = pair_rc(8 * CH + 4), p5 = pair_rc(8 * CH + 5),
+                 p6 = pair_rc(8 * CH + 6), p7 = pair_rc(8 * CH + 7);
+    return make_uint4(mul_bf16x2(pick2<p0.r, p1.r>(xp), pick2<p0.c, p1.c>(xp)),
+                      mul_bf16x2(pick2<p2.r, p3.r>(xp), pick2<p2.c, p3.c>(xp)),
+                      mul_bf16x2(pick2<p4.r, p5.r>(xp), pick2<p4.c, p5.c>(xp)),
+                      mul_bf16x2(pick2<p6.r, p7.r>(xp), pick2<p6.c, p7.c>(xp)));
+  } else if constexpr (CH < F_CONST_CHUNK) {
+    constexpr int k = 4 * (CH - F_LIN_CHUNK0);
+    return make_uint4(xp[k], xp[k + 1], xp[k + 2], xp[k + 3]);
+  } else if constexpr (CH == F_CONST_CHUNK) {
+    return make_uint4(0x00003F80u, 0u, 0u, 0u);   // bf16(1.0) in element 0
+  } else {
+    return make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
+template <int S, int... J>
+__device__ __forceinline__ void slab_bf16_impl(const uint32_t (&xp)[HD / 2], uint4* tile, int token,
+                                               std::integer_sequence<int, J...>) {
+  ((tile[J * CT + token] = feature_chunk_bf16<S * 16 + J>(xp)), ...);
+}
+
+// All 16 chunks of slab s of one token (coefficient-free, unscaled) into the slab tile.
+__device__ __forceinline__ void write_slab_bf16(int s, const uint32_t (&xp)[HD / 2], uint4* tile, int token) {
+#define OAL_SLAB_CASE(S)                                                               \
+  case S:                                                                              \
+    slab_bf16_impl<S>(xp, tile, token, std::make_integer_sequence<int, 16>{});          \
+    break;
+  switch (s) {
+    OAL_SLAB_CASE(0) OAL_SLAB_CASE(1) OAL_SLAB_CASE(2) OAL_SLAB_CASE(3) OAL_SLAB_CASE(4) OAL_SLAB_CASE(5)
+    OAL_SLAB_CASE(6) OAL_SLAB_CASE(7) OAL_SLAB_CASE(8) OAL_SLAB_CASE(9) OAL_SLAB_CASE(10) OAL_SLAB_CASE(11)
+    OAL_SLAB_CASE(12) OAL_SLAB_CASE(13) OAL_SLAB_CASE(14) OAL_SLAB_CASE(15) OAL_SLAB_CASE(16)
+    default: break;
+  }
+#undef OAL_SLAB_CASE
+}
+
+// Power of the query scale a coefficient-free, unscaled feature row lacks: pair features scale^2,
+// linear features scale, the constant feature 1.
+__device__ __forceinline__ float feature_scale_factor(int f, float scale) {
+  return f < 8 * F_PAIR_CHUNKS ? scale * scale : (f < 8 * F_CONST_CHUNK ? scale : 1.f);
+}
+
 // Threads per CTA of the kernels that generate feature slabs: 128 tokens x GEN_PARTS threads per
 // token, each thread writing 16 / GEN_PARTS chunks of a slab.
 constexpr int GEN_THREADS = 256;

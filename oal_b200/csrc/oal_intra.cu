@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
     mbar_fence_init();
     dead = 0;
   }
-  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, a.scale, a.scale * a.scale, tid, 256);
+  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, a.scale, a.scale * a.scale, 2.f * a.scale * a.scale, tid, 256);
   const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
   // a head with more padded slabs than the caller announced would not fit the images: refuse it
   const bool bad = pg.k16_start[IG] > a.slabs;
@@ -122,12 +122,12 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
 #pragma unroll
       for (int g = 0; g < IG; ++g) {
         f32x2 t[4];
-        const f32x2 bg = f2_bcast(pg.B[g]), cgg = f2_bcast(pg.C[g * IG + g]);
+        const f32x2 bg = pg.B2[g], cgg = pg.C2[g * IG + g];
 #pragma unroll
         for (int j = 0; j < 4; ++j) t[j] = f2_fma(cgg, s2[g][j], bg);
 #pragma unroll
         for (int g2 = 0; g2 < g; ++g2) {
-          const f32x2 c2 = f2_bcast(2.f * pg.C[g * IG + g2]);
+          const f32x2 c2 = pg.C2[g * IG + g2];
 #pragma unroll
           for (int j = 0; j < 4; ++j) t[j] = f2_fma(c2, s2[g2][j], t[j]);
         }

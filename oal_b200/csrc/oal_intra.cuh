@@ -19,17 +19,22 @@ constexpr int KT = 16;                       // keys (or queries) per tile of th
 constexpr int IG = OAL_IG;                   // groups handled by this build of the kernels
 constexpr int DP_MAX = 64 + (IG - 1) * 16;   // padded dims: every group rounded up to 16 (176 for 8 groups)
 
+typedef unsigned long long f32x2;   // two floats in one 64-bit register (packed fp32 arithmetic)
+
 // Padded, group-sorted dimension layout of one head.
 struct PaddedGroups {
   int k16_start[IG + 1];     // first 16-dim slab of group g; k16_start[IG] = number of slabs
   short src[DP_MAX];         // original dimension of padded position p, or -1 for zero padding
-  float A, B[IG], C[IG * IG];   // coefficients; B pre-multiplied by `bscale`, C by `cscale`
+  float A;
+  // coefficients as (c, c) pairs, so one 64-bit shared-memory load feeds a packed FMA:
+  // B times `bscale`; C[g][g] times `cdiag`, C[g][g'] times `coff`
+  f32x2 B2[IG], C2[IG * IG];
 };
 
 __device__ __forceinline__ void load_padded_groups(PaddedGroups& pg, const int32_t* dim_perm,
                                                    const int32_t* group_start, const float* A, const float* Bc,
-                                                   const float* Cc, int G, int h, float bscale, float cscale,
-                                                   int tid, int nthreads) {
+                                                   const float* Cc, int G, int h, float bscale, float cdiag,
+                                                   float coff, int tid, int nthreads) {
   if (tid == 0) {
     int acc = 0;
     for (int g = 0; g < IG; ++g) {
@@ -40,10 +45,14 @@ __device__ __forceinline__ void load_padded_groups(PaddedGroups& pg, const int32
     pg.k16_start[IG] = acc;
     pg.A = A[h];
   }
-  for (int x = tid; x < IG; x += nthreads) pg.B[x] = x < G ? bscale * Bc[h * G + x] : 0.f;
+  for (int x = tid; x < IG; x += nthreads) {
+    const float v = x < G ? bscale * Bc[h * G + x] : 0.f;
+    pg.B2[x] = ((f32x2)__float_as_uint(v) << 32) | __float_as_uint(v);
+  }
   for (int x = tid; x < IG * IG; x += nthreads) {
     const int g = x / IG, g2 = x % IG;
-    pg.C[x] = (g < G && g2 < G) ? cscale * Cc[((size_t)h * G + g) * G + g2] : 0.f;
+    const float v = (g < G && g2 < G) ? (g == g2 ? cdiag : coff) * Cc[((size_t)h * G + g) * G + g2] : 0.f;
+    pg.C2[x] = ((f32x2)__float_as_uint(v) << 32) | __float_as_uint(v);
   }
   __syncthreads();
   for (int p = tid; p < DP_MAX; p += nthreads) {
@@ -89,17 +98,6 @@ __device__ __forceinline__ void build_padded_image(unsigned char* img, uint32_t*
   __syncthreads();
 }
 
-// 32 lanes x 32-bit, 8 consecutive columns per thread.
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
-  uint32_t r[8];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-#pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 // 32 lanes x 32-bit, 4 consecutive columns per thread.
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
   uint32_t r[4];
@@ -113,7 +111,6 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
 
 // Packed fp32 pairs (sm_100 executes add / mul / fma on two floats held in one 64-bit register):
 // the per-pair combine is issue-bound, so two columns per instruction is the lever that matters.
-typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
   f32x2 r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));

@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
     mbar_fence_init();
     dead = 0;
   }
-  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, BT_ALL);
+  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 2.f, 2.f, tid, BT_ALL);
   const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
   if (tid == 0) {
     const unsigned char* gsrc =
@@ -208,10 +208,10 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
         }
 #pragma unroll
         for (int g = 0; g < IG; ++g) {
-          f32x2 t0 = f2_bcast(pg.B[g]), t1 = t0;
+          f32x2 t0 = pg.B2[g], t1 = t0;
 #pragma unroll
           for (int g2 = 0; g2 < IG; ++g2) {
-            const f32x2 c2 = f2_bcast(2.f * pg.C[g * IG + g2]);
+            const f32x2 c2 = pg.C2[g * IG + g2];
             t0 = f2_fma(c2, s2[g2][0], t0);
             t1 = f2_fma(c2, s2[g2][1], t1);
           }
@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
     mbar_fence_init();
     dead = 0;
   }
-  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, tid, BT_ALL);
+  load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, 1.f, tid, BT_ALL);
   const size_t koff = (size_t)(b * a.Hkv + kvh) * a.N, qoff = (size_t)(b * a.Hq + h) * a.N;
   if (tid == 0) {
     const unsigned char* gsrc =
@@ -469,11 +469,11 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
           f32x2 t0 = f2_bcast(0.f), t1 = t0;
 #pragma unroll
           for (int g2 = 0; g2 < IG; ++g2) {
-            const f32x2 c2 = f2_bcast(pg.C[g * IG + g2]);
+            const f32x2 c2 = pg.C2[g * IG + g2];
             t0 = f2_fma(c2, s2[g2][0], t0);
             t1 = f2_fma(c2, s2[g2][1], t1);
           }
-          const f32x2 bg = f2_bcast(pg.B[g]);
+          const f32x2 bg = pg.B2[g];
           // w += s_g (B_g + t);  ds_g = dw (B_g + 2 t)
           w0 = f2_fma(s2[g][0], f2_fma(t0, f2_bcast(1.f), bg), w0);
           w1 = f2_fma(s2[g][1], f2_fma(t1, f2_bcast(1.f), bg), w1);

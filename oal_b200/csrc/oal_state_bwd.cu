@@ -19,12 +19,6 @@ namespace {
 
 using namespace umma;
 
-// nine slab groups (2,...,2,1): two 80-column accumulators plus one Z buffer fit in 256 columns, so two
-// CTAs share an SM and fill each other's gaps
-constexpr int HGROUPS = 9;
-__device__ __forceinline__ int hgroup_first(int g) { return 2 * g; }
-__device__ __forceinline__ int hgroup_count(int g) { return g < 8 ? 2 : 1; }
-
 __device__ __forceinline__ void unpack_bf16x8(const uint4 t, float (&o)[8]) {
   const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
@@ -44,30 +38,78 @@ struct DStateArgs {
   const __nv_bfloat16* carry_img;  // [units, NB, 17, 10, 128, 8] or null (no coefficient gradients)
   const float* coef_table;         // [Hq, F_ROWS]
   float* dcarry;                   // [units, NB, F_ROWS, EP]
-  float* dcoef_partial;            // [B, NB, Hq, F_ROWS] or null
-  int N, NB, Hq, Hkv;
+  float* dcoef_partial;            // [B, NB, 2 column halves, Hq, F_ROWS] or null
+  int N, NB, Hq, Hkv, units;
   float scale;
   int32_t* status;
 };
 
-__global__ void __launch_bounds__(GEN_THREADS, 2) dstate_heads_kernel(const DStateArgs a) {
+// Persistent, warp-specialised kernel.  Work items are (batch x KV head, chunk, feature slab); CTA k
+// takes items k, k + gridDim.x, ... and walks the query heads of the KV head for each, so the flat
+// iteration `it` = (item, head) drives four pipelined roles:
+//   warps 0-3   thread = token: generate the coefficient-free, unscaled feature slab of (item, head)
+//               from the packed bf16 q row into A[it % 3]
+//   warp  13    lane 0 streams the head's G image into a 4-slot ring (bulk copies)
+//   warp  12    lane 0 issues the MMAs  Z[it % 3] = A^T G  once A and G are full and Z[it % 3] is drained
+//   warps 4-11  drain Z, thread = (feature row, half of the 80 columns): dot with the carry row for
+//               the coefficient gradient, acc += coef_h * Z in tensor memory; after the last head
+//               acc -> dCarry.  The powers of the query scale the features lack are applied here.
+// A slot and Z buffer share the index it % 3, so the MMA-completion barrier of that index tells the
+// generators "A is free" and the drain warps "Z is ready".
+constexpr int DS_GEN_WARPS = 4, DS_EPI_WARPS = 8;
+constexpr int DS_ISSUER = DS_GEN_WARPS + DS_EPI_WARPS, DS_LOADER = DS_ISSUER + 1;
+constexpr int DS_THREADS = (DS_LOADER + 1) * 32;
+constexpr int DS_RING = 3;      // A slots in shared memory = Z buffers in tensor memory
+constexpr int DS_GRING = 4;     // G image slots
+constexpr int DS_COLS = EP / 2; // columns per drain thread
+static_assert(DS_GEN_WARPS * 32 == CT, "one generator thread per token");
+static_assert(DS_GEN_WARPS % 4 == 0, "drain warp w must sit on tensor-memory lane quadrant w % 4");
+
+// (item, head) cursor of one role; advancing costs a division only when the item changes
+struct DsCursor {
+  int u, c, slab, hh, item;
+  __device__ __forceinline__ void set_item(int it_item, int NB) {
+    item = it_item;
+    slab = item % F_SLABS;
+    const int r = item / F_SLABS;
+    c = r % NB;
+    u = r / NB;
+  }
+  __device__ __forceinline__ void start(int NB) {
+    hh = 0;
+    set_item(blockIdx.x, NB);
+  }
+  __device__ __forceinline__ void next(int rep, int NB) {
+    if (++hh == rep) {
+      hh = 0;
+      set_item(item + gridDim.x, NB);
+    }
+  }
+};
+
+__global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStateArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* Abuf = smem;                        // 2 x SLAB_A_BYTES
-  unsigned char* Gbuf = smem + 2 * SLAB_A_BYTES;     // 2 x SLAB_S_BYTES  ([10][128 tokens][8 e])
-  __shared__ uint64_t mma_done[2], gfull[2];
+  unsigned char* Abuf = smem;                              // DS_RING x SLAB_A_BYTES
+  unsigned char* Gbuf = smem + DS_RING * SLAB_A_BYTES;     // DS_GRING x SLAB_S_BYTES  ([10][128 tokens][8 e])
+  __shared__ uint64_t full_a[DS_RING], mma_done[DS_RING], z_free[DS_RING], g_full[DS_GRING], g_free[DS_GRING];
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
-  __shared__ float dsum[2][2][128];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int grp = blockIdx.x, c = blockIdx.y, u = blockIdx.z;
-  const int b = u / a.Hkv, kvh = u % a.Hkv, rep = a.Hq / a.Hkv;
-  const int token = tid & 127, half = tid >> 7, wg = warp >> 2;
-  if (warp == 0) tmem_alloc(&tmem_base, 256);
+  const int rep = a.Hq / a.Hkv;
+  const int n_items = F_SLABS * a.NB * a.units;
+  const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int T = my_items * rep;
+  if (warp == DS_ISSUER) tmem_alloc(&tmem_base, 512);
   if (tid == 0) {
-    mbar_init(&mma_done[0], 1);
-    mbar_init(&mma_done[1], 1);
-    mbar_init(&gfull[0], 1);
-    mbar_init(&gfull[1], 1);
+    for (int s = 0; s < DS_RING; ++s) {
+      mbar_init(&full_a[s], DS_GEN_WARPS);
+      mbar_init(&mma_done[s], 1);
+      mbar_init(&z_free[s], DS_EPI_WARPS);
+    }
+    for (int s = 0; s < DS_GRING; ++s) {
+      mbar_init(&g_full[s], 1);
+      mbar_init(&g_free[s], 1);
+    }
     mbar_fence_init();
     dead = 0;
   }
@@ -75,114 +117,165 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) dstate_heads_kernel(const DSta
   __syncthreads();
   fence_after_sync();
   Waiter w{&dead};
-  const int s0 = hgroup_first(grp), ns = hgroup_count(grp);
-  const uint32_t tacc = tmem_base;                 // ns x 80 columns
-  const uint32_t tz = tmem_base + 160;             // 80 columns
-  const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
-  const uint32_t idesc = instr_desc_bf16(128, EP, 1, 1);
-  const int fr = 32 * (warp & 3) + lane;
-  const int col0 = wg == 0 ? 0 : 48, ncol = wg == 0 ? 48 : 32;
-  const size_t g_stride = (size_t)a.NB * SLAB_S_BYTES;   // bytes per (b,h) in gimg
-  auto gimg_ptr = [&](int h) {
-    return reinterpret_cast<const unsigned char*>(a.gimg) + (size_t)(b * a.Hq + h) * g_stride + (size_t)c * SLAB_S_BYTES;
-  };
-  if (tid == 0) {
-    mbar_arrive_expect_tx(&gfull[0], SLAB_S_BYTES);
-    bulk_g2s(Gbuf, gimg_ptr(kvh * rep), SLAB_S_BYTES, &gfull[0]);
-  }
-  const unsigned char* carry_base =
-      a.carry_img ? reinterpret_cast<const unsigned char*>(a.carry_img) + ((size_t)u * a.NB + c) * F_SLABS * SLAB_S_BYTES
-                  : nullptr;
 
-  // epilogue of flattened iteration m = head_index * ns + slab_index
-  auto epilogue = [&](int m) {
-    const int hm = m / ns, im = m - hm * ns, h = kvh * rep + hm;
-    w.wait(&mma_done[m & 1], (m >> 1) & 1);
-    fence_after_sync();
-    const int f = (s0 + im) * 128 + fr;
-    if (warp < 8) {                 // warps 0-7 cover the 128 lanes x 80 columns
-      const float cf = a.coef_table[(size_t)h * F_ROWS + f];
-      float dot = 0.f;
-      for (int cc = 0; cc < ncol; cc += 16) {
-        float z[16];
-        tmem_ld16(tz + lane_off + col0 + cc, z);
-        float acc[16];
-        if (hm > 0) tmem_ld16(tacc + im * EP + lane_off + col0 + cc, acc);
-        tmem_ld_wait();
-        if (carry_base) {
-          const uint4* cp = reinterpret_cast<const uint4*>(carry_base + (size_t)(s0 + im) * SLAB_S_BYTES);
-          const int ec = (col0 + cc) >> 3;
-          float c0[8], c1[8];
-          unpack_bf16x8(cp[ec * 128 + fr], c0);
-          unpack_bf16x8(cp[(ec + 1) * 128 + fr], c1);
+  if (warp < DS_GEN_WARPS) {
+    // ---------------- generators ----------------
+    const int token = tid;
+    uint4 nx[8];                               // packed q row of the next (item, head)
+    auto fetch = [&](const DsCursor& d) {
+      const int b = d.u / a.Hkv, h = (d.u % a.Hkv) * rep + d.hh, i = d.c * CT + token;
+      if (i < a.N) {
+        const uint4* p = reinterpret_cast<const uint4*>(a.q + ((size_t)(b * a.Hq + h) * a.N + i) * HD);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) dot = fmaf(z[j], c0[j], fmaf(z[8 + j], c1[j], dot));
-        }
-        uint32_t o[16];
+        for (int j = 0; j < 8; ++j) nx[j] = p[j];
+      } else {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(hm > 0 ? fmaf(cf, z[j], acc[j]) : cf * z[j]);
-        tmem_st16(tacc + im * EP + lane_off + col0 + cc, o);
+        for (int j = 0; j < 8; ++j) nx[j] = make_uint4(0u, 0u, 0u, 0u);
       }
-      tmem_st_wait();
-      if (a.dcoef_partial) dsum[m & 1][wg][fr] = dot;
-    }
-    if (a.dcoef_partial) {
-      __syncthreads();
-      if (warp < 4)
-        a.dcoef_partial[(((size_t)b * a.NB + c) * a.Hq + h) * F_ROWS + f] = dsum[m & 1][0][fr] + dsum[m & 1][1][fr];
-    }
-    fence_before_sync();
-  };
-
-  int n = 0;
-  for (int hh = 0; hh < rep; ++hh) {
-    const int h = kvh * rep + hh;
-    float x[HD];
-    load_row_bf16(x, a.q + (size_t)(b * a.Hq + h) * a.N * HD, c * CT + token, a.N, a.scale);
-    for (int it = 0; it < ns; ++it, ++n) {
-      const int buf = n & 1;
-      write_half_slab<false>(s0 + it, half, x, nullptr, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES), token);
-      // the single Z buffer must be drained before the next MMA is issued
-      if (n >= 1) epilogue(n - 1);
-      // every MMA of the previous head has completed: its G buffer can take the next head's image
-      if (it == 0 && tid == 0 && hh + 1 < rep) {
-        mbar_arrive_expect_tx(&gfull[(hh + 1) & 1], SLAB_S_BYTES);
-        bulk_g2s(Gbuf + ((hh + 1) & 1) * SLAB_S_BYTES, gimg_ptr(h + 1), SLAB_S_BYTES, &gfull[(hh + 1) & 1]);
+    };
+    DsCursor cur;
+    cur.start(a.NB);
+    if (T > 0) fetch(cur);
+    int s = 0, use = 0;                       // ring slot of `it` and how often it has been used before
+    for (int it = 0; it < T; ++it) {
+      const int slab = cur.slab;
+      uint32_t xp[HD / 2];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xp[4 * j] = nx[j].x;
+        xp[4 * j + 1] = nx[j].y;
+        xp[4 * j + 2] = nx[j].z;
+        xp[4 * j + 3] = nx[j].w;
       }
+      cur.next(rep, a.NB);
+      if (it + 1 < T) fetch(cur);             // in flight while this slab is generated
+      if (use > 0) w.wait(&mma_done[s], (use - 1) & 1, 0x31);   // the MMA that read A[s] has completed
+      write_slab_bf16(slab, xp, reinterpret_cast<uint4*>(Abuf + s * SLAB_A_BYTES), token);
       fence_async_smem();
-      __syncthreads();
-      if (tid == 0) {
-        if (it == 0) w.wait(&gfull[hh & 1], (hh >> 1) & 1);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_a[s]);
+      if (++s == DS_RING) { s = 0; ++use; }
+    }
+  } else if (warp < DS_ISSUER) {
+    // ---------------- drain warps ----------------
+    const int fr = 32 * (warp & 3) + lane, ch = (warp - DS_GEN_WARPS) >> 2, col0 = ch * DS_COLS;
+    const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+    const uint32_t tacc = tmem_base + col0;
+    uint4 cpk[DS_COLS / 8];
+#pragma unroll
+    for (int e = 0; e < DS_COLS / 8; ++e) cpk[e] = make_uint4(0u, 0u, 0u, 0u);
+    DsCursor d, dn;
+    d.start(a.NB);
+    dn = d;
+    int s = 0, use = 0;
+    float cf_next = T > 0 ? a.coef_table[(size_t)((d.u % a.Hkv) * rep) * F_ROWS + d.slab * 128 + fr] : 0.f;
+    for (int it = 0; it < T; ++it) {
+      const int b = d.u / a.Hkv, h = (d.u % a.Hkv) * rep + d.hh, f = d.slab * 128 + fr;
+      const float fs = feature_scale_factor(f, a.scale);
+      const float cf = cf_next * fs;
+      dn.next(rep, a.NB);
+      if (it + 1 < T)       // coefficient of the next (item, head): in flight during this drain
+        cf_next = a.coef_table[(size_t)((dn.u % a.Hkv) * rep + dn.hh) * F_ROWS + dn.slab * 128 + fr];
+      if (d.hh == 0 && a.carry_img) {
+        const uint4* cp = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(a.carry_img) +
+                                                         (((size_t)d.u * a.NB + d.c) * F_SLABS + d.slab) * SLAB_S_BYTES);
+#pragma unroll
+        for (int e = 0; e < DS_COLS / 8; ++e) cpk[e] = cp[(col0 / 8 + e) * 128 + fr];
+      }
+      w.wait(&mma_done[s], use & 1, 0x32);
+      fence_after_sync();
+      const uint32_t tz = tmem_base + EP * (1 + s) + col0;
+      float dot[4] = {0.f, 0.f, 0.f, 0.f};
+      // two register stages: the loads of the next 8 columns are in flight while these are combined
+      float z[2][8], acc[2][8];
+      tmem_ld8(tz + lane_off, z[0]);
+      if (d.hh > 0) tmem_ld8(tacc + lane_off, acc[0]);
+#pragma unroll
+      for (int r = 0; r < DS_COLS / 8; ++r) {
+        tmem_ld_wait();
+        if (r + 1 < DS_COLS / 8) {
+          tmem_ld8(tz + lane_off + 8 * (r + 1), z[(r + 1) & 1]);
+          if (d.hh > 0) tmem_ld8(tacc + lane_off + 8 * (r + 1), acc[(r + 1) & 1]);
+        }
+        float c0[8];
+        unpack_bf16x8(cpk[r], c0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dot[j & 3] = fmaf(z[r & 1][j], c0[j], dot[j & 3]);
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          o[j] = __float_as_uint(d.hh > 0 ? fmaf(cf, z[r & 1][j], acc[r & 1][j]) : cf * z[r & 1][j]);
+        tmem_st8(tacc + lane_off + 8 * r, o);
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&z_free[s]);      // every lane has its Z values in registers
+      tmem_st_wait();
+      if (a.dcoef_partial)      // one partial per column half, summed by the reduction over (batch, chunk, half)
+        a.dcoef_partial[((((size_t)b * a.NB + d.c) * 2 + ch) * a.Hq + h) * F_ROWS + f] =
+            fs * ((dot[0] + dot[1]) + (dot[2] + dot[3]));
+      if (d.hh == rep - 1) {
+        // dCarry rows of this slab: tensor memory -> HBM
+        float* dst = a.dcarry + (((size_t)d.u * a.NB + d.c) * F_ROWS + f) * EP + col0;
+        float vv[DS_COLS / 8][8];
+#pragma unroll
+        for (int r = 0; r < DS_COLS / 8; ++r) tmem_ld8(tacc + lane_off + 8 * r, vv[r]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int r = 0; r < DS_COLS / 8; ++r) {
+          *reinterpret_cast<float4*>(dst + 8 * r) = make_float4(vv[r][0], vv[r][1], vv[r][2], vv[r][3]);
+          *reinterpret_cast<float4*>(dst + 8 * r + 4) = make_float4(vv[r][4], vv[r][5], vv[r][6], vv[r][7]);
+        }
+      }
+      d.next(rep, a.NB);
+      if (++s == DS_RING) { s = 0; ++use; }
+    }
+  } else if (warp == DS_ISSUER) {
+    // ---------------- MMA issue ----------------
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16(128, EP, 1, 1);
+      int s = 0, use = 0, gs = 0, guse = 0;
+      for (int it = 0; it < T; ++it) {
+        const uint32_t a_addr = smem_u32(Abuf + s * SLAB_A_BYTES);
+        const uint32_t g_addr = smem_u32(Gbuf + gs * SLAB_S_BYTES);
+        const uint32_t tz = tmem_base + EP * (1 + s);
+        w.wait(&full_a[s], use & 1, 0x33);
+        w.wait(&g_full[gs], guse & 1, 0x34);
+        if (use > 0) w.wait(&z_free[s], (use - 1) & 1, 0x35);
         fence_after_sync();
-        const uint32_t a_addr = smem_u32(Abuf + buf * SLAB_A_BYTES);
-        const uint32_t g_addr = smem_u32(Gbuf + (hh & 1) * SLAB_S_BYTES);
 #pragma unroll
         for (int ks = 0; ks < CT / 16; ++ks)
-          mma_bf16_ss(tz, smem_desc(a_addr + ks * 256, 128, CT * 16), smem_desc(g_addr + ks * 256, 128, CT * 16),
-                      idesc, ks > 0);
-        mma_commit(&mma_done[buf]);
+          mma_bf16_ss(tz, smem_desc(a_addr + ks * 256, 128, CT * 16), smem_desc(g_addr + ks * 256, 128, CT * 16), idesc,
+                      ks > 0);
+        mma_commit(&mma_done[s]);
+        mma_commit(&g_free[gs]);               // the loader may refill this G slot when these MMAs are done
+        if (++s == DS_RING) { s = 0; ++use; }
+        if (++gs == DS_GRING) { gs = 0; ++guse; }
       }
     }
-  }
-  epilogue(n - 1);
-  fence_after_sync();
-  // dCarry rows of this slab group: tensor memory -> HBM
-  float* dbase = a.dcarry + ((size_t)u * a.NB + c) * F_ROWS * EP;
-  for (int it = 0; it < ns && warp < 8; ++it) {
-    float* dst = dbase + (size_t)((s0 + it) * 128 + fr) * EP + col0;
-    for (int cc = 0; cc < ncol; cc += 16) {
-      float vv[16];
-      tmem_ld16(tacc + it * EP + lane_off + col0 + cc, vv);
-      tmem_ld_wait();
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4)
-        *reinterpret_cast<float4*>(dst + cc + 4 * q4) =
-            make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]);
+    __syncwarp();
+  } else {
+    // ---------------- G image stream ----------------
+    if (lane == 0) {
+      DsCursor d;
+      d.start(a.NB);
+      int gs = 0, guse = 0;
+      for (int it = 0; it < T; ++it) {
+        const int b = d.u / a.Hkv, h = (d.u % a.Hkv) * rep + d.hh;
+        const unsigned char* src =
+            reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.Hq + h) * a.NB + d.c) * SLAB_S_BYTES;
+        if (guse > 0) w.wait(&g_free[gs], (guse - 1) & 1, 0x36);
+        mbar_arrive_expect_tx(&g_full[gs], SLAB_S_BYTES);
+        bulk_g2s(Gbuf + gs * SLAB_S_BYTES, src, SLAB_S_BYTES, &g_full[gs]);
+        d.next(rep, a.NB);
+        if (++gs == DS_GRING) { gs = 0; ++guse; }
+      }
     }
+    __syncwarp();
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, 256);
+  if (warp == DS_ISSUER) tmem_dealloc(tmem_base, 512);
   if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
@@ -504,13 +597,17 @@ __global__ void __launch_bounds__(256) norm_vjp_image_kernel(const void* grad_ou
 cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img, const float* coef_table,
                          float* dcarry, float* dcoef_partial, int B, int Hq, int Hkv, int N, int NB, float scale,
                          int32_t* status, cudaStream_t st) {
-  const int smem = 2 * SLAB_A_BYTES + 2 * SLAB_S_BYTES;
+  const int smem = DS_RING * SLAB_A_BYTES + DS_GRING * SLAB_S_BYTES;
   cudaError_t e = cudaFuncSetAttribute(dstate_heads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  const int items = F_SLABS * NB * B * Hkv;
   DStateArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(gimg),
                static_cast<const __nv_bfloat16*>(carry_img), coef_table, dcarry, dcoef_partial, N, NB, Hq, Hkv,
-               scale, status};
-  dstate_heads_kernel<<<dim3(HGROUPS, NB, B * Hkv), GEN_THREADS, smem, st>>>(a);
+               B * Hkv, scale, status};
+  dstate_heads_kernel<<<items < sms ? items : sms, DS_THREADS, smem, st>>>(a);
   return cudaGetLastError();
 }
 
