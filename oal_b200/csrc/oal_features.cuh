@@ -32,6 +32,13 @@ constexpr int CT = 128;                        // tokens per chunk of the scan
 constexpr int SLAB_A_BYTES = 128 * CT * 2;     // feature slab tile  [16 chunks][128 tokens][8] bf16
 constexpr int SLAB_S_BYTES = (EP / 8) * 128 * 16;   // state slab image [10][128 features][8 e] bf16
 
+// Per-chunk fp32 state increments (and state-gradient increments) are stored like the bf16 state
+// image, [slab][e / 8][128 rows][8 e], so that a warp whose lanes are consecutive feature rows writes
+// and reads contiguous kilobytes.  Float index of (feature row f, column e) inside one chunk:
+__host__ __device__ constexpr size_t state_inc_offset(int f, int e) {
+  return ((size_t)((f >> 7) * (EP / 8) + (e >> 3)) * 128 + (f & 127)) * 8 + (e & 7);
+}
+
 struct RC {
   int r, c;
 };

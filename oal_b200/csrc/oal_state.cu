@@ -60,7 +60,7 @@ __global__ void coef_table_kernel(const int32_t* dim_perm, const int32_t* group_
 // ---------------------------------------------------------------------------
 struct StateUpdateArgs {
   const __nv_bfloat16 *k, *v;   // [units, N, 64]
-  float* ds;                    // [units, NB, F_ROWS, EP]
+  float* ds;                    // [units, NB] chunks of F_ROWS x EP floats in state_inc_offset order
   int N, NB;
   int32_t* status;
 };
@@ -107,7 +107,6 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) state_update_kernel(const Stat
     if (warp >= 8) return;          // warps 0-7 cover the 128 lanes x 80 columns
     const int row = (s0 + it) * 128 + 32 * (warp & 3) + lane;
     const int col0 = warp < 4 ? 0 : 48, ncol = warp < 4 ? 48 : 32;
-    float* dst = ds_base + (size_t)row * EP + col0;
     const uint32_t t = tacc + (uint32_t)((it & 1) * EP) + ((uint32_t)(32 * (warp & 3)) << 16) + col0;
     for (int cc = 0; cc < ncol; cc += 16) {
       float vv[16];
@@ -115,7 +114,7 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) state_update_kernel(const Stat
       tmem_ld_wait();
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4)
-        *reinterpret_cast<float4*>(dst + cc + 4 * q4) =
+        *reinterpret_cast<float4*>(ds_base + state_inc_offset(row, col0 + cc + 4 * q4)) =
             make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]);
     }
     fence_before_sync();
@@ -169,7 +168,8 @@ __global__ void __launch_bounds__(256) state_scan_kernel(const float* ds, __nv_b
   }
   for (int n = 0; n < NB; ++n) {
     const int c = reverse ? NB - 1 - n : n;
-    const float4* p = reinterpret_cast<const float4*>(ds + (((size_t)u * NB + c) * F_ROWS + f) * EP + 8 * ec);
+    const float4* p =
+        reinterpret_cast<const float4*>(ds + ((size_t)u * NB + c) * F_ROWS * EP + state_inc_offset(f, 8 * ec));
     const float4 a0 = p[0], a1 = p[1];
     if (image) {
       uint4 o = make_uint4(pack_bf16(run[0], run[1]), pack_bf16(run[2], run[3]), pack_bf16(run[4], run[5]),

@@ -37,7 +37,7 @@ struct DStateArgs {
   const __nv_bfloat16* gimg;       // [B*Hq, NB, 10, 128, 8]
   const __nv_bfloat16* carry_img;  // [units, NB, 17, 10, 128, 8] or null (no coefficient gradients)
   const float* coef_table;         // [Hq, F_ROWS]
-  float* dcarry;                   // [units, NB, F_ROWS, EP]
+  float* dcarry;                   // [units, NB] chunks of F_ROWS x EP floats in state_inc_offset order
   float* dcoef_partial;            // [B, NB, 2 column halves, Hq, F_ROWS] or null
   int N, NB, Hq, Hkv, units;
   float scale;
@@ -216,15 +216,16 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
             fs * ((dot[0] + dot[1]) + (dot[2] + dot[3]));
       if (d.hh == rep - 1) {
         // dCarry rows of this slab: tensor memory -> HBM
-        float* dst = a.dcarry + (((size_t)d.u * a.NB + d.c) * F_ROWS + f) * EP + col0;
+        float* dst = a.dcarry + ((size_t)d.u * a.NB + d.c) * F_ROWS * EP + state_inc_offset(f, col0);
         float vv[DS_COLS / 8][8];
 #pragma unroll
         for (int r = 0; r < DS_COLS / 8; ++r) tmem_ld8(tacc + lane_off + 8 * r, vv[r]);
         tmem_ld_wait();
 #pragma unroll
         for (int r = 0; r < DS_COLS / 8; ++r) {
-          *reinterpret_cast<float4*>(dst + 8 * r) = make_float4(vv[r][0], vv[r][1], vv[r][2], vv[r][3]);
-          *reinterpret_cast<float4*>(dst + 8 * r + 4) = make_float4(vv[r][4], vv[r][5], vv[r][6], vv[r][7]);
+          // the next group of 8 columns of this row lies one 128-row block further
+          *reinterpret_cast<float4*>(dst + r * 1024) = make_float4(vv[r][0], vv[r][1], vv[r][2], vv[r][3]);
+          *reinterpret_cast<float4*>(dst + r * 1024 + 4) = make_float4(vv[r][4], vv[r][5], vv[r][6], vv[r][7]);
         }
       }
       d.next(rep, a.NB);
