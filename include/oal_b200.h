@@ -152,7 +152,7 @@ int oal_backward(const OalProblem* problem, const void* q, const void* k, const 
  *   state_total / dstate_total: fp32 [batch*kv_heads, OAL_STATE_ROWS, OAL_E_PAD]
  *   workspace: oal_workspace_bytes(problem, 0) for the forward call, (problem, 1) for the backward.
  */
-#define OAL_STATE_ROWS 2176
+#define OAL_STATE_ROWS 2432
 int oal_forward_local_state(const OalProblem* problem, const void* k, const void* v, float* state_total,
                             void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 int oal_backward_local_state(const OalProblem* problem, const void* q, const int32_t* dim_perm,
@@ -170,7 +170,7 @@ int oal_backward_local_state(const OalProblem* problem, const void* q, const int
  * memory is frozen after start-up (serving processes with a pre-carved pool, plugins run from
  * allocator-free callbacks).
  *   Limits: batch * kv_heads * ceil(seq_len / 128) <= 16 and q_heads <= 64; larger problems return
- *   OAL_ERR_WORKSPACE.  The array (about 11.7 MB) is resident on every GPU that loads the library.
+ *   OAL_ERR_WORKSPACE.  The array (about 13.1 MB) is resident on every GPU that loads the library.
  *   The first call on each device resolves the array's device address; make that call outside any
  *   stream capture, with the device current.
  *   All calls on a device share the array and it keeps the previous call's contents; every element

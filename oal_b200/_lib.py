@@ -21,7 +21,7 @@ DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 PRECISION_CODES = {"fp32_ieee": 0, "bf16_tensorcore": 1}
 
 GRAD_Q, GRAD_K, GRAD_V, GRAD_COEF, GRAD_REUSE_STATE_STAGE = 1, 2, 4, 8, 16
-STATE_ROWS = 2176
+STATE_ROWS = 2432
 STATUS_NONFINITE, STATUS_DENOMINATOR, STATUS_WAIT_TIMEOUT, STATUS_BAD_LAYOUT = 1, 2, 4, 8
 
 # every symbol include/oal_b200.h declares

@@ -153,7 +153,7 @@ BackwardSpaceTC carve_backward_tc(const OalProblem* p, void* ws) {
   const size_t units = (size_t)p->batch * p->kv_heads, nb = chunk_count(p);
   const size_t qrows = (size_t)p->batch * p->q_heads * p->seq_len;
   const size_t krows = (size_t)p->batch * p->kv_heads * p->seq_len;
-  const size_t slab_image = oal::state_image_bytes_per_chunk() / 17;
+  const size_t slab_image = oal::state_slab_image_bytes();
   s.g = c.take<float>(qrows * oal::EP);
   s.coef_pairs = c.take<float>((size_t)p->batch * p->q_heads * oal::pairs_tiles(p->seq_len) * oal::NCOEF);
   s.gimg = c.take<char>(2 * (size_t)p->batch * p->q_heads * nb * slab_image);   // hi image, then lo image
@@ -187,7 +187,7 @@ int backward_state_stage(const OalProblem* p, const void* q, const int32_t* dim_
                             p->batch * p->q_heads, p->seq_len, nb, st); }
   if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
   { LaunchScope scope("coef_table", st);
-    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, s.coef_table, st); }
+    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, p->scale, s.coef_table, st); }
   if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
   if (mask & (OAL_GRAD_K | OAL_GRAD_V | OAL_GRAD_COEF)) {
     { LaunchScope scope("dstate_heads", st);
@@ -303,7 +303,7 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
   const int units = p->batch * p->kv_heads, nb = chunk_count(p);
   cudaError_t e;
   { LaunchScope scope("coef_table", st);
-    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, s.coef_table, st); }
+    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, p->scale, s.coef_table, st); }
   if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
   { LaunchScope scope("state_update", st); e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
@@ -311,7 +311,7 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
   if (e != cudaSuccess) return fail_cuda(e, "state scan kernel");
   { LaunchScope scope("cross_read_q", st);
     e = oal::cross_read(true, q, saved_state, s.coef_table, num, den, p->batch, p->q_heads,
-                        p->q_heads / p->kv_heads, p->seq_len, nb, p->scale, status, st); }
+                        p->q_heads / p->kv_heads, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
   if (p->groups <= 8) {
     { LaunchScope scope("intra_forward", st);
@@ -403,7 +403,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     if (want_q) {
       { LaunchScope scope("feature_grad_q", st);
         e = oal::feature_grad(true, q, s.gimg, nullptr, saved_state, s.coef_table, s.dq_cross, p->batch, p->q_heads,
-                              rep, p->seq_len, nb, p->scale, p->scale, status, st); }
+                              rep, p->seq_len, nb, status, st); }
       if (e != cudaSuccess) return fail_cuda(e, "query feature gradient kernel");
     }
     if (tc_intra) {
@@ -433,13 +433,13 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     if (want_k) {
       { LaunchScope scope("feature_grad_k", st);
         e = oal::feature_grad(false, k, nullptr, v, s.dt_img, nullptr, s.dk_cross, p->batch, p->kv_heads, 1,
-                              p->seq_len, nb, 1.f, 1.f, status, st); }
+                              p->seq_len, nb, status, st); }
       if (e != cudaSuccess) return fail_cuda(e, "key feature gradient kernel");
     }
     if (want_v) {
       { LaunchScope scope("cross_read_k", st);
         e = oal::cross_read(false, k, s.dt_img, nullptr, s.dv_cross, nullptr, p->batch, p->kv_heads, 1, p->seq_len,
-                            nb, 1.f, status, st); }
+                            nb, status, st); }
       if (e != cudaSuccess) return fail_cuda(e, "key cross read kernel");
     }
     if (tc_intra) {
@@ -518,12 +518,12 @@ int oal_backward_local_state(const OalProblem* p, const void* q, const int32_t* 
 // table and the per-chunk state increments -- in the file-scope device array below.  The array has
 // a fixed size, so the entry point only accepts problems up to kStaticMaxUnitChunks (batch x KV heads
 // x 128-token chunks) and kStaticMaxHeads query heads; every GPU that loads the library holds the
-// array (about 11.7 MB) until the process exits.
+// array (about 13.1 MB) until the process exits.
 // ---------------------------------------------------------------------------------------------
 constexpr int kStaticMaxUnitChunks = 16;
 constexpr int kStaticMaxHeads = 64;
-constexpr size_t kStaticStateFloats = (size_t)kStaticMaxUnitChunks * 2176 * OAL_E_PAD;
-constexpr size_t kStaticTableFloats = (size_t)kStaticMaxHeads * 2176;
+constexpr size_t kStaticStateFloats = (size_t)kStaticMaxUnitChunks * OAL_STATE_ROWS * OAL_E_PAD;
+constexpr size_t kStaticTableFloats = (size_t)kStaticMaxHeads * OAL_STATE_ROWS;
 static __device__ __align__(256) float g_static_scratch[kStaticTableFloats + kStaticStateFloats];
 
 namespace {
@@ -573,7 +573,7 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   { LaunchScope scope("coef_table", st);
-    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, coef_table, st); }
+    e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, p->scale, coef_table, st); }
   if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
   { LaunchScope scope("state_update", st); e = oal::state_update(k, v, ds, units, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
@@ -581,7 +581,7 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
   if (e != cudaSuccess) return fail_cuda(e, "state scan kernel");
   { LaunchScope scope("cross_read_q", st);
     e = oal::cross_read(true, q, saved_state, coef_table, num, den, p->batch, p->q_heads, p->q_heads / p->kv_heads,
-                        p->seq_len, nb, p->scale, status, st); }
+                        p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
   if (p->groups <= 8) {
     { LaunchScope scope("intra_forward", st);

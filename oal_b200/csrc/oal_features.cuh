@@ -3,16 +3,21 @@
 // The reference materialises phi_k = [1, k_d, k_r k_c (r >= c)] and
 // phi_q = [A, B_{g(d)} q_d, m C_{g(r)g(c)} q_r q_c] as [tokens, 2145] matrices in HBM
 // (oal_attention/hd_block_gemm_feature_forward.py:225-253, :373-385; pair order
-// oal_attention/hd_block_gemm_cache.py:105-121).  Here a feature tile only ever exists
-// in shared memory: each thread owns one token, keeps its 64-element row in registers
-// and emits 16-byte chunks of 8 consecutive features as bf16.  The feature order is
-// internal (the running state is never exposed), chosen so that every index below is a
-// compile-time constant:
-//   chunks   0..259  pair features p = 8*chunk + j, p = r(r+1)/2 + c  (r >= c)
-//   chunks 260..267  linear features d = 8*(chunk-260) + j
-//   chunk  268       [constant, 0 x 7]
-//   chunks 269..271  zero padding
-// 16 chunks (128 features) form a slab: 17 slabs, 2176 feature rows.
+// oal_attention/hd_block_gemm_cache.py:105-121).  Here a feature tile only ever exists in
+// shared memory, as 16-byte chunks of 8 features in bf16.  The feature order is internal (the
+// running state is never exposed) and chosen so that a chunk multiplies one row element with eight
+// adjacent column elements, which the packed bf16 / fp32 multiplies do two at a time:
+//   pair chunk (cb, r), r = 8 cb .. 63:  features x[r] * x[8 cb + j], j = 0..7, zero where
+//       8 cb + j > r.  Chunks are ordered by cb, then r: while cb stays the same the eight
+//       column values stay in registers and only x[r] changes.
+//       chunk index = 64 cb - 4 cb (cb - 1) + (r - 8 cb); 288 pair chunks
+//   chunks 288..295  linear features d = 8 (chunk - 288) + j
+//   chunk  296       [constant, 0 x 7]
+//   chunks 297..303  zero padding
+// 16 chunks (128 features) form a slab: 19 slabs, 2432 feature rows.
+// Each thread owns one token and keeps its row in registers; every index in the generated code is a
+// compile-time constant.  Pairs (x[8 cb + 2k], x[8 cb + 2k + 1]) are adjacent in the packed row, so a
+// chunk is one broadcast of x[r] and four packed multiplies.
 #pragma once
 
 #include <utility>
@@ -22,12 +27,12 @@
 
 namespace oal {
 
-constexpr int F_PAIR_CHUNKS = 260;
-constexpr int F_LIN_CHUNK0 = 260;
-constexpr int F_CONST_CHUNK = 268;
-constexpr int F_CHUNKS = 272;
-constexpr int F_SLABS = 17;
-constexpr int F_ROWS = F_SLABS * 128;          // 2176
+constexpr int F_PAIR_CHUNKS = 288;
+constexpr int F_LIN_CHUNK0 = 288;
+constexpr int F_CONST_CHUNK = 296;
+constexpr int F_CHUNKS = 304;
+constexpr int F_SLABS = 19;
+constexpr int F_ROWS = F_SLABS * 128;          // 2432
 constexpr int CT = 128;                        // tokens per chunk of the scan
 constexpr int SLAB_A_BYTES = 128 * CT * 2;     // feature slab tile  [16 chunks][128 tokens][8] bf16
 constexpr int SLAB_S_BYTES = (EP / 8) * 128 * 16;   // state slab image [10][128 features][8 e] bf16
@@ -39,157 +44,220 @@ __host__ __device__ constexpr size_t state_inc_offset(int f, int e) {
   return ((size_t)((f >> 7) * (EP / 8) + (e >> 3)) * 128 + (f & 127)) * 8 + (e & 7);
 }
 
-struct RC {
-  int r, c;
+// Position in the pair-chunk order.
+struct PairCursor {
+  int r, cb;
+  __host__ __device__ constexpr void seek(int q) {      // q < F_PAIR_CHUNKS
+    cb = 0;
+    int base = 0;
+    while (q >= base + HD - 8 * cb) {
+      base += HD - 8 * cb;
+      ++cb;
+    }
+    r = 8 * cb + (q - base);
+  }
+  // number of features of the chunk that exist (c <= r); 8 or more means all
+  __host__ __device__ constexpr int valid() const { return r - 8 * cb + 1; }
 };
-__host__ __device__ constexpr RC pair_rc(int p) {
-  int r = 0;
-  while ((r + 1) * (r + 2) / 2 <= p) ++r;
-  return RC{r, p - r * (r + 1) / 2};
+__host__ __device__ constexpr PairCursor pair_pos(int q) {
+  PairCursor pc{0, 0};
+  pc.seek(q);
+  return pc;
 }
 
-// One chunk of 8 features of the token whose row is x[64].  QUERY multiplies by the
-// per-head coefficient table (same feature order, fp32, in shared memory).
-template <int CH, bool QUERY>
-__device__ __forceinline__ uint4 feature_chunk(const float (&x)[HD], const float* coef) {
-  float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  if constexpr (CH < F_PAIR_CHUNKS) {
-    constexpr RC p0 = pair_rc(8 * CH + 0), p1 = pair_rc(8 * CH + 1), p2 = pair_rc(8 * CH + 2),
-                 p3 = pair_rc(8 * CH + 3), p4 = pair_rc(8 * CH + 4), p5 = pair_rc(8 * CH + 5),
-                 p6 = pair_rc(8 * CH + 6), p7 = pair_rc(8 * CH + 7);
-    f[0] = x[p0.r] * x[p0.c]; f[1] = x[p1.r] * x[p1.c]; f[2] = x[p2.r] * x[p2.c]; f[3] = x[p3.r] * x[p3.c];
-    f[4] = x[p4.r] * x[p4.c]; f[5] = x[p5.r] * x[p5.c]; f[6] = x[p6.r] * x[p6.c]; f[7] = x[p7.r] * x[p7.c];
-  } else if constexpr (CH < F_CONST_CHUNK) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) f[j] = x[8 * (CH - F_LIN_CHUNK0) + j];
-  } else if constexpr (CH == F_CONST_CHUNK) {
-    f[0] = 1.f;
-#pragma unroll
-    for (int j = 1; j < 8; ++j) f[j] = 0.f;
-  } else {
-    return make_uint4(0u, 0u, 0u, 0u);
+// What feature row f is: kind 0 pair (r, c; `live` false for the zero entries above the diagonal),
+// 1 linear (r = dimension), 2 constant, 3 padding.
+struct FeatureId {
+  int kind, r, c;
+  bool live;
+};
+__host__ __device__ inline FeatureId feature_id(int f) {
+  const int q = f >> 3, j = f & 7;
+  FeatureId id{3, 0, 0, false};
+  if (q < F_PAIR_CHUNKS) {
+    const PairCursor pc = pair_pos(q);
+    id.kind = 0;
+    id.r = pc.r;
+    id.c = 8 * pc.cb + j;
+    id.live = id.c <= id.r;
+  } else if (q < F_CONST_CHUNK) {
+    id.kind = 1;
+    id.r = 8 * (q - F_LIN_CHUNK0) + j;
+    id.live = true;
+  } else if (q == F_CONST_CHUNK && j == 0) {
+    id.kind = 2;
+    id.live = true;
   }
-  if constexpr (QUERY) {
-    const float4 c0 = *reinterpret_cast<const float4*>(coef + 8 * CH);
-    const float4 c1 = *reinterpret_cast<const float4*>(coef + 8 * CH + 4);
-    f[0] *= c0.x; f[1] *= c0.y; f[2] *= c0.z; f[3] *= c0.w;
-    f[4] *= c1.x; f[5] *= c1.y; f[6] *= c1.z; f[7] *= c1.w;
-  }
-  return make_uint4(umma::pack_bf16(f[0], f[1]), umma::pack_bf16(f[2], f[3]), umma::pack_bf16(f[4], f[5]),
-                    umma::pack_bf16(f[6], f[7]));
+  return id;
 }
 
-// ---- coefficient-free features straight from the packed bf16 row ------------------------------
-// xp[k] holds (x[2k], x[2k+1]).  The product of two bf16 values rounded once to bf16 is what the
-// fp32 multiply followed by a conversion gives, so the packed multiply yields the same bits at two
-// features per instruction and needs no unpacked copy of the row.
-template <int A, int B>
-__device__ __forceinline__ uint32_t pick2(const uint32_t (&xp)[HD / 2]) {   // (x[A], x[B])
-  if constexpr ((A & 1) == 0 && B == A + 1) {
-    return xp[A / 2];
-  } else {
-    constexpr uint32_t lo = (A & 1) * 2, hi = 4 + (B & 1) * 2;
-    return __byte_perm(xp[A / 2], xp[B / 2], lo | ((lo + 1) << 4) | (hi << 8) | ((hi + 1) << 12));
-  }
+// Power of the query scale folded into the per-head coefficient table: the query-side kernels work
+// on the unscaled q, so pair coefficients carry scale^2 and linear ones scale.
+__host__ __device__ inline float feature_scale_factor(int f, float scale) {
+  return f < 8 * F_PAIR_CHUNKS ? scale * scale : (f < 8 * F_CONST_CHUNK ? scale : 1.f);
 }
+
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
-template <int CH>
-__device__ __forceinline__ uint4 feature_chunk_bf16(const uint32_t (&xp)[HD / 2]) {
-  if constexpr (CH < F_PAIR_CHUNKS) {
-    constexpr RC p0 = pair_rc(8 * CH + 0), p1 = pair_rc(8 * CH + 1), p2 = pair_rc(8 * CH + 2),
-                 p3 = pair_rc(8 * CH + 3), p4 = pair_rc(8 * CH + 4), p5 = pair_rc(8 * CH + 5),
-                 p6 = pair_rc(8 * CH + 6), p7 = pair_rc(8 * CH + 7);
-    return make_uint4(mul_bf16x2(pick2<p0.r, p1.r>(xp), pick2<p0.c, p1.c>(xp)),
-                      mul_bf16x2(pick2<p2.r, p3.r>(xp), pick2<p2.c, p3.c>(xp)),
-                      mul_bf16x2(pick2<p4.r, p5.r>(xp), pick2<p4.c, p5.c>(xp)),
-                      mul_bf16x2(pick2<p6.r, p7.r>(xp), pick2<p6.c, p7.c>(xp)));
-  } else if constexpr (CH < F_CONST_CHUNK) {
-    constexpr int k = 4 * (CH - F_LIN_CHUNK0);
+// ---- coefficient-free chunk from the packed bf16 row  xp[k] = (x[2k], x[2k+1]) -------------------
+// The product of two bf16 values rounded once to bf16 is what an fp32 multiply followed by a
+// conversion gives, so the packed multiply yields those bits at two features per instruction.
+template <int Q>
+__device__ __forceinline__ uint4 raw_chunk(const uint32_t (&xp)[HD / 2]) {
+  if constexpr (Q < F_PAIR_CHUNKS) {
+    constexpr PairCursor pc = pair_pos(Q);
+    constexpr int nv = pc.valid();
+    const uint32_t w = xp[pc.r / 2];
+    const uint32_t xr2 = __byte_perm(w, w, (pc.r & 1) ? 0x3232u : 0x1010u);
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t mask = (2 * k < nv ? 0x0000FFFFu : 0u) | (2 * k + 1 < nv ? 0xFFFF0000u : 0u);
+      o[k] = mask == 0u ? 0u : (mul_bf16x2(xr2, xp[4 * pc.cb + k]) & mask);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+  } else if constexpr (Q < F_CONST_CHUNK) {
+    constexpr int k = 4 * (Q - F_LIN_CHUNK0);
     return make_uint4(xp[k], xp[k + 1], xp[k + 2], xp[k + 3]);
-  } else if constexpr (CH == F_CONST_CHUNK) {
+  } else if constexpr (Q == F_CONST_CHUNK) {
     return make_uint4(0x00003F80u, 0u, 0u, 0u);   // bf16(1.0) in element 0
   } else {
     return make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
-template <int S, int... J>
-__device__ __forceinline__ void slab_bf16_impl(const uint32_t (&xp)[HD / 2], uint4* tile, int token,
-                                               std::integer_sequence<int, J...>) {
-  ((tile[J * CT + token] = feature_chunk_bf16<S * 16 + J>(xp)), ...);
-}
-
-// All 16 chunks of slab s of one token (coefficient-free, unscaled) into the slab tile.
-__device__ __forceinline__ void write_slab_bf16(int s, const uint32_t (&xp)[HD / 2], uint4* tile, int token) {
-#define OAL_SLAB_CASE(S)                                                               \
-  case S:                                                                              \
-    slab_bf16_impl<S>(xp, tile, token, std::make_integer_sequence<int, 16>{});          \
-    break;
-  switch (s) {
-    OAL_SLAB_CASE(0) OAL_SLAB_CASE(1) OAL_SLAB_CASE(2) OAL_SLAB_CASE(3) OAL_SLAB_CASE(4) OAL_SLAB_CASE(5)
-    OAL_SLAB_CASE(6) OAL_SLAB_CASE(7) OAL_SLAB_CASE(8) OAL_SLAB_CASE(9) OAL_SLAB_CASE(10) OAL_SLAB_CASE(11)
-    OAL_SLAB_CASE(12) OAL_SLAB_CASE(13) OAL_SLAB_CASE(14) OAL_SLAB_CASE(15) OAL_SLAB_CASE(16)
-    default: break;
+// ---- chunk times the per-head coefficient table (query side of the forward) -----------------------
+//   xq   : fp32 row as packed pairs, xq[k] = (x[2k], x[2k+1]), unscaled
+//   coef : table of the head in feature order, query scale folded in, zero above the diagonal and in
+//          the padding; every lane reads the same address, so global memory through L1 is fine
+__device__ __forceinline__ uint4 pack_pairs_bf16(const f32x2 (&f)[4]) {
+  uint32_t o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float lo, hi;
+    f2_unpack(f[k], lo, hi);
+    o[k] = umma::pack_bf16(lo, hi);
   }
-#undef OAL_SLAB_CASE
+  return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-// Power of the query scale a coefficient-free, unscaled feature row lacks: pair features scale^2,
-// linear features scale, the constant feature 1.
-__device__ __forceinline__ float feature_scale_factor(int f, float scale) {
-  return f < 8 * F_PAIR_CHUNKS ? scale * scale : (f < 8 * F_CONST_CHUNK ? scale : 1.f);
-}
-
-// Threads per CTA of the kernels that generate feature slabs: 128 tokens x GEN_PARTS threads per
-// token, each thread writing 16 / GEN_PARTS chunks of a slab.
-constexpr int GEN_THREADS = 256;
-constexpr int GEN_PARTS = GEN_THREADS / CT;
-constexpr int GEN_CHUNKS = 16 / GEN_PARTS;
-
-template <int S, int PART, bool QUERY, int... J>
-__device__ __forceinline__ void part_slab_impl(const float (&x)[HD], const float* coef, uint4* tile, int token,
-                                               std::integer_sequence<int, J...>) {
-  ((tile[(PART * GEN_CHUNKS + J) * CT + token] = feature_chunk<S * 16 + PART * GEN_CHUNKS + J, QUERY>(x, coef)), ...);
-}
-
-template <int S, bool QUERY>
-__device__ __forceinline__ void part_slab_select(int part, const float (&x)[HD], const float* coef, uint4* tile,
-                                                 int token) {
-  using Seq = std::make_integer_sequence<int, GEN_CHUNKS>;
-  if constexpr (GEN_PARTS == 2) {
-    if (part == 0) part_slab_impl<S, 0, QUERY>(x, coef, tile, token, Seq{});
-    else part_slab_impl<S, 1, QUERY>(x, coef, tile, token, Seq{});
-  } else {
-    switch (part) {
-      case 0: part_slab_impl<S, 0, QUERY>(x, coef, tile, token, Seq{}); break;
-      case 1: part_slab_impl<S, 1, QUERY>(x, coef, tile, token, Seq{}); break;
-      case 2: part_slab_impl<S, 2 % GEN_PARTS, QUERY>(x, coef, tile, token, Seq{}); break;
-      default: part_slab_impl<S, 3 % GEN_PARTS, QUERY>(x, coef, tile, token, Seq{}); break;
+template <int Q>
+__device__ __forceinline__ uint4 coef_chunk(const f32x2 (&xq)[HD / 2], const float* coef) {
+  if constexpr (Q <= F_CONST_CHUNK) {
+    const ulonglong2 ca = *reinterpret_cast<const ulonglong2*>(coef + 8 * Q);
+    const ulonglong2 cb2 = *reinterpret_cast<const ulonglong2*>(coef + 8 * Q + 4);
+    const f32x2 cf[4] = {ca.x, ca.y, cb2.x, cb2.y};
+    f32x2 f[4];
+    if constexpr (Q < F_PAIR_CHUNKS) {
+      constexpr PairCursor pc = pair_pos(Q);
+      float lo, hi;
+      f2_unpack(xq[pc.r / 2], lo, hi);
+      const f32x2 xr2 = f2_bcast((pc.r & 1) ? hi : lo);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) f[k] = f2_mul(f2_mul(xr2, xq[4 * pc.cb + k]), cf[k]);
+    } else if constexpr (Q < F_CONST_CHUNK) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) f[k] = f2_mul(xq[4 * (Q - F_LIN_CHUNK0) + k], cf[k]);
+    } else {
+      f[0] = cf[0];          // (A, 0): the table is zero in the padding
+      f[1] = f[2] = f[3] = 0ull;
     }
+    return pack_pairs_bf16(f);
+  } else {
+    return make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
-// Write this thread's chunks of slab s of its token into the slab tile ([16 chunks][128 tokens] x
-// 16 bytes).  s and part are runtime values; the bodies are static.
-template <bool QUERY>
-__device__ __forceinline__ void write_half_slab(int s, int part, const float (&x)[HD], const float* coef,
-                                                uint4* tile, int token) {
-#define OAL_SLAB_CASE(S)                                      \
-  case S:                                                     \
-    part_slab_select<S, QUERY>(part, x, coef, tile, token);   \
-    break;
-  switch (s) {
-    OAL_SLAB_CASE(0) OAL_SLAB_CASE(1) OAL_SLAB_CASE(2) OAL_SLAB_CASE(3) OAL_SLAB_CASE(4) OAL_SLAB_CASE(5)
-    OAL_SLAB_CASE(6) OAL_SLAB_CASE(7) OAL_SLAB_CASE(8) OAL_SLAB_CASE(9) OAL_SLAB_CASE(10) OAL_SLAB_CASE(11)
-    OAL_SLAB_CASE(12) OAL_SLAB_CASE(13) OAL_SLAB_CASE(14) OAL_SLAB_CASE(15) OAL_SLAB_CASE(16)
-    default: break;
+// Threads per CTA of the kernels whose threads split a slab as (token, half of the 16 chunks).
+constexpr int GEN_THREADS = 256;
+
+// Chunks [J0, J0 + NJ) of slab S of one token into the slab tile ([16 chunks][128 tokens] x 16 bytes);
+// `tile` points at the token's column.
+template <int S, int J0, int... J>
+__device__ __forceinline__ void raw_chunks_impl(const uint32_t (&xp)[HD / 2], uint4* tile,
+                                                std::integer_sequence<int, J...>) {
+  ((tile[(J0 + J) * CT] = raw_chunk<S * 16 + J0 + J>(xp)), ...);
+}
+template <int S, int J0, int... J>
+__device__ __forceinline__ void coef_chunks_impl(const f32x2 (&xq)[HD / 2], const float* coef, uint4* tile,
+                                                 std::integer_sequence<int, J...>) {
+  ((tile[(J0 + J) * CT] = coef_chunk<S * 16 + J0 + J>(xq, coef)), ...);
+}
+
+#define OAL_SLAB_SWITCH(s, CASE)                                                                      \
+  switch (s) {                                                                                        \
+    CASE(0) CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8) CASE(9) CASE(10) CASE(11) \
+    CASE(12) CASE(13) CASE(14) CASE(15) CASE(16) CASE(17) CASE(18)                                    \
+    default: break;                                                                                   \
   }
-#undef OAL_SLAB_CASE
+static_assert(F_SLABS == 19, "OAL_SLAB_SWITCH enumerates the slabs");
+
+// All 16 chunks of slab s (s is a run-time value; the bodies are static).
+__device__ __forceinline__ void write_slab_raw(int s, const uint32_t (&xp)[HD / 2], uint4* tile) {
+#define OAL_CASE(S) case S: raw_chunks_impl<S, 0>(xp, tile, std::make_integer_sequence<int, 16>{}); break;
+  OAL_SLAB_SWITCH(s, OAL_CASE)
+#undef OAL_CASE
+}
+// Half of the chunks of slab s: half 0 = chunks 0..7, half 1 = chunks 8..15.
+template <int J0>
+__device__ __forceinline__ void write_half_slab_raw_impl(int s, const uint32_t (&xp)[HD / 2], uint4* tile) {
+#define OAL_CASE(S) case S: raw_chunks_impl<S, J0>(xp, tile, std::make_integer_sequence<int, 8>{}); break;
+  OAL_SLAB_SWITCH(s, OAL_CASE)
+#undef OAL_CASE
+}
+__device__ __forceinline__ void write_half_slab_raw(int s, int half, const uint32_t (&xp)[HD / 2], uint4* tile) {
+  if (half == 0) write_half_slab_raw_impl<0>(s, xp, tile);
+  else write_half_slab_raw_impl<8>(s, xp, tile);
+}
+__device__ __forceinline__ void write_half_slab_coef(int s, int half, const f32x2 (&xq)[HD / 2], const float* coef,
+                                                     uint4* tile) {
+#define OAL_CASE(S)                                                                                 \
+  case S:                                                                                           \
+    if (half == 0) coef_chunks_impl<S, 0>(xq, coef, tile, std::make_integer_sequence<int, 8>{});    \
+    else coef_chunks_impl<S, 8>(xq, coef, tile, std::make_integer_sequence<int, 8>{});              \
+    break;
+  OAL_SLAB_SWITCH(s, OAL_CASE)
+#undef OAL_CASE
+}
+
+// The row stays the same while a kernel walks the slabs, and every feature is a pure function of it:
+// without this barrier the compiler hoists the features of all slabs out of the slab loop and spills
+// them.  Costs no instruction.
+__device__ __forceinline__ void keep_in_loop(uint32_t (&xp)[HD / 2]) {
+#pragma unroll
+  for (int w = 0; w < HD / 2; ++w) asm volatile("" : "+r"(xp[w]));
+}
+__device__ __forceinline__ void keep_in_loop(f32x2 (&xq)[HD / 2]) {
+#pragma unroll
+  for (int w = 0; w < HD / 2; ++w) asm volatile("" : "+l"(xq[w]));
+}
+
+// Row `i` (or zeros when i >= N) of a bf16 [.., N, 64] tensor as packed words / as fp32 pairs.
+__device__ __forceinline__ void load_row_packed(uint32_t (&xp)[HD / 2], const __nv_bfloat16* base, int i, int N) {
+  if (i < N) {
+    const uint4* p = reinterpret_cast<const uint4*>(base + (size_t)i * HD);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 t = p[c];
+      xp[4 * c] = t.x;
+      xp[4 * c + 1] = t.y;
+      xp[4 * c + 2] = t.z;
+      xp[4 * c + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int w = 0; w < HD / 2; ++w) xp[w] = 0u;
+  }
+}
+__device__ __forceinline__ void unpack_row(const uint32_t (&xp)[HD / 2], f32x2 (&xq)[HD / 2]) {
+#pragma unroll
+  for (int w = 0; w < HD / 2; ++w) xq[w] = f2_pack(bf16_lo(xp[w]), bf16_hi(xp[w]));
 }
 
 // Row `i` (or zeros when i >= N) of a bf16 [.., N, 64] tensor into registers, times mul.

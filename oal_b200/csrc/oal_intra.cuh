@@ -19,8 +19,6 @@ constexpr int KT = 16;                       // keys (or queries) per tile of th
 constexpr int IG = OAL_IG;                   // groups handled by this build of the kernels
 constexpr int DP_MAX = 64 + (IG - 1) * 16;   // padded dims: every group rounded up to 16 (176 for 8 groups)
 
-typedef unsigned long long f32x2;   // two floats in one 64-bit register (packed fp32 arithmetic)
-
 // Padded, group-sorted dimension layout of one head.
 struct PaddedGroups {
   int k16_start[IG + 1];     // first 16-dim slab of group g; k16_start[IG] = number of slabs
@@ -107,28 +105,6 @@ __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
                : "memory");
 #pragma unroll
   for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Packed fp32 pairs (sm_100 executes add / mul / fma on two floats held in one 64-bit register):
-// the per-pair combine is issue-bound, so two columns per instruction is the lever that matters.
-__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
-  f32x2 r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ f32x2 f2_bcast(float a) { return f2_pack(a, a); }
-__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
-  f32x2 d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
-  f32x2 d;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
 }
 
 // Issue the per-group score MMAs  S_g[128 x KT] = X_g (128 rows) . Y_g (KT rows)^T  for one tile.

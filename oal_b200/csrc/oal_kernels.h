@@ -42,18 +42,19 @@ cudaError_t reduce_coefs(const float* p0, int tiles0, const float* extra, int B,
                          float* dA, float* dB, float* dC, cudaStream_t st);
 
 // ---- tensor-core state kernels (oal_state.cu) ---------------------------------------
-size_t state_rows();                       // feature rows of the running state (2176)
-size_t state_image_bytes_per_chunk();      // bytes of one bf16 state image [17 slabs][10][128][8]
+size_t state_rows();                       // feature rows of the running state (2432)
+size_t state_image_bytes_per_chunk();      // bytes of one bf16 state image [19 slabs][10][128][8]
+size_t state_slab_image_bytes();           // bytes of one slab image [10][128][8] bf16
 
 cudaError_t build_coef_table(const int32_t* dim_perm, const int32_t* group_start, const float* A,
-                             const float* Bc, const float* Cc, int Hq, int G, float* table, cudaStream_t st);
+                             const float* Bc, const float* Cc, int Hq, int G, float scale, float* table,
+                             cudaStream_t st);
 cudaError_t state_update(const void* k, const void* v, float* ds, int units, int N, int NB, int32_t* status,
                          cudaStream_t st);
 cudaError_t state_scan(const float* ds, void* image, const float* state_in, float* state_total, int units,
                        int NB, int reverse, cudaStream_t st);
 cudaError_t cross_read(bool query, const void* x, const void* image, const float* coef_table, float* out64,
-                       float* out1, int B, int H, int rep, int N, int NB, float mul, int32_t* status,
-                       cudaStream_t st);
+                       float* out1, int B, int H, int rep, int N, int NB, int32_t* status, cudaStream_t st);
 
 
 // ---- tensor-core backward kernels (oal_state_bwd.cu) ----------------------------------
@@ -61,8 +62,8 @@ cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img,
                          float* dcarry, float* dcoef_partial, int B, int Hq, int Hkv, int N, int NB, float scale,
                          int32_t* status, cudaStream_t st);
 cudaError_t feature_grad(bool query, const void* x, const void* gimg, const void* v, const void* image,
-                         const float* coef_table, float* dx, int B, int H, int rep, int N, int NB, float mul,
-                         float outmul, int32_t* status, cudaStream_t st);
+                         const float* coef_table, float* dx, int B, int H, int rep, int N, int NB, int32_t* status,
+                         cudaStream_t st);
 cudaError_t dcoef_reduce(const float* partial, int outer, int Hq, const int32_t* dim_perm,
                          const int32_t* group_start, float* dcoef, float* slots, cudaStream_t st);
 cudaError_t norm_vjp_image(const void* grad_out, int out_dt, const float* grad_num, const float* grad_den,

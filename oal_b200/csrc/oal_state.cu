@@ -18,15 +18,17 @@ namespace {
 
 using namespace umma;
 
-// slabs are processed in four groups so that five 80-column accumulators fit in tensor memory
-__device__ __forceinline__ int group_first_slab(int g) { return g == 0 ? 0 : 1 + 4 * g; }   // 0,5,9,13
-__device__ __forceinline__ int group_slab_count(int g) { return g == 0 ? 5 : 4; }
+// the 19 slabs are processed by four CTAs per (chunk, unit): slab groups 5, 5, 5, 4
+constexpr int SU_GROUPS = 4;
+__device__ __forceinline__ int group_first_slab(int g) { return 5 * g; }
+__device__ __forceinline__ int group_slab_count(int g) { return g < 3 ? 5 : F_SLABS - 15; }
 
 // ---------------------------------------------------------------------------
-// per-head coefficient table in feature order (fp32 [Hq][F_ROWS])
+// per-head coefficient table in feature order (fp32 [Hq][F_ROWS]), query scale folded in:
+// pair rows carry scale^2, linear rows scale (the query-side kernels read the unscaled q)
 // ---------------------------------------------------------------------------
 __global__ void coef_table_kernel(const int32_t* dim_perm, const int32_t* group_start, const float* A,
-                                  const float* Bc, const float* Cc, int G, float* table) {
+                                  const float* Bc, const float* Cc, int G, float scale, float* table) {
   __shared__ int gdim[HD];
   const int h = blockIdx.x;
   if (threadIdx.x < HD) {
@@ -38,25 +40,22 @@ __global__ void coef_table_kernel(const int32_t* dim_perm, const int32_t* group_
   __syncthreads();
   for (int f = threadIdx.x; f < F_ROWS; f += blockDim.x) {
     float v = 0.f;
-    if (f < F_PAIR_CHUNKS * 8) {
-      int r = (int)((sqrtf(8.f * f + 1.f) - 1.f) * 0.5f);
-      while ((r + 1) * (r + 2) / 2 <= f) ++r;
-      while (r * (r + 1) / 2 > f) --r;
-      const int c = f - r * (r + 1) / 2;
-      const int gr = min(gdim[r], G - 1), gc = min(gdim[c], G - 1);
-      v = (r == c ? 1.f : 2.f) * Cc[((size_t)h * G + gr) * G + gc];
-    } else if (f < F_CONST_CHUNK * 8) {
-      v = Bc[h * G + min(gdim[f - F_LIN_CHUNK0 * 8], G - 1)];
-    } else if (f == F_CONST_CHUNK * 8) {
+    const FeatureId id = feature_id(f);
+    if (id.kind == 0 && id.live) {
+      const int gr = min(gdim[id.r], G - 1), gc = min(gdim[id.c], G - 1);
+      v = (id.r == id.c ? 1.f : 2.f) * Cc[((size_t)h * G + gr) * G + gc];
+    } else if (id.kind == 1) {
+      v = Bc[h * G + min(gdim[id.r], G - 1)];
+    } else if (id.kind == 2) {
       v = A[h];
     }
-    table[(size_t)h * F_ROWS + f] = v;
+    table[(size_t)h * F_ROWS + f] = v * feature_scale_factor(f, scale);
   }
 }
 
 // ---------------------------------------------------------------------------
 // state_update: dS[u,c][slab rows] = phi_k^T U
-//   grid (4 slab groups, chunks, units); 256 threads
+//   grid (4 slab groups, chunks, units); 256 threads, thread = (token, half of the slab's chunks)
 // ---------------------------------------------------------------------------
 struct StateUpdateArgs {
   const __nv_bfloat16 *k, *v;   // [units, N, 64]
@@ -85,8 +84,8 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) state_update_kernel(const Stat
   const int i = c * CT + token;
   const __nv_bfloat16* kbase = a.k + (size_t)u * a.N * HD;
   const __nv_bfloat16* vbase = a.v + (size_t)u * a.N * VD;
-  float x[HD];
-  load_row_bf16(x, kbase, i, a.N, 1.f);
+  uint32_t xp[HD / 2];
+  load_row_packed(xp, kbase, i, a.N);
   for (int idx = tid; idx < (EP / 8) * CT; idx += GEN_THREADS) {
     const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
     reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(vbase + (size_t)j * VD, ec, j < a.N);
@@ -123,7 +122,8 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) state_update_kernel(const Stat
   for (int it = 0; it < ns; ++it) {
     const int buf = it & 1;
     // A[buf] and accumulator buf were released by epilogue(it-2), which every thread has passed
-    write_half_slab<false>(s0 + it, half, x, nullptr, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES), token);
+    keep_in_loop(xp);
+    write_half_slab_raw(s0 + it, half, xp, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES) + token);
     fence_async_smem();
     __syncthreads();
     if (tid == 0) {
@@ -188,9 +188,8 @@ __global__ void __launch_bounds__(256) state_scan_kernel(const float* ds, __nv_b
 
 // ---------------------------------------------------------------------------
 // cross_read: Y[i, 0:80] = phi(i) . state_image[u, c]   (sum over all 17 slabs)
-//   QUERY : phi = phi_q of head h (coefficient table), x = scale * q, output num/den
+//   QUERY : phi = phi_q of head h (coefficient table with the query scale folded in), x = q, output num/den
 //   !QUERY: phi = phi_k, x = k, output columns 0..63 (the value part) to out64
-//   grid (chunks, heads, batch); 256 threads
 // ---------------------------------------------------------------------------
 struct CrossReadArgs {
   const __nv_bfloat16* x;        // q [B,Hq,N,64] or k [B,Hkv,N,64]
@@ -199,7 +198,6 @@ struct CrossReadArgs {
   float* out64;                  // [B,H,N,64]
   float* out1;                   // [B,H,N] (QUERY: denominator)
   int N, NB, H, rep;             // rep = heads per state unit (Hq/Hkv for QUERY, 1 otherwise)
-  float mul;
   int32_t* status;
 };
 
@@ -229,8 +227,10 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) cross_read_kernel(const CrossR
     dead = 0;
   }
   const int i = c * CT + token;
-  float x[HD];
-  load_row_bf16(x, a.x + (size_t)(b * a.H + h) * a.N * HD, i, a.N, a.mul);
+  uint32_t xp[HD / 2];
+  load_row_packed(xp, a.x + (size_t)(b * a.H + h) * a.N * HD, i, a.N);
+  f32x2 xq[QUERY ? HD / 2 : 1];
+  if constexpr (QUERY) unpack_row(xp, xq);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
@@ -255,7 +255,13 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) cross_read_kernel(const CrossR
         bulk_g2s(Sbuf + st * SLAB_S_BYTES, img + (size_t)nxt * SLAB_S_BYTES, SLAB_S_BYTES, &full[st]);
       }
     }
-    write_half_slab<QUERY>(s, half, x, coef, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES), token);
+    if constexpr (QUERY) {
+      keep_in_loop(xq);
+      write_half_slab_coef(s, half, xq, coef, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES) + token);
+    } else {
+      keep_in_loop(xp);
+      write_half_slab_raw(s, half, xp, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES) + token);
+    }
     fence_async_smem();
     __syncthreads();
     if (tid == 0) {
@@ -307,8 +313,9 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) cross_read_kernel(const CrossR
 // host-side launchers
 // ---------------------------------------------------------------------------
 cudaError_t build_coef_table(const int32_t* dim_perm, const int32_t* group_start, const float* A,
-                             const float* Bc, const float* Cc, int Hq, int G, float* table, cudaStream_t st) {
-  coef_table_kernel<<<Hq, 256, 0, st>>>(dim_perm, group_start, A, Bc, Cc, G, table);
+                             const float* Bc, const float* Cc, int Hq, int G, float scale, float* table,
+                             cudaStream_t st) {
+  coef_table_kernel<<<Hq, 256, 0, st>>>(dim_perm, group_start, A, Bc, Cc, G, scale, table);
   return cudaGetLastError();
 }
 
@@ -318,7 +325,7 @@ cudaError_t state_update(const void* k, const void* v, float* ds, int units, int
   cudaError_t e = cudaFuncSetAttribute(state_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   StateUpdateArgs a{static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ds, N, NB, status};
-  state_update_kernel<<<dim3(4, NB, units), GEN_THREADS, smem, st>>>(a);
+  state_update_kernel<<<dim3(SU_GROUPS, NB, units), GEN_THREADS, smem, st>>>(a);
   return cudaGetLastError();
 }
 
@@ -330,11 +337,11 @@ cudaError_t state_scan(const float* ds, void* image, const float* state_in, floa
 }
 
 cudaError_t cross_read(bool query, const void* x, const void* image, const float* coef_table, float* out64,
-                       float* out1, int B, int H, int rep, int N, int NB, float mul, int32_t* status,
+                       float* out1, int B, int H, int rep, int N, int NB, int32_t* status,
                        cudaStream_t st) {
   const int smem = 2 * SLAB_A_BYTES + CR_STAGES * SLAB_S_BYTES;
   CrossReadArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(image), coef_table,
-                  out64, out1, N, NB, H, rep, mul, status};
+                  out64, out1, N, NB, H, rep, status};
   cudaError_t e;
   if (query) {
     e = cudaFuncSetAttribute(cross_read_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -350,5 +357,6 @@ cudaError_t cross_read(bool query, const void* x, const void* image, const float
 
 size_t state_rows() { return F_ROWS; }
 size_t state_image_bytes_per_chunk() { return (size_t)F_SLABS * SLAB_S_BYTES; }
+size_t state_slab_image_bytes() { return SLAB_S_BYTES; }
 
 }  // namespace oal

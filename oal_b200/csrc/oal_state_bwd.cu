@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
       cur.next(rep, a.NB);
       if (it + 1 < T) fetch(cur);             // in flight while this slab is generated
       if (use > 0) w.wait(&mma_done[s], (use - 1) & 1, 0x31);   // the MMA that read A[s] has completed
-      write_slab_bf16(slab, xp, reinterpret_cast<uint4*>(Abuf + s * SLAB_A_BYTES), token);
+      write_slab_raw(slab, xp, reinterpret_cast<uint4*>(Abuf + s * SLAB_A_BYTES) + token);
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_a[s]);
@@ -171,8 +171,8 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
     float cf_next = T > 0 ? a.coef_table[(size_t)((d.u % a.Hkv) * rep) * F_ROWS + d.slab * 128 + fr] : 0.f;
     for (int it = 0; it < T; ++it) {
       const int b = d.u / a.Hkv, h = (d.u % a.Hkv) * rep + d.hh, f = d.slab * 128 + fr;
-      const float fs = feature_scale_factor(f, a.scale);
-      const float cf = cf_next * fs;
+      const float fs = feature_scale_factor(f, a.scale);   // d(table entry) / d(coefficient)
+      const float cf = cf_next;
       dn.next(rep, a.NB);
       if (it + 1 < T)       // coefficient of the next (item, head): in flight during this drain
         cf_next = a.coef_table[(size_t)((dn.u % a.Hkv) * rep + dn.hh) * F_ROWS + dn.slab * 128 + fr];
@@ -281,72 +281,89 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
 }
 
 // ---------------------------------------------------------------------------
-// fold of one 16-column load (two chunks of 8 features) of dphi into dx
+// fold of dphi (tensor memory, thread = token, columns = the 128 features of a slab) through the
+// feature map into dx.  x and dx are fp32 rows held as packed pairs (element 2k, 2k+1 in pair k);
+// every index is a compile-time constant.  Per pair chunk (cb, r), with t_j = dphi_j (* coef_j):
+//   dx[r]        += sum_j t_j x[8 cb + j]        dx[8 cb + j] += t_j x[r]
 // ---------------------------------------------------------------------------
-template <int CH, bool QUERY, int OFF>
-__device__ __forceinline__ void fold_chunk(const float (&v)[16], const float (&x)[HD], const float* coef,
-                                           float (&dx)[HD]) {
-  if constexpr (CH < F_CONST_CHUNK) {
-    float t[8];
+template <int Q, bool QUERY, int OFF>
+__device__ __forceinline__ void fold_chunk(const float (&v)[16], const f32x2 (&xq)[HD / 2], const float* coef,
+                                           f32x2 (&dxq)[HD / 2]) {
+  if constexpr (Q < F_CONST_CHUNK) {
+    f32x2 t[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) t[j] = v[OFF + j];
+    for (int k = 0; k < 4; ++k) t[k] = f2_pack(v[OFF + 2 * k], v[OFF + 2 * k + 1]);
     if constexpr (QUERY) {
-      const float4 c0 = *reinterpret_cast<const float4*>(coef + 8 * CH);
-      const float4 c1 = *reinterpret_cast<const float4*>(coef + 8 * CH + 4);
-      t[0] *= c0.x; t[1] *= c0.y; t[2] *= c0.z; t[3] *= c0.w;
-      t[4] *= c1.x; t[5] *= c1.y; t[6] *= c1.z; t[7] *= c1.w;
+      const ulonglong2 ca = *reinterpret_cast<const ulonglong2*>(coef + 8 * Q);
+      const ulonglong2 cb2 = *reinterpret_cast<const ulonglong2*>(coef + 8 * Q + 4);
+      t[0] = f2_mul(t[0], ca.x);
+      t[1] = f2_mul(t[1], ca.y);
+      t[2] = f2_mul(t[2], cb2.x);
+      t[3] = f2_mul(t[3], cb2.y);
     }
-    if constexpr (CH < F_PAIR_CHUNKS) {
-      constexpr RC p0 = pair_rc(8 * CH + 0), p1 = pair_rc(8 * CH + 1), p2 = pair_rc(8 * CH + 2),
-                   p3 = pair_rc(8 * CH + 3), p4 = pair_rc(8 * CH + 4), p5 = pair_rc(8 * CH + 5),
-                   p6 = pair_rc(8 * CH + 6), p7 = pair_rc(8 * CH + 7);
-#define OAL_FOLD(P, J)                         \
-  dx[P.r] = fmaf(t[J], x[P.c], dx[P.r]);       \
-  dx[P.c] = fmaf(t[J], x[P.r], dx[P.c]);
-      OAL_FOLD(p0, 0) OAL_FOLD(p1, 1) OAL_FOLD(p2, 2) OAL_FOLD(p3, 3)
-      OAL_FOLD(p4, 4) OAL_FOLD(p5, 5) OAL_FOLD(p6, 6) OAL_FOLD(p7, 7)
-#undef OAL_FOLD
-    } else {
+    if constexpr (Q < F_PAIR_CHUNKS) {
+      constexpr PairCursor pc = pair_pos(Q);
+      constexpr int nv = pc.valid();
+      float xlo, xhi;
+      f2_unpack(xq[pc.r / 2], xlo, xhi);
+      const f32x2 xr2 = f2_bcast((pc.r & 1) ? xhi : xlo);
+      f32x2 sr2 = 0ull;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dx[8 * (CH - F_LIN_CHUNK0) + j] += t[j];
+      for (int k = 0; k < 4; ++k) {
+        if (2 * k < nv) {                       // pairs entirely above the diagonal do not exist
+          if (2 * k + 1 >= nv) {                // the pair straddles the diagonal: drop its upper element
+            float lo, hi;
+            f2_unpack(t[k], lo, hi);
+            t[k] = f2_pack(lo, 0.f);
+          }
+          sr2 = f2_fma(t[k], xq[4 * pc.cb + k], sr2);
+          dxq[4 * pc.cb + k] = f2_fma(t[k], xr2, dxq[4 * pc.cb + k]);
+        }
+      }
+      float slo, shi, dlo, dhi;
+      f2_unpack(sr2, slo, shi);
+      f2_unpack(dxq[pc.r / 2], dlo, dhi);
+      if (pc.r & 1) dhi += slo + shi;
+      else dlo += slo + shi;
+      dxq[pc.r / 2] = f2_pack(dlo, dhi);
+    } else {
+      const f32x2 one2 = f2_bcast(1.f);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        dxq[4 * (Q - F_LIN_CHUNK0) + k] = f2_fma(t[k], one2, dxq[4 * (Q - F_LIN_CHUNK0) + k]);
     }
   }
 }
 
-template <int S, int HALF, bool QUERY, int Q>
-__device__ __forceinline__ void fold_quarter(uint32_t taddr, const float (&x)[HD], const float* coef,
-                                             float (&dx)[HD]) {
+template <int S, int HALF, bool QUERY, int P>
+__device__ __forceinline__ void fold_pair_of_chunks(uint32_t taddr, const f32x2 (&xq)[HD / 2], const float* coef,
+                                                    f32x2 (&dxq)[HD / 2]) {
   float v[16];
-  tmem_ld16(taddr + HALF * 64 + 16 * Q, v);
+  tmem_ld16(taddr + HALF * 64 + 16 * P, v);
   tmem_ld_wait();
-  fold_chunk<S * 16 + HALF * 8 + 2 * Q, QUERY, 0>(v, x, coef, dx);
-  fold_chunk<S * 16 + HALF * 8 + 2 * Q + 1, QUERY, 8>(v, x, coef, dx);
+  fold_chunk<S * 16 + HALF * 8 + 2 * P, QUERY, 0>(v, xq, coef, dxq);
+  fold_chunk<S * 16 + HALF * 8 + 2 * P + 1, QUERY, 8>(v, xq, coef, dxq);
 }
 
 template <int S, int HALF, bool QUERY>
-__device__ __forceinline__ void fold_half_slab_impl(uint32_t taddr, const float (&x)[HD], const float* coef,
-                                                    float (&dx)[HD]) {
-  fold_quarter<S, HALF, QUERY, 0>(taddr, x, coef, dx);
-  fold_quarter<S, HALF, QUERY, 1>(taddr, x, coef, dx);
-  fold_quarter<S, HALF, QUERY, 2>(taddr, x, coef, dx);
-  fold_quarter<S, HALF, QUERY, 3>(taddr, x, coef, dx);
+__device__ __forceinline__ void fold_half_slab_impl(uint32_t taddr, const f32x2 (&xq)[HD / 2], const float* coef,
+                                                    f32x2 (&dxq)[HD / 2]) {
+  fold_pair_of_chunks<S, HALF, QUERY, 0>(taddr, xq, coef, dxq);
+  fold_pair_of_chunks<S, HALF, QUERY, 1>(taddr, xq, coef, dxq);
+  fold_pair_of_chunks<S, HALF, QUERY, 2>(taddr, xq, coef, dxq);
+  fold_pair_of_chunks<S, HALF, QUERY, 3>(taddr, xq, coef, dxq);
 }
 
 template <bool QUERY>
-__device__ __forceinline__ void fold_half_slab(int s, int half, uint32_t taddr, const float (&x)[HD],
-                                               const float* coef, float (&dx)[HD]) {
-#define OAL_FOLD_CASE(S)                                                               \
+__device__ __forceinline__ void fold_half_slab(int s, int half, uint32_t taddr, const f32x2 (&xq)[HD / 2],
+                                               const float* coef, f32x2 (&dxq)[HD / 2]) {
+#define OAL_CASE(S)                                                                    \
   case S:                                                                              \
-    if (half == 0) fold_half_slab_impl<S, 0, QUERY>(taddr, x, coef, dx);               \
-    else fold_half_slab_impl<S, 1, QUERY>(taddr, x, coef, dx);                         \
+    if (half == 0) fold_half_slab_impl<S, 0, QUERY>(taddr, xq, coef, dxq);             \
+    else fold_half_slab_impl<S, 1, QUERY>(taddr, xq, coef, dxq);                       \
     break;
-  switch (s) {
-    OAL_FOLD_CASE(0) OAL_FOLD_CASE(1) OAL_FOLD_CASE(2) OAL_FOLD_CASE(3) OAL_FOLD_CASE(4) OAL_FOLD_CASE(5)
-    OAL_FOLD_CASE(6) OAL_FOLD_CASE(7) OAL_FOLD_CASE(8) OAL_FOLD_CASE(9) OAL_FOLD_CASE(10) OAL_FOLD_CASE(11)
-    OAL_FOLD_CASE(12) OAL_FOLD_CASE(13) OAL_FOLD_CASE(14) OAL_FOLD_CASE(15) OAL_FOLD_CASE(16)
-    default: break;
-  }
-#undef OAL_FOLD_CASE
+  OAL_SLAB_SWITCH(s, OAL_CASE)
+#undef OAL_CASE
 }
 
 // ---------------------------------------------------------------------------
@@ -361,7 +378,6 @@ struct FeatGradArgs {
   const float* coef_table;       // QUERY
   float* dx;                     // [B,H,N,64] fp32
   int N, NB, H, rep;
-  float mul, outmul;
   int32_t* status;
 };
 
@@ -394,10 +410,14 @@ __global__ void __launch_bounds__(256, 1) feature_grad_kernel(const FeatGradArgs
     for (int f = tid; f < F_ROWS; f += 256) coef[f] = a.coef_table[(size_t)h * F_ROWS + f];
   const int i = c * CT + token;
   const size_t head_off = (size_t)(b * a.H + h) * a.N;
-  float x[HD], dx[HD];
-  load_row_bf16(x, a.x + head_off * HD, i, a.N, a.mul);
+  f32x2 xq[HD / 2], dxq[HD / 2];
+  {
+    uint32_t xp[HD / 2];
+    load_row_packed(xp, a.x + head_off * HD, i, a.N);
+    unpack_row(xp, xq);
+  }
 #pragma unroll
-  for (int d = 0; d < HD; ++d) dx[d] = 0.f;
+  for (int d = 0; d < HD / 2; ++d) dxq[d] = 0ull;
   if (!QUERY) {
     for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
       const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
@@ -431,7 +451,7 @@ __global__ void __launch_bounds__(256, 1) feature_grad_kernel(const FeatGradArgs
     const int fs_ = (S_);                                                                   \
     w.wait(&mma_done[fs_ & 1], (fs_ >> 1) & 1);                                             \
     fence_after_sync();                                                                     \
-    fold_half_slab<QUERY>(fs_, wg, tmem_base + (fs_ & 1) * 128 + lane_off, x, coef, dx);    \
+    fold_half_slab<QUERY>(fs_, wg, tmem_base + (fs_ & 1) * 128 + lane_off, xq, coef, dxq);  \
     fence_before_sync();                                                                    \
   } while (0)
 
@@ -461,6 +481,9 @@ __global__ void __launch_bounds__(256, 1) feature_grad_kernel(const FeatGradArgs
   OAL_FOLD_SLAB(F_SLABS - 1);
 #undef OAL_FOLD_SLAB
   // combine the two halves of every token and write
+  float dx[HD];
+#pragma unroll
+  for (int d = 0; d < HD / 2; ++d) f2_unpack(dxq[d], dx[2 * d], dx[2 * d + 1]);
   if (wg == 1) {
 #pragma unroll
     for (int d = 0; d < HD; ++d) red[token * 65 + d] = dx[d];
@@ -470,10 +493,9 @@ __global__ void __launch_bounds__(256, 1) feature_grad_kernel(const FeatGradArgs
     float* dst = a.dx + (head_off + i) * HD;
 #pragma unroll
     for (int d4 = 0; d4 < HD; d4 += 4)
-      *reinterpret_cast<float4*>(dst + d4) = make_float4(a.outmul * (dx[d4] + red[token * 65 + d4]),
-                                                          a.outmul * (dx[d4 + 1] + red[token * 65 + d4 + 1]),
-                                                          a.outmul * (dx[d4 + 2] + red[token * 65 + d4 + 2]),
-                                                          a.outmul * (dx[d4 + 3] + red[token * 65 + d4 + 3]));
+      *reinterpret_cast<float4*>(dst + d4) =
+          make_float4(dx[d4] + red[token * 65 + d4], dx[d4 + 1] + red[token * 65 + d4 + 1],
+                      dx[d4 + 2] + red[token * 65 + d4 + 2], dx[d4 + 3] + red[token * 65 + d4 + 3]);
   }
   fence_before_sync();
   __syncthreads();
@@ -510,17 +532,14 @@ __global__ void dcoef_slots_kernel(const float* dcoef, const int32_t* dim_perm, 
   for (int f = threadIdx.x; f < F_ROWS; f += blockDim.x) {
     int slot = -1;
     float wgt = 1.f;
-    if (f < F_PAIR_CHUNKS * 8) {
-      int r = (int)((sqrtf(8.f * f + 1.f) - 1.f) * 0.5f);
-      while ((r + 1) * (r + 2) / 2 <= f) ++r;
-      while (r * (r + 1) / 2 > f) --r;
-      const int cdim = f - r * (r + 1) / 2;
-      const int ga = min(gdim[r], gdim[cdim]), gb = max(gdim[r], gdim[cdim]);
+    const FeatureId id = feature_id(f);
+    if (id.kind == 0 && id.live) {
+      const int ga = min(gdim[id.r], gdim[id.c]), gb = max(gdim[id.r], gdim[id.c]);
       slot = 1 + GMAX + tri_slot(ga, gb);
-      wgt = (ga == gb && r != cdim) ? 2.f : 1.f;
-    } else if (f < F_CONST_CHUNK * 8) {
-      slot = 1 + gdim[f - F_LIN_CHUNK0 * 8];
-    } else if (f == F_CONST_CHUNK * 8) {
+      wgt = (ga == gb && id.r != id.c) ? 2.f : 1.f;
+    } else if (id.kind == 1) {
+      slot = 1 + gdim[id.r];
+    } else if (id.kind == 2) {
       slot = 0;
     }
     fslot[f] = (short)slot;
@@ -613,12 +632,12 @@ cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img,
 }
 
 cudaError_t feature_grad(bool query, const void* x, const void* gimg, const void* v, const void* image,
-                         const float* coef_table, float* dx, int B, int H, int rep, int N, int NB, float mul,
-                         float outmul, int32_t* status, cudaStream_t st) {
+                         const float* coef_table, float* dx, int B, int H, int rep, int N, int NB, int32_t* status,
+                         cudaStream_t st) {
   const int smem = SLAB_S_BYTES + FG_STAGES * SLAB_S_BYTES + F_ROWS * (int)sizeof(float) + 128 * 65 * (int)sizeof(float);
   FeatGradArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gimg),
                  static_cast<const __nv_bfloat16*>(v), static_cast<const __nv_bfloat16*>(image), coef_table, dx,
-                 N, NB, H, rep, mul, outmul, status};
+                 N, NB, H, rep, status};
   cudaError_t e;
   if (query) {
     e = cudaFuncSetAttribute(feature_grad_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

@@ -205,4 +205,29 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 }  // namespace umma
+
+typedef unsigned long long f32x2;   // two floats in one 64-bit register (packed fp32 arithmetic)
+
+// Packed fp32 pairs (sm_100 executes add / mul / fma on two floats held in one 64-bit register):
+// the per-pair combine is issue-bound, so two columns per instruction is the lever that matters.
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ f32x2 f2_bcast(float a) { return f2_pack(a, a); }
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 }  // namespace oal

@@ -54,7 +54,7 @@ def exclusive_prefix_over_ranks(local: torch.Tensor, group=None, *, reverse: boo
 
 
 def local_state_total(k: torch.Tensor, v: torch.Tensor, plan) -> torch.Tensor:
-    """fp32 ``[B*Hkv, 2176, 80]``: this rank's contribution to the running state."""
+    """fp32 ``[B*Hkv, 2432, 80]``: this rank's contribution to the running state."""
     lib = _lib.load()
     B, Hq, Hkv, N, D, Dv = plan.geometry
     kp, vp = _pad_last(k), _pad_last(v)
