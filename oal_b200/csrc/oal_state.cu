@@ -197,113 +197,194 @@ struct CrossReadArgs {
   const float* coef_table;       // [Hq, F_ROWS] (QUERY)
   float* out64;                  // [B,H,N,64]
   float* out1;                   // [B,H,N] (QUERY: denominator)
-  int N, NB, H, rep;             // rep = heads per state unit (Hq/Hkv for QUERY, 1 otherwise)
+  int N, NB, H, rep, B;          // rep = heads per state unit (Hq/Hkv for QUERY, 1 otherwise)
   int32_t* status;
 };
 
-constexpr int CR_STAGES = 2;      // two CTAs share an SM: the other CTA hides this one's copy latency
+// Persistent, warp-specialised kernel.  Work items are (batch, head, chunk) with the heads of one
+// state unit adjacent, so CTAs running at the same time read the same state image from L2.  CTA k
+// takes items k, k + gridDim.x, ...; the flat iteration `it` = (item, slab) drives four roles:
+//   warps 0-7   generate feature slab `slab` of the item's 128 tokens into A[it % 3]
+//   warp  13    lane 0 streams the state slab images into a 4-slot ring and the head's coefficient
+//               table into one of two buffers (bulk copies)
+//   warp  12    lane 0 issues the MMAs  acc[item & 1] += A . S  once both are full
+//   warps 8-11  after the item's last slab: accumulator -> HBM, then release it
+constexpr int CR_GEN_WARPS = 8, CR_EPI_WARPS = 4;
+constexpr int CR_ISSUER = CR_GEN_WARPS + CR_EPI_WARPS, CR_LOADER = CR_ISSUER + 1;
+constexpr int CR_THREADS = (CR_LOADER + 1) * 32;
+constexpr int CR_ARING = 3, CR_SRING = 4;
+static_assert(CR_GEN_WARPS * 32 == GEN_THREADS, "the slab generator is written for GEN_THREADS threads");
+
+struct CrItem {
+  int b, h, c;
+};
+// item index -> (batch, head, chunk): the `rep` heads of a state unit are adjacent, then chunks
+__device__ __forceinline__ CrItem cr_item(int item, int H, int rep, int NB) {
+  CrItem r;
+  const int hh = item % rep, t = item / rep;
+  r.c = t % NB;
+  const int unit = t / NB, units_per_b = H / rep;
+  r.b = unit / units_per_b;
+  r.h = (unit % units_per_b) * rep + hh;
+  return r;
+}
 
 template <bool QUERY>
-__global__ void __launch_bounds__(GEN_THREADS, 2) cross_read_kernel(const CrossReadArgs a) {
+__global__ void __launch_bounds__(CR_THREADS, 1) cross_read_kernel(const CrossReadArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* Abuf = smem;                                   // 2 x SLAB_A_BYTES
-  unsigned char* Sbuf = smem + 2 * SLAB_A_BYTES;                // CR_STAGES x SLAB_S_BYTES
-  // per-head coefficient table, read straight from global memory (warp-uniform, L1-resident)
-  const float* coef = QUERY ? a.coef_table + (size_t)blockIdx.y * F_ROWS : nullptr;
-  __shared__ uint64_t full[CR_STAGES];
-  __shared__ uint64_t mma_done[2];
+  unsigned char* Abuf = smem;                                   // CR_ARING x SLAB_A_BYTES
+  unsigned char* Sbuf = smem + CR_ARING * SLAB_A_BYTES;         // CR_SRING x SLAB_S_BYTES, then the head's coefficient table
+  __shared__ uint64_t full_a[CR_ARING], a_free[CR_ARING], s_full[CR_SRING], s_free[CR_SRING], acc_full[2], acc_free[2];
+  __shared__ uint64_t coef_full[2], coef_free[2];
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int token = tid & 127, half = tid >> 7;
-  const int unit = (b * a.H + h) / a.rep;
-  if (warp == 0) tmem_alloc(&tmem_base, 128);
+  const int n_items = a.B * a.H * a.NB;
+  const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  if (warp == CR_ISSUER) tmem_alloc(&tmem_base, 256);
   if (tid == 0) {
-    for (int s = 0; s < CR_STAGES; ++s) mbar_init(&full[s], 1);
-    mbar_init(&mma_done[0], 1);
-    mbar_init(&mma_done[1], 1);
+    for (int s = 0; s < CR_ARING; ++s) {
+      mbar_init(&full_a[s], CR_GEN_WARPS);
+      mbar_init(&a_free[s], 1);
+    }
+    for (int s = 0; s < CR_SRING; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_free[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_free[s], CR_EPI_WARPS);
+      mbar_init(&coef_full[s], 1);
+      mbar_init(&coef_free[s], CR_GEN_WARPS);
+    }
     mbar_fence_init();
     dead = 0;
   }
-  const int i = c * CT + token;
-  uint32_t xp[HD / 2];
-  load_row_packed(xp, a.x + (size_t)(b * a.H + h) * a.N * HD, i, a.N);
-  f32x2 xq[QUERY ? HD / 2 : 1];
-  if constexpr (QUERY) unpack_row(xp, xq);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   Waiter w{&dead};
-  const uint32_t tacc = tmem_base;
-  const unsigned char* img = reinterpret_cast<const unsigned char*>(a.image) +
-                             ((size_t)unit * a.NB + c) * F_SLABS * SLAB_S_BYTES;
-  if (tid == 0) {
-    for (int s = 0; s < CR_STAGES; ++s) {
-      mbar_arrive_expect_tx(&full[s], SLAB_S_BYTES);
-      bulk_g2s(Sbuf + s * SLAB_S_BYTES, img + (size_t)s * SLAB_S_BYTES, SLAB_S_BYTES, &full[s]);
-    }
-  }
-  const uint32_t idesc = instr_desc_bf16(128, EP, 0, 1);
-  for (int s = 0; s < F_SLABS; ++s) {
-    const int buf = s & 1;
-    if (s >= 2) {
-      w.wait(&mma_done[buf], ((s - 2) >> 1) & 1);      // slab s-2 finished: A[buf] and its state stage are free
-      if (tid == 0 && s + CR_STAGES - 2 < F_SLABS) {
-        const int nxt = s + CR_STAGES - 2, st = nxt % CR_STAGES;
-        mbar_arrive_expect_tx(&full[st], SLAB_S_BYTES);
-        bulk_g2s(Sbuf + st * SLAB_S_BYTES, img + (size_t)nxt * SLAB_S_BYTES, SLAB_S_BYTES, &full[st]);
+
+  if (warp < CR_GEN_WARPS) {
+    // ---------------- generators: thread = (token, half of the slab's chunks) ----------------
+    const int token = tid & 127, half = tid >> 7;
+    int s3 = 0, use = 0;
+    for (int k = 0; k < my_items; ++k) {
+      const CrItem it = cr_item(blockIdx.x + k * gridDim.x, a.H, a.rep, a.NB);
+      // this head's coefficient table, brought in by the loader warp (two buffers)
+      const float* coef = reinterpret_cast<const float*>(Sbuf + CR_SRING * SLAB_S_BYTES) + (k & 1) * F_ROWS;
+      if constexpr (QUERY) w.wait(&coef_full[k & 1], (k >> 1) & 1, 0x47);
+      uint32_t xp[HD / 2];
+      load_row_packed(xp, a.x + (size_t)(it.b * a.H + it.h) * a.N * HD, it.c * CT + token, a.N);
+      f32x2 xq[QUERY ? HD / 2 : 1];
+      if constexpr (QUERY) unpack_row(xp, xq);
+      for (int s = 0; s < F_SLABS; ++s) {
+        if (use > 0) w.wait(&a_free[s3], (use - 1) & 1, 0x41);      // the MMAs that read A[s3] have completed
+        uint4* tile = reinterpret_cast<uint4*>(Abuf + s3 * SLAB_A_BYTES) + token;
+        if constexpr (QUERY) {
+          keep_in_loop(xq);
+          write_half_slab_coef(s, half, xq, coef, tile);
+        } else {
+          keep_in_loop(xp);
+          write_half_slab_raw(s, half, xp, tile);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_a[s3]);
+        if (++s3 == CR_ARING) { s3 = 0; ++use; }
+      }
+      if constexpr (QUERY) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&coef_free[k & 1]);     // this warp no longer reads the table
       }
     }
-    if constexpr (QUERY) {
-      keep_in_loop(xq);
-      write_half_slab_coef(s, half, xq, coef, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES) + token);
-    } else {
-      keep_in_loop(xp);
-      write_half_slab_raw(s, half, xp, reinterpret_cast<uint4*>(Abuf + buf * SLAB_A_BYTES) + token);
-    }
-    fence_async_smem();
-    __syncthreads();
-    if (tid == 0) {
-      w.wait(&full[s % CR_STAGES], (s / CR_STAGES) & 1);
+  } else if (warp < CR_ISSUER) {
+    // ---------------- accumulator -> HBM ----------------
+    const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+    for (int k = 0; k < my_items; ++k) {
+      const CrItem it = cr_item(blockIdx.x + k * gridDim.x, a.H, a.rep, a.NB);
+      const int row = it.c * CT + 32 * (warp & 3) + lane;
+      const size_t orow = (size_t)(it.b * a.H + it.h) * a.N + row;
+      w.wait(&acc_full[k & 1], (k >> 1) & 1, 0x42);
       fence_after_sync();
-      const uint32_t a_addr = smem_u32(Abuf + buf * SLAB_A_BYTES);
-      const uint32_t s_addr = smem_u32(Sbuf + (s % CR_STAGES) * SLAB_S_BYTES);
+      const uint32_t t = tmem_base + (k & 1) * EP + lane_off;
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks)       // 16 features per step
-        mma_bf16_ss(tacc, smem_desc(a_addr + ks * 2 * CT * 16, CT * 16, 128),
-                    smem_desc(s_addr + ks * 256, 128, 128 * 16), idesc, (s > 0 || ks > 0));
-      mma_commit(&mma_done[buf]);
+      for (int cc = 0; cc < EP; cc += 16) {
+        if (cc < VD || QUERY) {
+          float vv[16];
+          tmem_ld16(t + cc, vv);
+          tmem_ld_wait();
+          if (row < a.N && !dead) {
+            if (cc < VD) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<float4*>(a.out64 + orow * VD + cc + 4 * q4) =
+                    make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]);
+            } else if (QUERY) {
+              a.out1[orow] = vv[0];
+            }
+          }
+        }
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_free[k & 1]);
     }
-  }
-  w.wait(&mma_done[1], ((F_SLABS - 2) >> 1) & 1);    // slab 15
-  w.wait(&mma_done[0], ((F_SLABS - 1) >> 1) & 1);    // slab 16
-  fence_after_sync();
-  if (warp < 8) {
-    const int row = c * CT + 32 * (warp & 3) + lane;
-    const int col0 = warp < 4 ? 0 : 48, ncol = warp < 4 ? 48 : 32;
-    const uint32_t t = tacc + ((uint32_t)(32 * (warp & 3)) << 16) + col0;
-    const size_t orow = (size_t)(b * a.H + h) * a.N + row;
-    for (int cc = 0; cc < ncol; cc += 16) {
-      float vv[16];
-      tmem_ld16(t + cc, vv);
-      tmem_ld_wait();
-      if (row < a.N && !dead) {
-        const int col = col0 + cc;
-        if (col < VD) {
+  } else if (warp == CR_ISSUER) {
+    // ---------------- MMA issue ----------------
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16(128, EP, 0, 1);
+      int s3 = 0, use = 0, gs = 0, guse = 0;
+      for (int k = 0; k < my_items; ++k) {
+        const uint32_t tacc = tmem_base + (k & 1) * EP;
+        if (k >= 2) w.wait(&acc_free[k & 1], ((k >> 1) - 1) & 1, 0x43);   // item k-2 has left this accumulator
+        for (int s = 0; s < F_SLABS; ++s) {
+          const uint32_t a_addr = smem_u32(Abuf + s3 * SLAB_A_BYTES);
+          const uint32_t s_addr = smem_u32(Sbuf + gs * SLAB_S_BYTES);
+          w.wait(&full_a[s3], use & 1, 0x44);
+          w.wait(&s_full[gs], guse & 1, 0x45);
+          fence_after_sync();
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
-            *reinterpret_cast<float4*>(a.out64 + orow * VD + col + 4 * q4) =
-                make_float4(vv[4 * q4], vv[4 * q4 + 1], vv[4 * q4 + 2], vv[4 * q4 + 3]);
-        } else if (QUERY) {
-          a.out1[orow] = vv[0];
+          for (int ks = 0; ks < 8; ++ks)       // 16 features per step
+            mma_bf16_ss(tacc, smem_desc(a_addr + ks * 2 * CT * 16, CT * 16, 128),
+                        smem_desc(s_addr + ks * 256, 128, 128 * 16), idesc, (s > 0 || ks > 0));
+          mma_commit(&a_free[s3]);
+          mma_commit(&s_free[gs]);
+          if (s == F_SLABS - 1) mma_commit(&acc_full[k & 1]);
+          if (++s3 == CR_ARING) { s3 = 0; ++use; }
+          if (++gs == CR_SRING) { gs = 0; ++guse; }
         }
       }
     }
+    __syncwarp();
+  } else {
+    // ---------------- state image stream ----------------
+    if (lane == 0) {
+      int gs = 0, guse = 0;
+      for (int k = 0; k < my_items; ++k) {
+        const CrItem it = cr_item(blockIdx.x + k * gridDim.x, a.H, a.rep, a.NB);
+        const int unit = (it.b * a.H + it.h) / a.rep;
+        const unsigned char* img = reinterpret_cast<const unsigned char*>(a.image) +
+                                   ((size_t)unit * a.NB + it.c) * F_SLABS * SLAB_S_BYTES;
+        if constexpr (QUERY) {
+          if (k >= 2) w.wait(&coef_free[k & 1], ((k >> 1) - 1) & 1, 0x48);   // item k-2 no longer reads this buffer
+          mbar_arrive_expect_tx(&coef_full[k & 1], F_ROWS * (uint32_t)sizeof(float));
+          bulk_g2s(Sbuf + CR_SRING * SLAB_S_BYTES + (k & 1) * F_ROWS * sizeof(float),
+                   a.coef_table + (size_t)it.h * F_ROWS, F_ROWS * (uint32_t)sizeof(float), &coef_full[k & 1]);
+        }
+        for (int s = 0; s < F_SLABS; ++s) {
+          if (guse > 0) w.wait(&s_free[gs], (guse - 1) & 1, 0x46);
+          mbar_arrive_expect_tx(&s_full[gs], SLAB_S_BYTES);
+          bulk_g2s(Sbuf + gs * SLAB_S_BYTES, img + (size_t)s * SLAB_S_BYTES, SLAB_S_BYTES, &s_full[gs]);
+          if (++gs == CR_SRING) { gs = 0; ++guse; }
+        }
+      }
+    }
+    __syncwarp();
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, 128);
+  if (warp == CR_ISSUER) tmem_dealloc(tmem_base, 256);
   if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
@@ -339,18 +420,22 @@ cudaError_t state_scan(const float* ds, void* image, const float* state_in, floa
 cudaError_t cross_read(bool query, const void* x, const void* image, const float* coef_table, float* out64,
                        float* out1, int B, int H, int rep, int N, int NB, int32_t* status,
                        cudaStream_t st) {
-  const int smem = 2 * SLAB_A_BYTES + CR_STAGES * SLAB_S_BYTES;
+  const int smem = CR_ARING * SLAB_A_BYTES + CR_SRING * SLAB_S_BYTES + 2 * F_ROWS * (int)sizeof(float);
   CrossReadArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(image), coef_table,
-                  out64, out1, N, NB, H, rep, status};
+                  out64, out1, N, NB, H, rep, B, status};
   cudaError_t e;
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  const int items = B * H * NB, grid = items < sms ? items : sms;
   if (query) {
     e = cudaFuncSetAttribute(cross_read_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    cross_read_kernel<true><<<dim3(NB, H, B), GEN_THREADS, smem, st>>>(a);
+    cross_read_kernel<true><<<grid, CR_THREADS, smem, st>>>(a);
   } else {
     e = cudaFuncSetAttribute(cross_read_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    cross_read_kernel<false><<<dim3(NB, H, B), GEN_THREADS, smem, st>>>(a);
+    cross_read_kernel<false><<<grid, CR_THREADS, smem, st>>>(a);
   }
   return cudaGetLastError();
 }
