@@ -63,8 +63,9 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
   // a head with more padded slabs than the caller announced would not fit the images: refuse it
   const bool bad = pg.k16_start[IG] > a.slabs;
   if (!bad) {
-    build_padded_image(Qimg, stage, a.q + qoff * HD, c * CT, a.N, pg, tid, 256);
-    build_padded_image(Kimg, stage, a.k + koff * HD, c * CT, a.N, pg, tid, 256);
+    // second staging area: the U image, which is built right after
+    build_padded_images(Qimg, Kimg, stage, reinterpret_cast<uint32_t*>(Uimg), a.q + qoff * HD, a.k + koff * HD, c * CT,
+                        a.N, pg, tid, 256);
   } else if (tid == 0) {
     atomicOr(a.status, OAL_STATUS_BAD_LAYOUT);
   }

@@ -96,6 +96,39 @@ __device__ __forceinline__ void build_padded_image(unsigned char* img, uint32_t*
   __syncthreads();
 }
 
+// Both images of a CTA at once: the q and k tiles travel to their staging areas in one round of
+// global loads, one barrier, one gather pass, one barrier.
+__device__ __forceinline__ void build_padded_images(unsigned char* img_a, unsigned char* img_b, uint32_t* stage_a,
+                                                    uint32_t* stage_b, const __nv_bfloat16* base_a,
+                                                    const __nv_bfloat16* base_b, int row0, int N,
+                                                    const PaddedGroups& pg, int tid, int nthreads) {
+  for (int x = tid; x < 2 * CT * 8; x += nthreads) {
+    const int which = x >= CT * 8, xx = x - which * CT * 8;
+    const int r = xx >> 3, seg = xx & 7, i = row0 + r;
+    uint4 t = make_uint4(0u, 0u, 0u, 0u);
+    if (i < N) t = *reinterpret_cast<const uint4*>((which ? base_b : base_a) + (size_t)i * HD + seg * 8);
+    uint32_t* d = (which ? stage_b : stage_a) + r * 33 + seg * 4;
+    d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+  }
+  __syncthreads();
+  const int per_img = 2 * pg.k16_start[IG] * CT;
+  for (int x = tid; x < 2 * per_img; x += nthreads) {
+    const int which = x >= per_img, xx = x - which * per_img;
+    const int c8 = xx >> 7, r = xx & 127;
+    const unsigned short* raw = reinterpret_cast<const unsigned short*>(which ? stage_b : stage_a);
+    unsigned short e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int sd = pg.src[c8 * 8 + j];
+      e[j] = sd >= 0 ? raw[r * 66 + sd] : (unsigned short)0;
+    }
+    reinterpret_cast<uint4*>(which ? img_b : img_a)[xx] =
+        make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16), e[4] | ((uint32_t)e[5] << 16),
+                   e[6] | ((uint32_t)e[7] << 16));
+  }
+  __syncthreads();
+}
+
 // 32 lanes x 32-bit, 4 consecutive columns per thread.
 __device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
   uint32_t r[4];

@@ -23,6 +23,8 @@ using namespace umma;
 constexpr int IMG_BYTES = (DP_MAX / 8) * CT * 16;        // 45056
 constexpr int TILE_BYTES = (KT / 8) * CT * 16;           // 4096: bf16 [2][128 rows][8]
 constexpr int NTRI = IG * (IG + 1) / 2;
+static_assert(STAGE_BYTES <= SLAB_S_BYTES && STAGE_BYTES <= 2 * IG * TILE_BYTES, "image staging areas");
+constexpr int NVAL = 1 + IG + NTRI;      // coefficient-gradient partial sums per thread: A, B_g, C_gg' (g <= g')
 constexpr int BT = 512;                 // compute threads per CTA: 128 rows x 4 column parts
 constexpr int BT_ALL = BT + 32;         // plus one warp whose lane 0 issues every MMA
 constexpr int CWARPS = BT / 32;         // compute warps: arrival count of the warp-level barriers
@@ -107,8 +109,9 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
     bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
   }
   // the ds tile buffers are idle during set-up: use them as the staging area of the image builds
-  build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, BT_ALL);
-  build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, BT_ALL);
+  // staging: the ds tile buffers and the U image are still idle (U is built right after)
+  build_padded_images(Qimg, Kimg, reinterpret_cast<uint32_t*>(DS), reinterpret_cast<uint32_t*>(Uimg), a.q + qoff * HD,
+                      a.k + koff * HD, c * CT, a.N, pg, tid, BT_ALL);
   for (int idx = tid; idx < (EP / 8) * CT; idx += BT_ALL) {
     const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
     reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
@@ -264,6 +267,20 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
       }
     }
   }
+  if (a.coef_partial) {
+    // U, G and the ds tiles are idle once the last MMA has completed: park the partial sums there
+    static_assert(NVAL * BT * 4 <= 3 * SLAB_S_BYTES + 2 * IG * TILE_BYTES, "partial sums must fit");
+    float* red = reinterpret_cast<float*>(Uimg);
+    if (!issuer) {
+      red[tid] = cA;
+#pragma unroll
+      for (int g = 0; g < IG; ++g) red[(1 + g) * BT + tid] = cB[g];
+#pragma unroll
+      for (int x = 0; x < NTRI; ++x) red[(1 + IG + x) * BT + tid] = cC[x];
+    }
+    float* dst = a.coef_partial + ((size_t)(b * a.Hq + h) * a.NB + c) * NCOEF;
+    for (int x = tid; x < NCOEF; x += BT_ALL) dst[x] = 0.f;      // slots of groups this build does not have
+  }
   fence_before_sync();
   __syncthreads();
   if (a.dq && !dead) {
@@ -285,39 +302,27 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
     }
   }
   if (a.coef_partial) {
-    float* red = reinterpret_cast<float*>(DS);      // the ds tiles are idle now: [16 warps][NCOEF]
-    if (!issuer) {
-      auto wsum = [](float v) {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        return v;
-      };
-      for (int x = lane; x < NCOEF; x += 32) red[warp * NCOEF + x] = 0.f;
-      __syncwarp();
-      float v = wsum(cA);
-      if (lane == 0) red[warp * NCOEF + 0] = v;
-#pragma unroll
-      for (int g = 0; g < IG; ++g) {
-        v = wsum(cB[g]);
-        if (lane == 0) red[warp * NCOEF + 1 + g] = v;
-      }
-      int idx = 0;
-#pragma unroll
-      for (int g = 0; g < IG; ++g)
-#pragma unroll
-        for (int g2 = g; g2 < IG; ++g2) {
-          v = wsum(cC[idx]);
-          if (lane == 0) red[warp * NCOEF + 1 + GMAX + tri8(g, g2)] = v;
-          ++idx;
-        }
-    }
-    __syncthreads();
+    // column sums of the per-thread partials: red[value][thread], one warp per value
+    const float* red = reinterpret_cast<const float*>(Uimg);
     float* dst = a.coef_partial + ((size_t)(b * a.Hq + h) * a.NB + c) * NCOEF;
-    for (int x = tid; x < NCOEF; x += BT_ALL) {
+    for (int v = warp; v < NVAL; v += BT_ALL / 32) {
       float t = 0.f;
 #pragma unroll
-      for (int ww = 0; ww < CWARPS; ++ww) t += red[ww * NCOEF + x];
-      dst[x] = t;
+      for (int x = 0; x < BT / 32; ++x) t += red[v * BT + 32 * x + lane];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (lane == 0) {
+        int slot = v;                                  // 0: A, 1..IG: B_g
+        if (v > IG) {                                  // C_gg', g <= g', in the order of the accumulators
+          int g = 0, rest = v - 1 - IG;
+          while (rest >= IG - g) {
+            rest -= IG - g;
+            ++g;
+          }
+          slot = 1 + GMAX + tri8(g, g + rest);
+        }
+        dst[slot] = t;
+      }
     }
   }
   __syncthreads();
@@ -369,8 +374,8 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
     bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, &gfull);
     bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
   }
-  build_padded_image(Kimg, reinterpret_cast<uint32_t*>(DS), a.k + koff * HD, c * CT, a.N, pg, tid, BT_ALL);
-  build_padded_image(Qimg, reinterpret_cast<uint32_t*>(DS), a.q + qoff * HD, c * CT, a.N, pg, tid, BT_ALL);
+  build_padded_images(Kimg, Qimg, reinterpret_cast<uint32_t*>(DS), reinterpret_cast<uint32_t*>(Uimg), a.k + koff * HD,
+                      a.q + qoff * HD, c * CT, a.N, pg, tid, BT_ALL);
   for (int idx = tid; idx < (EP / 8) * CT; idx += BT_ALL) {
     const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
     reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
