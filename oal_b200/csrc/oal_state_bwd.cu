@@ -367,139 +367,205 @@ __device__ __forceinline__ void fold_half_slab(int s, int half, uint32_t taddr, 
 }
 
 // ---------------------------------------------------------------------------
-// feature_grad
-//   grid (chunks, heads, batch); 256 threads; thread = (token, half of the slab's features)
+// feature_grad: persistent, warp-specialised.  Work items are (batch, head, chunk) with the heads of
+// one state unit adjacent; CTA k takes items k, k + gridDim.x, ...  Roles:
+//   warps 0-7  fold: thread = (token, half of the slab's 128 features); drains dphi of slab `s` from
+//              tensor memory (three buffers) into its packed dx row; halves are combined per item
+//   warp  8    lane 0 issues  dphi[s] = A . S[s]^T  (M = tokens, N = 128 features, K = 80)
+//   warp  9    lane 0 streams the state slab images (4-slot ring) and, per item, the A operand
+//              image (QUERY: the image of G) and the head's coefficient table (two buffers each)
+// KEY: the A operand [v | 1] is built in shared memory by the fold warps.
 // ---------------------------------------------------------------------------
 struct FeatGradArgs {
   const __nv_bfloat16* x;        // q [B,Hq,N,64] (QUERY) or k [B,Hkv,N,64]
   const __nv_bfloat16* gimg;     // QUERY: A-operand image of G  [B*Hq, NB, 10, 128, 8]
   const __nv_bfloat16* v;        // KEY: values, the A operand [v | 1] is built in shared memory
-  const __nv_bfloat16* image;    // state image [units, NB, 17, 10, 128, 8]: carry (QUERY) / dT (KEY)
+  const __nv_bfloat16* image;    // state image [units, NB, 19, 10, 128, 8]: carry (QUERY) / dT (KEY)
   const float* coef_table;       // QUERY
   float* dx;                     // [B,H,N,64] fp32
-  int N, NB, H, rep;
+  int N, NB, H, rep, B;
   int32_t* status;
 };
 
-constexpr int FG_STAGES = 4;
+constexpr int FG_FOLD_WARPS = 8, FG_ISSUER = FG_FOLD_WARPS, FG_LOADER = FG_ISSUER + 1;
+constexpr int FG_THREADS = (FG_LOADER + 1) * 32;
+constexpr int FG_SRING = 4, FG_DRING = 3;
+
+struct FgItem {
+  int b, h, c;
+};
+__device__ __forceinline__ FgItem fg_item(int item, int H, int rep, int NB) {
+  FgItem r;
+  const int hh = item % rep, t = item / rep;
+  r.c = t % NB;
+  const int unit = t / NB, units_per_b = H / rep;
+  r.b = unit / units_per_b;
+  r.h = (unit % units_per_b) * rep + hh;
+  return r;
+}
 
 template <bool QUERY>
-__global__ void __launch_bounds__(256, 1) feature_grad_kernel(const FeatGradArgs a) {
+__global__ void __launch_bounds__(FG_THREADS, 1) feature_grad_kernel(const FeatGradArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* Aimg = smem;                                        // SLAB_S_BYTES: [10][128 tokens][8 e]
-  unsigned char* Sbuf = smem + SLAB_S_BYTES;                         // FG_STAGES x SLAB_S_BYTES
-  float* coef = reinterpret_cast<float*>(Sbuf + FG_STAGES * SLAB_S_BYTES);   // F_ROWS
-  float* red = coef + F_ROWS;                                        // [128][65]
-  __shared__ uint64_t full[FG_STAGES], mma_done[2], afull;
+  unsigned char* Sbuf = smem;                                        // FG_SRING x SLAB_S_BYTES
+  unsigned char* Aimg = Sbuf + FG_SRING * SLAB_S_BYTES;              // 2 x SLAB_S_BYTES: [10][128 tokens][8 e]
+  float* coef_s = reinterpret_cast<float*>(Aimg + 2 * SLAB_S_BYTES); // 2 x F_ROWS
+  float* red = coef_s + 2 * F_ROWS;                                  // [128][65]
+  __shared__ uint64_t s_full[FG_SRING], s_free[FG_SRING], a_full[2], a_free[2], coef_full[2], coef_free[2];
+  __shared__ uint64_t d_full[FG_DRING], d_free[FG_DRING];
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int wg = warp >> 2, token = 32 * (warp & 3) + lane;
-  const int unit = (b * a.H + h) / a.rep;
-  if (warp == 0) tmem_alloc(&tmem_base, 256);
+  const int n_items = a.B * a.H * a.NB;
+  const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  if (warp == FG_ISSUER) tmem_alloc(&tmem_base, 512);
   if (tid == 0) {
-    for (int s = 0; s < FG_STAGES; ++s) mbar_init(&full[s], 1);
-    mbar_init(&mma_done[0], 1);
-    mbar_init(&mma_done[1], 1);
-    mbar_init(&afull, 1);
+    for (int s = 0; s < FG_SRING; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_free[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&a_full[s], QUERY ? 1 : FG_FOLD_WARPS);
+      mbar_init(&a_free[s], 1);
+      mbar_init(&coef_full[s], 1);
+      mbar_init(&coef_free[s], FG_FOLD_WARPS);
+    }
+    for (int s = 0; s < FG_DRING; ++s) {
+      mbar_init(&d_full[s], 1);
+      mbar_init(&d_free[s], FG_FOLD_WARPS);
+    }
     mbar_fence_init();
     dead = 0;
-  }
-  if (QUERY)
-    for (int f = tid; f < F_ROWS; f += 256) coef[f] = a.coef_table[(size_t)h * F_ROWS + f];
-  const int i = c * CT + token;
-  const size_t head_off = (size_t)(b * a.H + h) * a.N;
-  f32x2 xq[HD / 2], dxq[HD / 2];
-  {
-    uint32_t xp[HD / 2];
-    load_row_packed(xp, a.x + head_off * HD, i, a.N);
-    unpack_row(xp, xq);
-  }
-#pragma unroll
-  for (int d = 0; d < HD / 2; ++d) dxq[d] = 0ull;
-  if (!QUERY) {
-    for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
-      const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
-      reinterpret_cast<uint4*>(Aimg)[idx] = u_image_chunk(a.v + (head_off + j) * VD, ec, j < a.N);
-    }
-    fence_async_smem();
   }
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   Waiter w{&dead};
-  const unsigned char* img = reinterpret_cast<const unsigned char*>(a.image) +
-                             ((size_t)unit * a.NB + c) * F_SLABS * SLAB_S_BYTES;
-  if (tid == 0) {
-    if (QUERY) {
-      mbar_arrive_expect_tx(&afull, SLAB_S_BYTES);
-      bulk_g2s(Aimg, reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.H + h) * a.NB + c) * SLAB_S_BYTES,
-               SLAB_S_BYTES, &afull);
-    }
-    for (int s = 0; s < FG_STAGES; ++s) {
-      mbar_arrive_expect_tx(&full[s], SLAB_S_BYTES);
-      bulk_g2s(Sbuf + s * SLAB_S_BYTES, img + (size_t)s * SLAB_S_BYTES, SLAB_S_BYTES, &full[s]);
-    }
-  }
-  const uint32_t idesc = instr_desc_bf16(128, 128, 0, 0);
-  const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
-  const uint32_t a_addr = smem_u32(Aimg);
 
-#define OAL_FOLD_SLAB(S_)                                                                   \
-  do {                                                                                      \
-    const int fs_ = (S_);                                                                   \
-    w.wait(&mma_done[fs_ & 1], (fs_ >> 1) & 1);                                             \
-    fence_after_sync();                                                                     \
-    fold_half_slab<QUERY>(fs_, wg, tmem_base + (fs_ & 1) * 128 + lane_off, xq, coef, dxq);  \
-    fence_before_sync();                                                                    \
-  } while (0)
-
-  for (int s = 0; s < F_SLABS; ++s) {
-    __syncthreads();      // fold(s-2) is finished by every thread: accumulator s&1 may be overwritten
-    if (tid == 0) {
-      if (QUERY && s == 0) w.wait(&afull, 0);
-      w.wait(&full[s % FG_STAGES], (s / FG_STAGES) & 1);
-      fence_after_sync();
-      const uint32_t s_addr = smem_u32(Sbuf + (s % FG_STAGES) * SLAB_S_BYTES);
+  if (warp < FG_FOLD_WARPS) {
+    // ---------------- fold warps ----------------
+    const int wg = warp >> 2, token = 32 * (warp & 3) + lane;
+    const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
+    int ds = 0, duse = 0;
+    for (int k = 0; k < my_items; ++k) {
+      const FgItem it = fg_item(blockIdx.x + k * gridDim.x, a.H, a.rep, a.NB);
+      const int i = it.c * CT + token;
+      const size_t head_off = (size_t)(it.b * a.H + it.h) * a.N;
+      f32x2 xq[HD / 2], dxq[HD / 2];
+      {
+        uint32_t xp[HD / 2];
+        load_row_packed(xp, a.x + head_off * HD, i, a.N);
+        unpack_row(xp, xq);
+      }
 #pragma unroll
-      for (int ks = 0; ks < EP / 16; ++ks)
-        mma_bf16_ss(tmem_base + (s & 1) * 128, smem_desc(a_addr + ks * 2 * CT * 16, CT * 16, 128),
-                    smem_desc(s_addr + ks * 2 * 128 * 16, 128 * 16, 128), idesc, ks > 0);
-      mma_commit(&mma_done[s & 1]);
+      for (int d = 0; d < HD / 2; ++d) dxq[d] = 0ull;
+      if (!QUERY) {
+        // A operand [v | 1] of this item, once the MMAs of item k-2 have left the buffer
+        if (k >= 2) w.wait(&a_free[k & 1], ((k >> 1) - 1) & 1, 0x51);
+        uint4* dst = reinterpret_cast<uint4*>(Aimg + (k & 1) * SLAB_S_BYTES);
+        for (int idx = tid; idx < (EP / 8) * CT; idx += FG_FOLD_WARPS * 32) {
+          const int ec = idx >> 7, t = idx & 127, j = it.c * CT + t;
+          dst[idx] = u_image_chunk(a.v + (head_off + j) * VD, ec, j < a.N);
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[k & 1]);
+      }
+      const float* coef = coef_s + (k & 1) * F_ROWS;
+      if (QUERY) w.wait(&coef_full[k & 1], (k >> 1) & 1, 0x52);
+      for (int s = 0; s < F_SLABS; ++s) {
+        w.wait(&d_full[ds], duse & 1, 0x53);
+        fence_after_sync();
+        fold_half_slab<QUERY>(s, wg, tmem_base + ds * 128 + lane_off, xq, coef, dxq);
+        fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&d_free[ds]);
+        if (++ds == FG_DRING) { ds = 0; ++duse; }
+      }
+      if (QUERY) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&coef_free[k & 1]);
+      }
+      // combine the two halves of every token and write
+      float dx[HD];
+#pragma unroll
+      for (int d = 0; d < HD / 2; ++d) f2_unpack(dxq[d], dx[2 * d], dx[2 * d + 1]);
+      if (wg == 1) {
+#pragma unroll
+        for (int d = 0; d < HD; ++d) red[token * 65 + d] = dx[d];
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(FG_FOLD_WARPS * 32) : "memory");
+      if (wg == 0 && i < a.N && !dead) {
+        float* dst = a.dx + (head_off + i) * HD;
+#pragma unroll
+        for (int d4 = 0; d4 < HD; d4 += 4)
+          *reinterpret_cast<float4*>(dst + d4) =
+              make_float4(dx[d4] + red[token * 65 + d4], dx[d4 + 1] + red[token * 65 + d4 + 1],
+                          dx[d4 + 2] + red[token * 65 + d4 + 2], dx[d4 + 3] + red[token * 65 + d4 + 3]);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(FG_FOLD_WARPS * 32) : "memory");
     }
-    if (s >= 1) {
-      OAL_FOLD_SLAB(s - 1);
-      // slab s-1 has been consumed by the tensor core: refill its stage
-      if (tid == 0 && s + 3 < F_SLABS) {
-        const int st = (s + 3) % FG_STAGES;
-        mbar_arrive_expect_tx(&full[st], SLAB_S_BYTES);
-        bulk_g2s(Sbuf + st * SLAB_S_BYTES, img + (size_t)(s + 3) * SLAB_S_BYTES, SLAB_S_BYTES, &full[st]);
+  } else if (warp == FG_ISSUER) {
+    // ---------------- MMA issue ----------------
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16(128, 128, 0, 0);
+      int gs = 0, guse = 0, ds = 0, duse = 0;
+      for (int k = 0; k < my_items; ++k) {
+        const uint32_t a_addr = smem_u32(Aimg + (k & 1) * SLAB_S_BYTES);
+        w.wait(&a_full[k & 1], (k >> 1) & 1, 0x54);
+        for (int s = 0; s < F_SLABS; ++s) {
+          const uint32_t s_addr = smem_u32(Sbuf + gs * SLAB_S_BYTES);
+          w.wait(&s_full[gs], guse & 1, 0x55);
+          if (duse > 0) w.wait(&d_free[ds], (duse - 1) & 1, 0x56);
+          fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < EP / 16; ++ks)
+            mma_bf16_ss(tmem_base + ds * 128, smem_desc(a_addr + ks * 2 * CT * 16, CT * 16, 128),
+                        smem_desc(s_addr + ks * 2 * 128 * 16, 128 * 16, 128), idesc, ks > 0);
+          mma_commit(&d_full[ds]);
+          mma_commit(&s_free[gs]);
+          if (s == F_SLABS - 1) mma_commit(&a_free[k & 1]);
+          if (++gs == FG_SRING) { gs = 0; ++guse; }
+          if (++ds == FG_DRING) { ds = 0; ++duse; }
+        }
       }
     }
-  }
-  OAL_FOLD_SLAB(F_SLABS - 1);
-#undef OAL_FOLD_SLAB
-  // combine the two halves of every token and write
-  float dx[HD];
-#pragma unroll
-  for (int d = 0; d < HD / 2; ++d) f2_unpack(dxq[d], dx[2 * d], dx[2 * d + 1]);
-  if (wg == 1) {
-#pragma unroll
-    for (int d = 0; d < HD; ++d) red[token * 65 + d] = dx[d];
-  }
-  __syncthreads();
-  if (wg == 0 && i < a.N && !dead) {
-    float* dst = a.dx + (head_off + i) * HD;
-#pragma unroll
-    for (int d4 = 0; d4 < HD; d4 += 4)
-      *reinterpret_cast<float4*>(dst + d4) =
-          make_float4(dx[d4] + red[token * 65 + d4], dx[d4 + 1] + red[token * 65 + d4 + 1],
-                      dx[d4 + 2] + red[token * 65 + d4 + 2], dx[d4 + 3] + red[token * 65 + d4 + 3]);
+    __syncwarp();
+  } else {
+    // ---------------- image / table stream ----------------
+    if (lane == 0) {
+      int gs = 0, guse = 0;
+      for (int k = 0; k < my_items; ++k) {
+        const FgItem it = fg_item(blockIdx.x + k * gridDim.x, a.H, a.rep, a.NB);
+        const int unit = (it.b * a.H + it.h) / a.rep;
+        const unsigned char* img = reinterpret_cast<const unsigned char*>(a.image) +
+                                   ((size_t)unit * a.NB + it.c) * F_SLABS * SLAB_S_BYTES;
+        if (QUERY) {
+          if (k >= 2) {
+            w.wait(&a_free[k & 1], ((k >> 1) - 1) & 1, 0x57);
+            w.wait(&coef_free[k & 1], ((k >> 1) - 1) & 1, 0x58);
+          }
+          mbar_arrive_expect_tx(&a_full[k & 1], SLAB_S_BYTES);
+          bulk_g2s(Aimg + (k & 1) * SLAB_S_BYTES,
+                   reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(it.b * a.H + it.h) * a.NB + it.c) * SLAB_S_BYTES,
+                   SLAB_S_BYTES, &a_full[k & 1]);
+          mbar_arrive_expect_tx(&coef_full[k & 1], F_ROWS * (uint32_t)sizeof(float));
+          bulk_g2s(coef_s + (k & 1) * F_ROWS, a.coef_table + (size_t)it.h * F_ROWS, F_ROWS * (uint32_t)sizeof(float),
+                   &coef_full[k & 1]);
+        }
+        for (int s = 0; s < F_SLABS; ++s) {
+          if (guse > 0) w.wait(&s_free[gs], (guse - 1) & 1, 0x59);
+          mbar_arrive_expect_tx(&s_full[gs], SLAB_S_BYTES);
+          bulk_g2s(Sbuf + gs * SLAB_S_BYTES, img + (size_t)s * SLAB_S_BYTES, SLAB_S_BYTES, &s_full[gs]);
+          if (++gs == FG_SRING) { gs = 0; ++guse; }
+        }
+      }
+    }
+    __syncwarp();
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, 256);
+  if (warp == FG_ISSUER) tmem_dealloc(tmem_base, 512);
   if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
@@ -634,19 +700,24 @@ cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img,
 cudaError_t feature_grad(bool query, const void* x, const void* gimg, const void* v, const void* image,
                          const float* coef_table, float* dx, int B, int H, int rep, int N, int NB, int32_t* status,
                          cudaStream_t st) {
-  const int smem = SLAB_S_BYTES + FG_STAGES * SLAB_S_BYTES + F_ROWS * (int)sizeof(float) + 128 * 65 * (int)sizeof(float);
+  const int smem = FG_SRING * SLAB_S_BYTES + 2 * SLAB_S_BYTES + 2 * F_ROWS * (int)sizeof(float) +
+                   128 * 65 * (int)sizeof(float);
   FeatGradArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gimg),
                  static_cast<const __nv_bfloat16*>(v), static_cast<const __nv_bfloat16*>(image), coef_table, dx,
-                 N, NB, H, rep, status};
+                 N, NB, H, rep, B, status};
   cudaError_t e;
+  int dev = 0, sms = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
+  const int items = B * H * NB, grid = items < sms ? items : sms;
   if (query) {
     e = cudaFuncSetAttribute(feature_grad_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    feature_grad_kernel<true><<<dim3(NB, H, B), 256, smem, st>>>(a);
+    feature_grad_kernel<true><<<grid, FG_THREADS, smem, st>>>(a);
   } else {
     e = cudaFuncSetAttribute(feature_grad_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    feature_grad_kernel<false><<<dim3(NB, H, B), 256, smem, st>>>(a);
+    feature_grad_kernel<false><<<grid, FG_THREADS, smem, st>>>(a);
   }
   return cudaGetLastError();
 }
