@@ -183,7 +183,9 @@ int backward_state_stage(const OalProblem* p, const void* q, const int32_t* dim_
   const bool want_c = mask & OAL_GRAD_COEF;
   cudaError_t e;
   { LaunchScope scope("norm_vjp", st);
-    e = oal::norm_vjp_image(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor, s.g, s.gimg,
+    // the fp32 rows of g are read by the token-pair kernels only (heads with more than 8 groups)
+    e = oal::norm_vjp_image(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor,
+                            p->groups <= 8 ? nullptr : s.g, s.gimg,
                             p->batch * p->q_heads, p->seq_len, nb, st); }
   if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
   { LaunchScope scope("coef_table", st);

@@ -335,23 +335,28 @@ __device__ __forceinline__ void fold_chunk(const float (&v)[16], const f32x2 (&x
   }
 }
 
-template <int S, int HALF, bool QUERY, int P>
-__device__ __forceinline__ void fold_pair_of_chunks(uint32_t taddr, const f32x2 (&xq)[HD / 2], const float* coef,
-                                                    f32x2 (&dxq)[HD / 2]) {
-  float v[16];
-  tmem_ld16(taddr + HALF * 64 + 16 * P, v);
-  tmem_ld_wait();
-  fold_chunk<S * 16 + HALF * 8 + 2 * P, QUERY, 0>(v, xq, coef, dxq);
-  fold_chunk<S * 16 + HALF * 8 + 2 * P + 1, QUERY, 8>(v, xq, coef, dxq);
-}
-
+// Eight chunks = four 16-column loads; the next load is in flight while the previous one is folded.
 template <int S, int HALF, bool QUERY>
 __device__ __forceinline__ void fold_half_slab_impl(uint32_t taddr, const f32x2 (&xq)[HD / 2], const float* coef,
                                                     f32x2 (&dxq)[HD / 2]) {
-  fold_pair_of_chunks<S, HALF, QUERY, 0>(taddr, xq, coef, dxq);
-  fold_pair_of_chunks<S, HALF, QUERY, 1>(taddr, xq, coef, dxq);
-  fold_pair_of_chunks<S, HALF, QUERY, 2>(taddr, xq, coef, dxq);
-  fold_pair_of_chunks<S, HALF, QUERY, 3>(taddr, xq, coef, dxq);
+  constexpr int Q0 = S * 16 + HALF * 8;
+  float va[16], vb[16];
+  tmem_ld16(taddr + HALF * 64, va);
+  tmem_ld_wait();
+  tmem_ld16(taddr + HALF * 64 + 16, vb);
+  fold_chunk<Q0 + 0, QUERY, 0>(va, xq, coef, dxq);
+  fold_chunk<Q0 + 1, QUERY, 8>(va, xq, coef, dxq);
+  tmem_ld_wait();
+  tmem_ld16(taddr + HALF * 64 + 32, va);
+  fold_chunk<Q0 + 2, QUERY, 0>(vb, xq, coef, dxq);
+  fold_chunk<Q0 + 3, QUERY, 8>(vb, xq, coef, dxq);
+  tmem_ld_wait();
+  tmem_ld16(taddr + HALF * 64 + 48, vb);
+  fold_chunk<Q0 + 4, QUERY, 0>(va, xq, coef, dxq);
+  fold_chunk<Q0 + 5, QUERY, 8>(va, xq, coef, dxq);
+  tmem_ld_wait();
+  fold_chunk<Q0 + 6, QUERY, 0>(vb, xq, coef, dxq);
+  fold_chunk<Q0 + 7, QUERY, 8>(vb, xq, coef, dxq);
 }
 
 template <bool QUERY>
@@ -620,61 +625,91 @@ __global__ void dcoef_slots_kernel(const float* dcoef, const int32_t* dim_perm, 
   }
 }
 
-// normalisation VJP writing, besides the fp32 rows, the bf16 operand image of G
-//   rows are enumerated over padded chunks so that tail tokens of the last chunk are zeroed
+// normalisation VJP writing the bf16 operand images of G (hi, lo) and, when `g` is given, its fp32 rows
+//   CTA = 32 consecutive tokens of one (head, chunk); warp = 8 consecutive columns, lane = token, so a
+//   warp stores 512 contiguous bytes of an image chunk.  Rows are enumerated over padded chunks so
+//   that tail tokens of the last chunk are zeroed.
 __global__ void __launch_bounds__(256) norm_vjp_image_kernel(const void* grad_out, int out_dt, const float* grad_num,
                                                              const float* grad_den, const float* num,
                                                              const float* den, float floor_v, float* g,
                                                              __nv_bfloat16* gimg, int N, int NB, int heads) {
-  const size_t r = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
+  __shared__ float part[8][32];
+  const int ec = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t per_head = (size_t)NB * CT;
-  if (r >= per_head * heads) return;
+  const size_t r = (size_t)blockIdx.x * 32 + lane;          // grid covers heads * per_head rows exactly
   const size_t bh = r / per_head;
   const int t = (int)(r % per_head);
   const int cidx = t / CT, tl = t % CT;
-  float gv[2] = {0.f, 0.f}, gd = 0.f;
-  if (t < N) {
-    const size_t row = bh * N + t;
-    const float dn = den[row];
-    const float dw = fmaxf(dn, floor_v);
-    float dot = 0.f;
-    if (grad_out) {
+  const bool live = t < N;
+  const size_t row = bh * N + t;
+  float gv[8], dot = 0.f, dn = 1.f, dw = 1.f;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const float go = load_elem(grad_out, row * VD + lane + 32 * c, out_dt);
-        dot = fmaf(go, num[row * VD + lane + 32 * c], dot);
-        gv[c] = go / dw;
+  for (int j = 0; j < 8; ++j) gv[j] = 0.f;
+  if (live) {
+    dn = den[row];
+    dw = fmaxf(dn, floor_v);
+    if (grad_out) {
+      float go[8];
+      if (out_dt == OAL_DTYPE_BF16) {
+        const uint4 w = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grad_out) + row * VD + 8 * ec);
+        unpack_bf16x8(w, go);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) go[j] = load_elem(grad_out, row * VD + 8 * ec + j, out_dt);
+      }
+      const float4 n0 = *reinterpret_cast<const float4*>(num + row * VD + 8 * ec);
+      const float4 n1 = *reinterpret_cast<const float4*>(num + row * VD + 8 * ec + 4);
+      const float nn[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        dot = fmaf(go[j], nn[j], dot);
+        gv[j] = go[j] / dw;
       }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      if (grad_num) gv[c] += grad_num[row * VD + lane + 32 * c];
-      g[row * EP + lane + 32 * c] = gv[c];
+    if (grad_num) {
+      const float4 a0 = *reinterpret_cast<const float4*>(grad_num + row * VD + 8 * ec);
+      const float4 a1 = *reinterpret_cast<const float4*>(grad_num + row * VD + 8 * ec + 4);
+      gv[0] += a0.x; gv[1] += a0.y; gv[2] += a0.z; gv[3] += a0.w;
+      gv[4] += a1.x; gv[5] += a1.y; gv[6] += a1.z; gv[7] += a1.w;
     }
-    if (grad_out) gd = (dn >= floor_v) ? -(dot / dw) / dw : 0.f;
-    if (grad_den) gd += grad_den[row];
-    if (lane < EP - VD) g[row * EP + VD + lane] = lane == 0 ? gd : 0.f;
   }
+  part[ec][lane] = dot;
   // hi image = bf16(g); lo image = bf16(g - hi): dW = g . [v|1] is formed from both, because its two
   // large terms (dout.v / den and dout.num / den^2) nearly cancel
-  __nv_bfloat16* img = gimg + (bh * NB + cidx) * (size_t)(SLAB_S_BYTES / 2);
-  __nv_bfloat16* img_lo = img + (size_t)heads * NB * (SLAB_S_BYTES / 2);
+  uint4* img = reinterpret_cast<uint4*>(gimg + (bh * NB + cidx) * (size_t)(SLAB_S_BYTES / 2));
+  uint4* img_lo = reinterpret_cast<uint4*>(gimg + ((size_t)heads * NB + bh * NB + cidx) * (size_t)(SLAB_S_BYTES / 2));
+  {
+    uint32_t hi[4], lo[4];
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    const int e = lane + 32 * c;
-    const __nv_bfloat16 hi = __float2bfloat16_rn(gv[c]);
-    img[((e >> 3) * CT + tl) * 8 + (e & 7)] = hi;
-    img_lo[((e >> 3) * CT + tl) * 8 + (e & 7)] = __float2bfloat16_rn(gv[c] - __bfloat162float(hi));
+    for (int k = 0; k < 4; ++k) {
+      const __nv_bfloat16 h0 = __float2bfloat16_rn(gv[2 * k]), h1 = __float2bfloat16_rn(gv[2 * k + 1]);
+      hi[k] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+      lo[k] = pack_bf16(gv[2 * k] - __bfloat162float(h0), gv[2 * k + 1] - __bfloat162float(h1));
+    }
+    img[ec * CT + tl] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    img_lo[ec * CT + tl] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
   }
-  if (lane < EP - VD) {
-    const int e = VD + lane;
-    const float val = lane == 0 ? gd : 0.f;
-    const __nv_bfloat16 hi = __float2bfloat16_rn(val);
-    img[((e >> 3) * CT + tl) * 8 + (e & 7)] = hi;
-    img_lo[((e >> 3) * CT + tl) * 8 + (e & 7)] = __float2bfloat16_rn(val - __bfloat162float(hi));
+  if (g && live) {
+    *reinterpret_cast<float4*>(g + row * EP + 8 * ec) = make_float4(gv[0], gv[1], gv[2], gv[3]);
+    *reinterpret_cast<float4*>(g + row * EP + 8 * ec + 4) = make_float4(gv[4], gv[5], gv[6], gv[7]);
+  }
+  __syncthreads();
+  if (ec < 2) {            // columns 64..79: [d den, 0 x 15]
+    float gd = 0.f;
+    if (ec == 0 && live) {
+      float d = 0.f;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) d += part[x][lane];
+      if (grad_out) gd = (dn >= floor_v) ? -(d / dw) / dw : 0.f;
+      if (grad_den) gd += grad_den[row];
+    }
+    const __nv_bfloat16 h0 = __float2bfloat16_rn(gd);
+    img[(VD / 8 + ec) * CT + tl] = make_uint4((uint32_t)__bfloat16_as_ushort(h0), 0u, 0u, 0u);
+    img_lo[(VD / 8 + ec) * CT + tl] = make_uint4(pack_bf16(gd - __bfloat162float(h0), 0.f), 0u, 0u, 0u);
+    if (g && live) {
+      *reinterpret_cast<float4*>(g + row * EP + VD + 8 * ec) = make_float4(gd, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(g + row * EP + VD + 8 * ec + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
 }
 
@@ -734,8 +769,8 @@ cudaError_t dcoef_reduce(const float* partial, int outer, int Hq, const int32_t*
 cudaError_t norm_vjp_image(const void* grad_out, int out_dt, const float* grad_num, const float* grad_den,
                            const float* num, const float* den, float floor_v, float* g, void* gimg, int heads,
                            int N, int NB, cudaStream_t st) {
-  const size_t rows = (size_t)heads * NB * CT;
-  norm_vjp_image_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(grad_out, out_dt, grad_num, grad_den, num, den,
+  const size_t rows = (size_t)heads * NB * CT;      // a multiple of 32
+  norm_vjp_image_kernel<<<(unsigned)(rows / 32), 256, 0, st>>>(grad_out, out_dt, grad_num, grad_den, num, den,
                                                                    floor_v, g, static_cast<__nv_bfloat16*>(gimg), N,
                                                                    NB, heads);
   return cudaGetLastError();
