@@ -65,24 +65,27 @@ constexpr int DS_COLS = EP / 2; // columns per drain thread
 static_assert(DS_GEN_WARPS * 32 == CT, "one generator thread per token");
 static_assert(DS_GEN_WARPS % 4 == 0, "drain warp w must sit on tensor-memory lane quadrant w % 4");
 
-// (item, head) cursor of one role; advancing costs a division only when the item changes
+// (item, head) cursor of one role; the divisions happen only when the item changes
 struct DsCursor {
   int u, c, slab, hh, item;
-  __device__ __forceinline__ void set_item(int it_item, int NB) {
+  int b, h0;          // batch row and first query head of the item's KV head
+  __device__ __forceinline__ void set_item(int it_item, int NB, int Hkv, int rep) {
     item = it_item;
     slab = item % F_SLABS;
     const int r = item / F_SLABS;
     c = r % NB;
     u = r / NB;
+    b = u / Hkv;
+    h0 = (u - b * Hkv) * rep;
   }
-  __device__ __forceinline__ void start(int NB) {
+  __device__ __forceinline__ void start(int NB, int Hkv, int rep) {
     hh = 0;
-    set_item(blockIdx.x, NB);
+    set_item(blockIdx.x, NB, Hkv, rep);
   }
-  __device__ __forceinline__ void next(int rep, int NB) {
+  __device__ __forceinline__ void next(int rep, int NB, int Hkv) {
     if (++hh == rep) {
       hh = 0;
-      set_item(item + gridDim.x, NB);
+      set_item(item + gridDim.x, NB, Hkv, rep);
     }
   }
 };
@@ -123,9 +126,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
     const int token = tid;
     uint4 nx[8];                               // packed q row of the next (item, head)
     auto fetch = [&](const DsCursor& d) {
-      const int b = d.u / a.Hkv, h = (d.u % a.Hkv) * rep + d.hh, i = d.c * CT + token;
+      const int h = d.h0 + d.hh, i = d.c * CT + token;
       if (i < a.N) {
-        const uint4* p = reinterpret_cast<const uint4*>(a.q + ((size_t)(b * a.Hq + h) * a.N + i) * HD);
+        const uint4* p = reinterpret_cast<const uint4*>(a.q + ((size_t)(d.b * a.Hq + h) * a.N + i) * HD);
 #pragma unroll
         for (int j = 0; j < 8; ++j) nx[j] = p[j];
       } else {
@@ -134,7 +137,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
       }
     };
     DsCursor cur;
-    cur.start(a.NB);
+    cur.start(a.NB, a.Hkv, rep);
     if (T > 0) fetch(cur);
     int s = 0, use = 0;                       // ring slot of `it` and how often it has been used before
     for (int it = 0; it < T; ++it) {
@@ -147,7 +150,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
         xp[4 * j + 2] = nx[j].z;
         xp[4 * j + 3] = nx[j].w;
       }
-      cur.next(rep, a.NB);
+      cur.next(rep, a.NB, a.Hkv);
       if (it + 1 < T) fetch(cur);             // in flight while this slab is generated
       if (use > 0) w.wait(&mma_done[s], (use - 1) & 1, 0x31);   // the MMA that read A[s] has completed
       write_slab_raw(slab, xp, reinterpret_cast<uint4*>(Abuf + s * SLAB_A_BYTES) + token);
@@ -165,17 +168,17 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
 #pragma unroll
     for (int e = 0; e < DS_COLS / 8; ++e) cpk[e] = make_uint4(0u, 0u, 0u, 0u);
     DsCursor d, dn;
-    d.start(a.NB);
+    d.start(a.NB, a.Hkv, rep);
     dn = d;
     int s = 0, use = 0;
-    float cf_next = T > 0 ? a.coef_table[(size_t)((d.u % a.Hkv) * rep) * F_ROWS + d.slab * 128 + fr] : 0.f;
+    float cf_next = T > 0 ? a.coef_table[(size_t)d.h0 * F_ROWS + d.slab * 128 + fr] : 0.f;
     for (int it = 0; it < T; ++it) {
-      const int b = d.u / a.Hkv, h = (d.u % a.Hkv) * rep + d.hh, f = d.slab * 128 + fr;
+      const int b = d.b, h = d.h0 + d.hh, f = d.slab * 128 + fr;
       const float fs = feature_scale_factor(f, a.scale);   // d(table entry) / d(coefficient)
       const float cf = cf_next;
-      dn.next(rep, a.NB);
+      dn.next(rep, a.NB, a.Hkv);
       if (it + 1 < T)       // coefficient of the next (item, head): in flight during this drain
-        cf_next = a.coef_table[(size_t)((dn.u % a.Hkv) * rep + dn.hh) * F_ROWS + dn.slab * 128 + fr];
+        cf_next = a.coef_table[(size_t)(dn.h0 + dn.hh) * F_ROWS + dn.slab * 128 + fr];
       if (d.hh == 0 && a.carry_img) {
         const uint4* cp = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(a.carry_img) +
                                                          (((size_t)d.u * a.NB + d.c) * F_SLABS + d.slab) * SLAB_S_BYTES);
@@ -228,7 +231,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
           *reinterpret_cast<float4*>(dst + r * 1024 + 4) = make_float4(vv[r][4], vv[r][5], vv[r][6], vv[r][7]);
         }
       }
-      d.next(rep, a.NB);
+      d = dn;
       if (++s == DS_RING) { s = 0; ++use; }
     }
   } else if (warp == DS_ISSUER) {
@@ -259,16 +262,16 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
     // ---------------- G image stream ----------------
     if (lane == 0) {
       DsCursor d;
-      d.start(a.NB);
+      d.start(a.NB, a.Hkv, rep);
       int gs = 0, guse = 0;
       for (int it = 0; it < T; ++it) {
-        const int b = d.u / a.Hkv, h = (d.u % a.Hkv) * rep + d.hh;
+        const int h = d.h0 + d.hh;
         const unsigned char* src =
-            reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.Hq + h) * a.NB + d.c) * SLAB_S_BYTES;
+            reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(d.b * a.Hq + h) * a.NB + d.c) * SLAB_S_BYTES;
         if (guse > 0) w.wait(&g_free[gs], (guse - 1) & 1, 0x36);
         mbar_arrive_expect_tx(&g_full[gs], SLAB_S_BYTES);
         bulk_g2s(Gbuf + gs * SLAB_S_BYTES, src, SLAB_S_BYTES, &g_full[gs]);
-        d.next(rep, a.NB);
+        d.next(rep, a.NB, a.Hkv);
         if (++gs == DS_GRING) { gs = 0; ++guse; }
       }
     }
@@ -577,12 +580,24 @@ __global__ void __launch_bounds__(FG_THREADS, 1) feature_grad_kernel(const FeatG
 // ---------------------------------------------------------------------------
 // coefficient gradients of the cross-chunk term: per-feature sums -> (A, B_g, C_gg') slots
 // ---------------------------------------------------------------------------
-__global__ void dcoef_sum_kernel(const float* partial, int outer /* B*NB */, int Hq, float* dcoef) {
-  const int f = blockIdx.x * blockDim.x + threadIdx.x, h = blockIdx.y;
-  if (f >= F_ROWS) return;
+// block = 32 feature rows x 8 segments of the outer index; the segments are added in fixed order
+__global__ void __launch_bounds__(256) dcoef_sum_kernel(const float* partial, int outer /* B*NB*2 */, int Hq,
+                                                        float* dcoef) {
+  __shared__ float seg_sum[8][32];
+  const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+  const int f = blockIdx.x * 32 + lane, h = blockIdx.y;
+  const int per = (outer + 7) / 8, o0 = seg * per, o1 = min(outer, o0 + per);
   float t = 0.f;
-  for (int o = 0; o < outer; ++o) t += partial[((size_t)o * Hq + h) * F_ROWS + f];
-  dcoef[(size_t)h * F_ROWS + f] = t;
+#pragma unroll 4
+  for (int o = o0; o < o1; ++o) t += partial[((size_t)o * Hq + h) * F_ROWS + f];
+  seg_sum[seg][lane] = t;
+  __syncthreads();
+  if (seg == 0) {
+    float r = 0.f;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) r += seg_sum[x][lane];
+    dcoef[(size_t)h * F_ROWS + f] = r;
+  }
 }
 
 __device__ __forceinline__ int tri_slot(int g, int g2) { return g * GMAX - (g * (g - 1)) / 2 + (g2 - g); }
@@ -759,7 +774,7 @@ cudaError_t feature_grad(bool query, const void* x, const void* gimg, const void
 
 cudaError_t dcoef_reduce(const float* partial, int outer, int Hq, const int32_t* dim_perm,
                          const int32_t* group_start, float* dcoef, float* slots, cudaStream_t st) {
-  dcoef_sum_kernel<<<dim3((F_ROWS + 255) / 256, Hq), 256, 0, st>>>(partial, outer, Hq, dcoef);
+  dcoef_sum_kernel<<<dim3(F_ROWS / 32, Hq), 256, 0, st>>>(partial, outer, Hq, dcoef);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dcoef_slots_kernel<<<Hq, 256, 0, st>>>(dcoef, dim_perm, group_start, slots);
