@@ -177,9 +177,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
-    // back off so that waiting warps do not take issue slots from working ones; look at the clock
-    // only now and then
-    __nanosleep(64);
+    // The first polls go back to back (try_wait itself suspends the thread for a while): the hand-offs
+    // between the roles of the pipelined kernels are short, and a sleep here would add its length to
+    // every one of them.  Long waits back off so that they do not take issue slots from working warps.
+    // The clock is looked at only now and then.
+    if (spin >= 16) __nanosleep(64);
     if ((spin & 15) == 0) {
       const long long now = clock64();
       if (t0 == 0) t0 = now;
