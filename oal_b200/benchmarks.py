@@ -8,6 +8,12 @@
         sequence-parallel forward+backward: the sequence is cut into P contiguous ranges, one
         all-gather of the range-final states per direction (NCCL).
 
+    [torchrun --nproc-per-node P] -m oal_b200.benchmarks step [--layers 24] [--batch 8] [--seq 4096]
+        model-level training step: Qwen2.5-0.5B-shaped decoder stack (random weights, LoRA rank 16 on
+        q/k/v/o, trainable kernel factors, synthetic token ids) with the operator in every layer;
+        forward, backward, gradient all-reduce of the trainable parameters across ranks (batch
+        parallel), AdamW step.  Reports the share of the step spent in the operator's kernels.
+
 Each measurement prints one JSON line (rank 0).  Inputs are the seeded synthetic tensors of
 ``oal_b200.synthetic``.
 """
@@ -100,9 +106,69 @@ def sequence_parallel(n: int, steps: int, warmup: int) -> None:
         dist.destroy_process_group()
 
 
+def training_step(layers: int, batch: int, n: int, steps: int, warmup: int) -> None:
+    import torch.distributed as dist
+
+    from .qwen_block import QwenOalStack
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(1234)                                   # same weights on every rank
+    model = QwenOalStack(num_layers=layers, device=dev)
+    params = model.trainable_parameters()
+    opt = torch.optim.AdamW(params, lr=1e-4, weight_decay=0.0, fused=True)
+    gen = torch.Generator(device=dev).manual_seed(99 + rank)  # each rank its own batch
+    ids = torch.randint(0, model.embed.num_embeddings, (batch, n), generator=gen, device=dev)
+    losses = []
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = model(ids)
+        loss.backward()
+        if world > 1:
+            flat = torch.cat([p.grad.reshape(-1).float() for p in params])
+            dist.all_reduce(flat)
+            flat /= world
+            off = 0
+            for p in params:
+                p.grad.copy_(flat[off:off + p.numel()].view_as(p.grad))
+                off += p.numel()
+        opt.step()
+        losses.append(loss.detach())
+
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([_time_steps(step, steps, warmup)], device=dev, dtype=torch.float64)
+    # the operator's share: its kernels timed by the library's own event pairs over one more step
+    _lib.profile_enable(True)
+    step()
+    torch.cuda.synchronize()
+    report = _lib.profile_report()
+    _lib.profile_enable(False)
+    op_ms = sum(v[1] for v in report.values()) if report else float("nan")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps(dict(benchmark="training_step", layers=layers, batch_per_rank=batch, n=n, ranks=world,
+                              ms_per_step=ms.item(), tokens_per_s=world * batch * n / (ms.item() * 1e-3),
+                              operator_ms_per_step=op_ms, operator_share=op_ms / ms.item(),
+                              trainable_parameters=sum(p.numel() for p in params),
+                              first_loss=float(losses[0]), last_loss=float(losses[-1]),
+                              peak_memory_gb=torch.cuda.max_memory_allocated(dev) / 2**30)), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("mode", choices=["sweep", "sp"])
+    ap.add_argument("mode", choices=["sweep", "sp", "step"])
+    ap.add_argument("--layers", type=int, default=24)
+    ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", default=None, help="sequence length(s), comma separated")
     ap.add_argument("--groups", default="1,4,8,16")
     ap.add_argument("--steps", type=int, default=5)
@@ -111,8 +177,10 @@ def main():
     if a.mode == "sweep":
         ns = [int(x) for x in (a.seq or "1024,4096,16384,65536").split(",")]
         sweep(ns, [int(x) for x in a.groups.split(",")], a.steps, a.warmup)
-    else:
+    elif a.mode == "sp":
         sequence_parallel(int(a.seq or 32768), a.steps, a.warmup)
+    else:
+        training_step(a.layers, a.batch, int(a.seq or 4096), a.steps, a.warmup)
 
 
 if __name__ == "__main__":

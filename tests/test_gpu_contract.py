@@ -102,3 +102,80 @@ def test_workspace_too_small_is_a_value_error():
     rc = _lib.load().oal_forward(ctypes.byref(problem), p, p, p, p, p, p, p, p, p, p, p, p, None, p, 16, p, None)
     with pytest.raises(ValueError, match="workspace too small"):
         _lib.check(rc)
+
+
+# ---- the rest of the public-entry semantics the reference pins (test_grouped_quadratic.py:135-183,
+# :223-262, :417-427, :464-473 there), replayed through oal_b200.oal_attention on the GPU ----------------
+
+def _dense(q, k, v, groups, factor, scale, kernel_eps=1e-6):
+    a, b, c = orc.expand_factor(factor.double(), q.shape[1], kernel_eps)
+    return orc.dense_forward(q.double(), k.double(), v.double(), groups, a, b, c, scale=scale)
+
+
+def test_public_entry_matches_dense_oracle_with_unnormalized_outputs():
+    q, k, v = _case(dimension=4)
+    groups, factor = _groups(dimension=4), _factor()
+    out, num, den = oal_b200.oal_attention(q.cuda(), k.cuda(), v.cuda(), groups.cuda(), factor.cuda(), scale=0.37,
+                                           kernel_eps=0.07, causal=True, return_unnormalized=True)
+    want, want_num, want_den = _dense(q, k, v, groups, factor, 0.37, 0.07)
+    assert ERR(out, want) < 1e-5 and ERR(num, want_num) < 1e-5 and ERR(den, want_den) < 1e-5
+    assert num.dtype == torch.float32 and den.dtype == torch.float32
+    assert torch.isfinite(den).all() and (den > 0).all()
+
+
+def test_fixed_initialization_is_independent_of_legal_group_partition():
+    q, k, v = (t.cuda() for t in _case(query_heads=1, key_heads=1, dimension=4))
+    factor = torch.tensor((1.0, 0.5, 0.5, 0.5, 0.5, 0.0)).cuda()
+    out_a = oal_b200.oal_attention(q, k, v, torch.tensor((0, 0, 1, 1)).cuda(), factor)
+    out_b = oal_b200.oal_attention(q, k, v, torch.tensor((0, 1, 0, 1)).cuda(), factor)
+    assert ERR(out_a, out_b) < 1e-5
+
+
+def test_cross_group_coefficient_changes_result():
+    q, k, v = (t.cuda() for t in _case(query_heads=1, key_heads=1, dimension=4))
+    groups = torch.tensor((0, 0, 1, 1), dtype=torch.int32).cuda()
+    factor = _factor().cuda()
+    no_cross = factor.clone()
+    no_cross[3] = 0.0
+    assert not torch.allclose(oal_b200.oal_attention(q, k, v, groups, factor),
+                              oal_b200.oal_attention(q, k, v, groups, no_cross))
+
+
+@pytest.mark.parametrize("precision,io_dtype,tol", [("fp32_ieee", torch.float32, 1e-4),
+                                                     ("bf16_tensorcore", torch.bfloat16, 2e-2)])
+def test_factor_and_qkv_gradients_match_dense_oracle_through_the_public_entry(precision, io_dtype, tol):
+    q0, k0, v0 = (t.to(io_dtype).float() for t in _case(sequence=150))
+    groups, factor0 = _groups(), _factor().expand(q0.shape[1], -1).clone()
+    q, k, v = (t.to(device="cuda", dtype=io_dtype).requires_grad_() for t in (q0, k0, v0))
+    factor = factor0.cuda().requires_grad_()
+    out = oal_b200.oal_attention(q, k, v, groups.cuda(), factor, precision=precision, output_dtype=torch.float32)
+    g = torch.Generator().manual_seed(7)
+    dout = torch.randn(out.shape, generator=g)
+    out.backward(dout.cuda())
+    qd, kd, vd = (t.double().requires_grad_() for t in (q0, k0, v0))
+    fd = factor0.double().requires_grad_()
+    a, b, c = orc.expand_factor(fd, q0.shape[1], 1e-6)
+    want, _, _ = orc.dense_forward(qd, kd, vd, groups, a, b, c, scale=q0.shape[-1] ** -0.5)
+    want.backward(dout.double())
+    assert ERR(out, want.detach()) < tol
+    for got, ref in ((q.grad, qd.grad), (k.grad, kd.grad), (v.grad, vd.grad), (factor.grad, fd.grad)):
+        assert ERR(got, ref) < tol
+
+
+def test_default_scale_is_d_inverse_sqrt():
+    q, k, v = (t.cuda() for t in _case(dimension=4))
+    groups, factor = _groups(dimension=4).cuda(), _factor().cuda()
+    assert ERR(oal_b200.oal_attention(q, k, v, groups, factor),
+               oal_b200.oal_attention(q, k, v, groups, factor, scale=0.5)) < 1e-6
+    with pytest.raises(ValueError):     # D > 64 is a reference-execution feature only
+        wide = torch.randn(1, 1, 8, 72, device="cuda")
+        oal_b200.oal_attention(wide, wide, wide, torch.zeros(72, dtype=torch.int32, device="cuda"),
+                               torch.tensor((1.0, 0.5, 0.5), device="cuda"))
+
+
+def test_shared_dim_groups_remain_a_logical_broadcast():
+    q, k, v = (t.cuda() for t in _case())
+    groups, factor = _groups(), _factor().cuda()
+    shared = oal_b200.oal_attention(q, k, v, groups[0].cuda(), factor)
+    expanded = oal_b200.oal_attention(q, k, v, groups.cuda(), factor)
+    assert torch.equal(shared, expanded)
