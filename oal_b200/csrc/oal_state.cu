@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(256) state_scan_kernel(const float* ds, __nv_b
 }
 
 // ---------------------------------------------------------------------------
-// cross_read: Y[i, 0:80] = phi(i) . state_image[u, c]   (sum over all 17 slabs)
+// cross_read: Y[i, 0:80] = phi(i) . state_image[u, c]   (sum over all slabs)
 //   QUERY : phi = phi_q of head h (coefficient table with the query scale folded in), x = q, output num/den
 //   !QUERY: phi = phi_k, x = k, output columns 0..63 (the value part) to out64
 // ---------------------------------------------------------------------------
