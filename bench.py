@@ -57,13 +57,26 @@ def measured_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs."""
+    """SM clocks and throttle reasons (read-only) while the GPU is under load.
+
+    A separate ``nvidia-smi`` process does the sampling, so that the Python thread that launches the
+    kernels cannot starve it; samples are kept when their timestamp lies inside the window the caller
+    marks (warm-up and timed steps).  Without nvidia-smi an NVML thread in this process is used.
+    """
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.samples, self.max_mhz, self.bits = index, [], None, 0
-        self.stop, self.thread, self.error = threading.Event(), None, None
+        self.stop, self.thread, self.error, self.proc = threading.Event(), None, None, None
+        self.t_begin = self.t_end = None
+
+    def _uuid(self):
+        uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+        return uuid if uuid.startswith("GPU-") else "GPU-" + uuid
 
     def _run(self):
         try:
@@ -71,35 +84,83 @@ class ClockSampler:
 
             pynvml.nvmlInit()
             try:
-                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
-                handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(self._uuid())
             except Exception:
                 handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
             while not self.stop.is_set():
-                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                now = time.time()
+                mhz = float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
                 try:
-                    self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                    bits = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
                 except Exception:
-                    self.bits |= int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                    bits = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                self.samples.append((now, mhz, bits))
                 time.sleep(0.005)
         except Exception as exc:      # NVML missing: report no samples rather than fail the run
             self.error = repr(exc)
 
     def __enter__(self):
-        self.thread = threading.Thread(target=self._run, daemon=True)
-        self.thread.start()
-        time.sleep(0.05)
+        import shutil
+        import subprocess
+
+        smi = shutil.which("nvidia-smi")
+        if smi:
+            try:
+                self.proc = subprocess.Popen([smi, f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                              "-i", self._uuid(), "-lms", "10"], stdout=subprocess.PIPE,
+                                             stderr=subprocess.DEVNULL, text=True)
+            except Exception as exc:
+                self.error, self.proc = repr(exc), None
+        if self.proc is None:
+            self.thread = threading.Thread(target=self._run, daemon=True)
+            self.thread.start()
+        time.sleep(0.3)               # let the sampler come up before the load starts
         return self
 
+    def begin(self):
+        self.t_begin = time.time()
+
+    def end(self):
+        self.t_end = time.time()
+
     def __exit__(self, *exc):
+        if self.t_end is None:
+            self.end()
         self.stop.set()
-        self.thread.join(timeout=5)
+        if self.thread is not None:
+            self.thread.join(timeout=5)
+        if self.proc is not None:
+            import datetime
+
+            self.proc.terminate()
+            try:
+                text, _ = self.proc.communicate(timeout=5)
+            except Exception:
+                self.proc.kill()
+                text = ""
+            for line in text.splitlines():
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 7:
+                    continue
+                try:
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    mhz, self.max_mhz = float(f[1]), float(f[2])
+                except ValueError:
+                    continue
+                bits = sum(bit for bit, col in ((0x8, 3), (0x40, 4), (0x20, 5), (0x4, 6)) if f[col] == "Active")
+                self.samples.append((ts, mhz, bits))
+        lo, hi = self.t_begin or 0.0, self.t_end
+        kept = [(m, b) for t, m, b in self.samples if lo <= t <= hi]
+        self.window = kept
+        for _, b in kept:
+            self.bits |= b
 
     def summary(self) -> dict:
         reasons = sorted(name for bit, name in self.REASONS.items() if self.bits & bit)
-        out = dict(sm_mhz=statistics.median(self.samples) if self.samples else None, sm_max_mhz=self.max_mhz,
-                   reasons=reasons, samples=len(self.samples))
+        mhz = [m for m, _ in self.window]
+        out = dict(sm_mhz=statistics.median(mhz) if mhz else None, sm_max_mhz=self.max_mhz,
+                   reasons=reasons, samples=len(mhz), sampler="nvidia-smi" if self.proc is not None else "nvml")
         if self.error:
             out["error"] = self.error
         return out
@@ -222,15 +283,15 @@ def run_gpu_arm(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(max(args.warmup, 3)):
-        step(sets[i % 2]["dev"])
-    barrier()
-
-    # ---- timed region: K steps, CUDA events on the launching stream, L2 flushed between steps
-    launches0 = _lib.launch_count()
+    # ---- warm-up, then the timed region: K steps, CUDA events on the launching stream, L2 flushed between
+    # steps; the clock sampler keeps the samples taken while the GPU is under load (warm-up + timed steps)
     events = []
     with ClockSampler(local) as clocks:
+        clocks.begin()
+        for i in range(max(args.warmup, 3)):
+            step(sets[i % 2]["dev"])
         barrier()
+        launches0 = _lib.launch_count()
         for i in range(args.steps):
             flush.fill_(i & 0xFF)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -239,6 +300,7 @@ def run_gpu_arm(args) -> None:
             e1.record()
             events.append((e0, e1))
         barrier()
+        clocks.end()
     launches = _lib.launch_count() - launches0
     total_ms = sum(a.elapsed_time(b) for a, b in events)
     clock_summary = clocks.summary()
