@@ -160,56 +160,64 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
   if (tiles >= 2) w.wait(&w_done[(tiles - 2) & 1], ((tiles - 2) >> 1) & 1, 0x13);
   if (tiles >= 1) w.wait(&w_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, 0x14);
   fence_after_sync();
-  // epilogue: add the cross-chunk part, normalise, status
+  // epilogue: add the cross-chunk part, normalise, status.  The intra-chunk numerators go through a
+  // row-major staging tile in shared memory (the q / k / U images are idle now) so that the global
+  // reads and writes below are full 16- and 32-byte vectors, contiguous across the lanes of a warp.
   const int i = c * CT + row;
   const size_t orow = qoff + i;
   const int col0 = half == 0 ? 0 : 48, ncol = half == 0 ? 48 : 32;
-  float y[48];
+  float* stage_out = reinterpret_cast<float*>(smem);        // [128][65] fp32, fits in Qimg + Kimg + Uimg
+  int flags = 0;
 #pragma unroll
   for (int cc = 0; cc < 48; cc += 16) {
     if (cc < ncol) {
       float vv[16];
       tmem_ld16(tY + lane_off + col0 + cc, vv);
       tmem_ld_wait();
+      if (col0 + cc < VD) {
 #pragma unroll
-      for (int x = 0; x < 16; ++x) y[cc + x] = vv[x];
+        for (int x = 0; x < 16; ++x) stage_out[row * 65 + col0 + cc + x] = vv[x];
+      } else {
+        float den = vv[0];                    // column 64
+        if (i < a.N && !bad) {
+          den += a.den[orow];
+          a.den[orow] = den;
+          if (!finite_f(den)) flags |= OAL_STATUS_NONFINITE;
+          else if (!(den > 0.f)) flags |= OAL_STATUS_DENOMINATOR;
+        }
+        den_s[row] = den;
+      }
     }
-  }
-  int flags = 0;
-  if (half == 1) {
-    float den = y[16];                      // column 64
-    if (i < a.N && !bad) {
-      den += a.den[orow];
-      a.den[orow] = den;
-      if (!finite_f(den)) flags |= OAL_STATUS_NONFINITE;
-      else if (!(den > 0.f)) flags |= OAL_STATUS_DENOMINATOR;
-    }
-    den_s[row] = den;
   }
   __syncthreads();
-  if (i < a.N && !dead && !bad) {
-    const float dn = fmaxf(den_s[row], a.floor);
-    const int nval = half == 0 ? 48 : 16;
+  if (!dead && !bad) {
+    for (int x = tid; x < CT * 8; x += 256) {
+      const int r = x >> 3, seg = x & 7, ii = c * CT + r;
+      if (ii >= a.N) continue;
+      const float dn = fmaxf(den_s[r], a.floor);
+      const size_t oo = (qoff + ii) * VD + seg * 8;
+      float* np = a.num + oo;
+      const float4 o0 = *reinterpret_cast<const float4*>(np), o1 = *reinterpret_cast<const float4*>(np + 4);
+      const float* sp = stage_out + r * 65 + seg * 8;
+      const float n[8] = {sp[0] + o0.x, sp[1] + o0.y, sp[2] + o0.z, sp[3] + o0.w,
+                          sp[4] + o1.x, sp[5] + o1.y, sp[6] + o1.z, sp[7] + o1.w};
+      *reinterpret_cast<float4*>(np) = make_float4(n[0], n[1], n[2], n[3]);
+      *reinterpret_cast<float4*>(np + 4) = make_float4(n[4], n[5], n[6], n[7]);
+      bool fin = true;
 #pragma unroll
-    for (int x4 = 0; x4 < 48; x4 += 4) {
-      if (x4 < nval) {
-        float* np = a.num + orow * VD + col0 + x4;
-        const float4 o = *reinterpret_cast<const float4*>(np);
-        const float n0 = y[x4] + o.x, n1 = y[x4 + 1] + o.y, n2 = y[x4 + 2] + o.z, n3 = y[x4 + 3] + o.w;
-        *reinterpret_cast<float4*>(np) = make_float4(n0, n1, n2, n3);
-        if (!(finite_f(n0) && finite_f(n1) && finite_f(n2) && finite_f(n3))) flags |= OAL_STATUS_NONFINITE;
-        const size_t oo = orow * VD + col0 + x4;          // four consecutive outputs, one vector store
-        if (a.out_dt == OAL_DTYPE_BF16) {
-          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(a.out) + oo) =
-              make_uint2(pack_bf16(n0 / dn, n1 / dn), pack_bf16(n2 / dn, n3 / dn));
-        } else if (a.out_dt == OAL_DTYPE_F32) {
-          *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + oo) = make_float4(n0 / dn, n1 / dn, n2 / dn, n3 / dn);
-        } else {
-          store_elem(a.out, oo, a.out_dt, n0 / dn);
-          store_elem(a.out, oo + 1, a.out_dt, n1 / dn);
-          store_elem(a.out, oo + 2, a.out_dt, n2 / dn);
-          store_elem(a.out, oo + 3, a.out_dt, n3 / dn);
-        }
+      for (int j = 0; j < 8; ++j) fin = fin && finite_f(n[j]);
+      if (!fin) flags |= OAL_STATUS_NONFINITE;
+      if (a.out_dt == OAL_DTYPE_BF16) {
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + oo) =
+            make_uint4(pack_bf16(n[0] / dn, n[1] / dn), pack_bf16(n[2] / dn, n[3] / dn),
+                       pack_bf16(n[4] / dn, n[5] / dn), pack_bf16(n[6] / dn, n[7] / dn));
+      } else if (a.out_dt == OAL_DTYPE_F32) {
+        float* op = reinterpret_cast<float*>(a.out) + oo;
+        *reinterpret_cast<float4*>(op) = make_float4(n[0] / dn, n[1] / dn, n[2] / dn, n[3] / dn);
+        *reinterpret_cast<float4*>(op + 4) = make_float4(n[4] / dn, n[5] / dn, n[6] / dn, n[7] / dn);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) store_elem(a.out, oo + j, a.out_dt, n[j] / dn);
       }
     }
   }
