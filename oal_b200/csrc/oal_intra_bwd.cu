@@ -24,6 +24,8 @@ constexpr int IMG_BYTES = (DP_MAX / 8) * CT * 16;        // 45056
 constexpr int TILE_BYTES = (KT / 8) * CT * 16;           // 4096: bf16 [2][128 rows][8]
 constexpr int NTRI = IG * (IG + 1) / 2;
 static_assert(STAGE_BYTES <= SLAB_S_BYTES && STAGE_BYTES <= 2 * IG * TILE_BYTES, "image staging areas");
+constexpr int STAGE_OUT_FLOATS = CT * 65 + 3;   // one [128][65] fp32 output staging tile (padded to 16 bytes)
+static_assert(2 * STAGE_OUT_FLOATS * 4 <= 2 * IMG_BYTES + 3 * SLAB_S_BYTES, "output staging tiles must fit in the images");
 constexpr int NVAL = 1 + IG + NTRI;      // coefficient-gradient partial sums per thread: A, B_g, C_gg' (g <= g')
 constexpr int BT = 512;                 // compute threads per CTA: 128 rows x 4 column parts
 constexpr int BT_ALL = BT + 32;         // plus one warp whose lane 0 issues every MMA
@@ -388,7 +390,6 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
   const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tK = tmem_base + IG * KT + KT, tU = tK + DP_MAX;
   const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
   const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
-  const int jglob = c * CT + row;
 
   if (issuer) {
     if (lane == 0) {
@@ -507,8 +508,8 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
     if (tiles >= 2) w.wait(&ds_done[(tiles - 2) & 1], ((tiles - 2) >> 1) & 1, 0x33);
     w.wait(&ds_done[(tiles - 1) & 1], ((tiles - 1) >> 1) & 1, 0x34);
     fence_after_sync();
-    // tensor-memory loads are warp-collective: every thread executes them, only the stores are guarded
-    const bool valid = jglob < a.N && !dead;
+    // tensor-memory loads are warp-collective: every thread executes them; rows beyond N are dropped at
+    // the write-out
     const int nslab = pg.k16_start[IG];
     float* stage_out = reinterpret_cast<float*>(smem);    // the k / q images are free: [128][65] fp32 staging tile
     for (int k16 = part; k16 < nslab; k16 += BT / CT) {
@@ -526,24 +527,22 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
       float vv[16];
       tmem_ld16(tU + lane_off + col0, vv);
       tmem_ld_wait();
-      if (valid && a.dv_part) {
-        float* dst = a.dv_part + (qoff + jglob) * VD + col0;
+      // second staging tile, behind the first: the q / k / U / G images are all idle by now
 #pragma unroll
-        for (int x4 = 0; x4 < 16; x4 += 4)
-          *reinterpret_cast<float4*>(dst + x4) = make_float4(vv[x4], vv[x4 + 1], vv[x4 + 2], vv[x4 + 3]);
-      }
+      for (int x = 0; x < 16; ++x) stage_out[STAGE_OUT_FLOATS + row * 65 + col0 + x] = vv[x];
     }
   }
   fence_before_sync();
   __syncthreads();
-  if (a.dk_part && !dead) {
+  if (!dead) {
     const float* stage_out = reinterpret_cast<const float*>(smem);
-    for (int x = tid; x < CT * 16; x += BT_ALL) {       // coalesced write-out, four dims per thread
-      const int r = x >> 4, seg = x & 15, j = c * CT + r;
-      if (j >= a.N) continue;
-      *reinterpret_cast<float4*>(a.dk_part + (qoff + j) * HD + seg * 4) =
-          make_float4(stage_out[r * 65 + seg * 4], stage_out[r * 65 + seg * 4 + 1], stage_out[r * 65 + seg * 4 + 2],
-                      stage_out[r * 65 + seg * 4 + 3]);
+    for (int x = tid; x < 2 * CT * 16; x += BT_ALL) {   // coalesced write-out, four dims per thread: dk, then dv
+      const int which = x >= CT * 16, xx = x - which * CT * 16;
+      const int r = xx >> 4, seg = xx & 15, j = c * CT + r;
+      float* dst = which ? a.dv_part : a.dk_part;
+      if (j >= a.N || dst == nullptr) continue;
+      const float* sp = stage_out + which * STAGE_OUT_FLOATS + r * 65 + seg * 4;
+      *reinterpret_cast<float4*>(dst + (qoff + j) * HD + seg * 4) = make_float4(sp[0], sp[1], sp[2], sp[3]);
     }
   }
   __syncthreads();
