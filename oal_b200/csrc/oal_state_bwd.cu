@@ -52,8 +52,8 @@ struct DStateArgs {
 //   warp  13    lane 0 streams the head's G image into a 4-slot ring (bulk copies)
 //   warp  12    lane 0 issues the MMAs  Z[it % 3] = A^T G  once A and G are full and Z[it % 3] is drained
 //   warps 4-11  drain Z, thread = (feature row, half of the 80 columns): dot with the carry row for
-//               the coefficient gradient, acc += coef_h * Z in tensor memory; after the last head
-//               acc -> dCarry.  The powers of the query scale the features lack are applied here.
+//               the coefficient gradient, acc += coef_h * Z in registers; after the last head
+//               acc -> dCarry
 // A slot and Z buffer share the index it % 3, so the MMA-completion barrier of that index tells the
 // generators "A is free" and the drain warps "Z is ready".
 constexpr int DS_GEN_WARPS = 4, DS_EPI_WARPS = 8;
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
   const int n_items = F_SLABS * a.NB * a.units;
   const int my_items = (int)blockIdx.x < n_items ? (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
   const int T = my_items * rep;
-  if (warp == DS_ISSUER) tmem_alloc(&tmem_base, 512);
+  if (warp == DS_ISSUER) tmem_alloc(&tmem_base, 256);
   if (tid == 0) {
     for (int s = 0; s < DS_RING; ++s) {
       mbar_init(&full_a[s], DS_GEN_WARPS);
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
     // ---------------- drain warps ----------------
     const int fr = 32 * (warp & 3) + lane, ch = (warp - DS_GEN_WARPS) >> 2, col0 = ch * DS_COLS;
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
-    const uint32_t tacc = tmem_base + col0;
+    float acc[DS_COLS];            // this thread's part of the dCarry row, summed over the heads of the item
     uint4 cpk[DS_COLS / 8];
 #pragma unroll
     for (int e = 0; e < DS_COLS / 8; ++e) cpk[e] = make_uint4(0u, 0u, 0u, 0u);
@@ -187,48 +187,41 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
       }
       w.wait(&mma_done[s], use & 1, 0x32);
       fence_after_sync();
-      const uint32_t tz = tmem_base + EP * (1 + s) + col0;
+      const uint32_t tz = tmem_base + EP * s + col0;
+      if (d.hh == 0) {
+#pragma unroll
+        for (int j = 0; j < DS_COLS; ++j) acc[j] = 0.f;
+      }
       float dot[4] = {0.f, 0.f, 0.f, 0.f};
       // two register stages: the loads of the next 8 columns are in flight while these are combined
-      float z[2][8], acc[2][8];
+      float z[2][8];
       tmem_ld8(tz + lane_off, z[0]);
-      if (d.hh > 0) tmem_ld8(tacc + lane_off, acc[0]);
 #pragma unroll
       for (int r = 0; r < DS_COLS / 8; ++r) {
         tmem_ld_wait();
-        if (r + 1 < DS_COLS / 8) {
-          tmem_ld8(tz + lane_off + 8 * (r + 1), z[(r + 1) & 1]);
-          if (d.hh > 0) tmem_ld8(tacc + lane_off + 8 * (r + 1), acc[(r + 1) & 1]);
-        }
+        if (r + 1 < DS_COLS / 8) tmem_ld8(tz + lane_off + 8 * (r + 1), z[(r + 1) & 1]);
         float c0[8];
         unpack_bf16x8(cpk[r], c0);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dot[j & 3] = fmaf(z[r & 1][j], c0[j], dot[j & 3]);
-        uint32_t o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          o[j] = __float_as_uint(d.hh > 0 ? fmaf(cf, z[r & 1][j], acc[r & 1][j]) : cf * z[r & 1][j]);
-        tmem_st8(tacc + lane_off + 8 * r, o);
+        for (int j = 0; j < 8; ++j) {
+          dot[j & 3] = fmaf(z[r & 1][j], c0[j], dot[j & 3]);
+          acc[8 * r + j] = fmaf(cf, z[r & 1][j], acc[8 * r + j]);
+        }
       }
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&z_free[s]);      // every lane has its Z values in registers
-      tmem_st_wait();
       if (a.dcoef_partial)      // one partial per column half, summed by the reduction over (batch, chunk, half)
         a.dcoef_partial[((((size_t)b * a.NB + d.c) * 2 + ch) * a.Hq + h) * F_ROWS + f] =
             fs * ((dot[0] + dot[1]) + (dot[2] + dot[3]));
       if (d.hh == rep - 1) {
-        // dCarry rows of this slab: tensor memory -> HBM
+        // dCarry rows of this slab -> HBM; the next group of 8 columns of a row lies one 128-row block further
         float* dst = a.dcarry + ((size_t)d.u * a.NB + d.c) * F_ROWS * EP + state_inc_offset(f, col0);
-        float vv[DS_COLS / 8][8];
-#pragma unroll
-        for (int r = 0; r < DS_COLS / 8; ++r) tmem_ld8(tacc + lane_off + 8 * r, vv[r]);
-        tmem_ld_wait();
 #pragma unroll
         for (int r = 0; r < DS_COLS / 8; ++r) {
-          // the next group of 8 columns of this row lies one 128-row block further
-          *reinterpret_cast<float4*>(dst + r * 1024) = make_float4(vv[r][0], vv[r][1], vv[r][2], vv[r][3]);
-          *reinterpret_cast<float4*>(dst + r * 1024 + 4) = make_float4(vv[r][4], vv[r][5], vv[r][6], vv[r][7]);
+          *reinterpret_cast<float4*>(dst + r * 1024) = make_float4(acc[8 * r], acc[8 * r + 1], acc[8 * r + 2], acc[8 * r + 3]);
+          *reinterpret_cast<float4*>(dst + r * 1024 + 4) =
+              make_float4(acc[8 * r + 4], acc[8 * r + 5], acc[8 * r + 6], acc[8 * r + 7]);
         }
       }
       d = dn;
@@ -242,7 +235,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
       for (int it = 0; it < T; ++it) {
         const uint32_t a_addr = smem_u32(Abuf + s * SLAB_A_BYTES);
         const uint32_t g_addr = smem_u32(Gbuf + gs * SLAB_S_BYTES);
-        const uint32_t tz = tmem_base + EP * (1 + s);
+        const uint32_t tz = tmem_base + EP * s;
         w.wait(&full_a[s], use & 1, 0x33);
         w.wait(&g_full[gs], guse & 1, 0x34);
         if (use > 0) w.wait(&z_free[s], (use - 1) & 1, 0x35);
@@ -279,7 +272,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == DS_ISSUER) tmem_dealloc(tmem_base, 512);
+  if (warp == DS_ISSUER) tmem_dealloc(tmem_base, 256);
   if (tid == 0 && dead) atomicOr(a.status, w.status_bits());
 }
 
