@@ -389,6 +389,12 @@ def run_gpu_arm(args) -> None:
             if name in kernel_flops:
                 kernels[name]["tflops"] = round(kernel_flops[name] / (ms / max(cnt, 1) * 1e-3) / 1e12, 2)
         tc = {n_: k_ for n_, k_ in kernels.items() if n_ in kernel_flops}
+        # DRAM bytes (read + write) per launch of each kernel from the committed ncu capture of one batch
+        # row (profiles/bench_headline_bf16_tensorcore.md, section 2); traffic grows in proportion to the
+        # batch, so a launch of this workload moves batch x these bytes
+        ncu_dram_mb_per_row = {"intra_backward_q": 42.86, "intra_backward_kv": 27.98, "dstate_heads": 49.71,
+                               "feature_grad_q": 41.79, "cross_read_q": 32.48, "intra_forward": 24.40,
+                               "state_update": 2.97, "feature_grad_k": 27.09, "cross_read_k": 26.01}
         roofline = None
         if tc:
             # the dominant kernel by device time
@@ -396,7 +402,11 @@ def run_gpu_arm(args) -> None:
             achieved = kernel_flops[top] / (tc[top]["ms_per_launch"] * 1e-3) / 1e12
             best = max(tc, key=lambda n_: tc[n_]["tflops"])
             roofline = dict(bound="tensor", kernel=top, achieved=round(achieved, 2), peak=peaks["tflops"],
-                            unit="TFLOP/s", frac=round(achieved / peaks["tflops"], 4), traffic=None,
+                            unit="TFLOP/s", frac=round(achieved / peaks["tflops"], 4),
+                            traffic=(round(ncu_dram_mb_per_row[top] * 1e6 * w["batch"]) if top in ncu_dram_mb_per_row
+                                     else None),
+                            traffic_note="bytes per launch: DRAM read + write of the kernel in the committed ncu "
+                                         "capture of one batch row, times the batch",
                             peak_source=peaks["source"] + " (sustained bf16)",
                             note="algorithmic MMA FLOPs of the kernel / its mean launch time; the intra-chunk "
                                  "kernels spend their time in the fp32 combine on the CUDA cores",
