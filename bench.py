@@ -52,8 +52,9 @@ def measured_peaks() -> dict:
     if p.exists():
         d = json.loads(p.read_text())
         return dict(tflops=float(d.get("bf16_tflops_sustained", d.get("bf16_tflops", 1420.0))),
+                    tflops_burst=float(d.get("bf16_tflops", d.get("bf16_tflops_sustained", 1590.0))),
                     hbm=float(d.get("hbm_gbs", 6454.6)), source="measured")
-    return dict(tflops=1400.0, hbm=6650.0, source="fallback")
+    return dict(tflops=1400.0, tflops_burst=1590.0, hbm=6650.0, source="fallback")
 
 
 class ClockSampler:
@@ -410,8 +411,10 @@ def run_gpu_arm(args) -> None:
                             peak_source=peaks["source"] + " (sustained bf16)",
                             note="algorithmic MMA FLOPs of the kernel / its mean launch time; the intra-chunk "
                                  "kernels spend their time in the fp32 combine on the CUDA cores",
+                            frac_of_burst_peak=round(achieved / peaks["tflops_burst"], 4), burst_peak=peaks["tflops_burst"],
                             best_kernel=best, best_kernel_frac=round(tc[best]["tflops"] / peaks["tflops"], 4),
-                            whole_step_frac=round(value * fpt / 1e12 / peaks["tflops"], 4))
+                            whole_step_frac=round(value / world * fpt / 1e12 / peaks["tflops"], 4),
+                            whole_step_frac_of_burst_peak=round(value / world * fpt / 1e12 / peaks["tflops_burst"], 4))
         cpu = cpu_reference_run(2, 1) if world >= 1 and not args.no_cpu_baseline else None
         line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps,
                     warmup=max(args.warmup, 3), ms_per_step=total_ms / args.steps, higher_is_better=True,
