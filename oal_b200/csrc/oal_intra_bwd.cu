@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
   unsigned char* Gimg = Uimg + SLAB_S_BYTES;               // hi image, lo image
   unsigned char* DS = Gimg + 2 * SLAB_S_BYTES;            // [2][IG][TILE_BYTES]
   __shared__ PaddedGroups pg;
-  __shared__ uint64_t s_done, s_free, ds_ready[2], ds_done[2], gfull;
+  __shared__ uint64_t s_done[2], s_free[2], ds_ready[2], ds_done[2], gfull;
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -91,8 +91,10 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
   const bool issuer = warp == CWARPS;
   if (warp == 0) tmem_alloc(&tmem_base, 512);
   if (tid == 0) {
-    mbar_init(&s_done, 1);
-    mbar_init(&s_free, CWARPS);
+    mbar_init(&s_done[0], 1);
+    mbar_init(&s_done[1], 1);
+    mbar_init(&s_free[0], CWARPS);
+    mbar_init(&s_free[1], CWARPS);
     mbar_init(&ds_ready[0], CWARPS);
     mbar_init(&ds_ready[1], CWARPS);
     mbar_init(&ds_done[0], 1);
@@ -123,7 +125,11 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
   __syncthreads();
   fence_after_sync();
   Waiter w{&dead};
-  const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tQ = tmem_base + IG * KT + KT;
+  // two score buffers (S_g tiles + dW tile each): the MMAs of tile kt+2 start as soon as every warp has
+  // read tile kt, so a warp never waits for scores after its combine
+  constexpr uint32_t SBUF = IG * KT + KT;
+  static_assert(2 * SBUF + DP_MAX <= 512, "tensor-memory columns");
+  const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tQ = tmem_base + 2 * SBUF;
   const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
   const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
   // every MMA has completed when the tile loop is left, so the q / k images are free by then:
@@ -142,24 +148,26 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
       const uint32_t idesc16 = instr_desc_bf16(128, KT, 0, 0);
       const uint32_t idesc_dq = instr_desc_bf16(128, 16, 0, 1);
       auto issue_scores = [&](int kt) {
-        issue_group_scores(tS, q_addr, k_addr, kt * KT, pg);
+        const uint32_t off = (kt & 1) * SBUF;
+        issue_group_scores(tS + off, q_addr, k_addr, kt * KT, pg);
 #pragma unroll
         for (int ks = 0; ks < 2 * (EP / 16); ++ks) {       // G = hi + lo: the K extent is walked twice
           const int gp = ks / (EP / 16), kk = ks % (EP / 16);
-          mma_bf16_ss(tW, smem_desc(g_addr + gp * SLAB_S_BYTES + kk * 4096, CT * 16, 128),
+          mma_bf16_ss(tW + off, smem_desc(g_addr + gp * SLAB_S_BYTES + kk * 4096, CT * 16, 128),
                       smem_desc(u_addr + kk * 4096 + kt * KT * 16, CT * 16, 128), idesc16, ks > 0);
         }
-        mma_commit(&s_done);
+        mma_commit(&s_done[kt & 1]);
       };
       w.wait(&gfull, 0, 0x20);
       fence_after_sync();
       issue_scores(0);
+      if (tiles > 1) issue_scores(1);
       for (int kt = 0; kt < tiles; ++kt) {
         const int buf = kt & 1;
-        if (kt + 1 < tiles) {
-          w.wait(&s_free, kt & 1, 0x25);            // every compute warp holds the scores of tile kt
+        if (kt + 2 < tiles) {
+          w.wait(&s_free[buf], (kt >> 1) & 1, 0x25);   // every compute warp holds the scores of tile kt
           fence_after_sync();
-          issue_scores(kt + 1);
+          issue_scores(kt + 2);
         }
         w.wait(&ds_ready[buf], (kt >> 1) & 1, 0x26);  // ds tiles of tile kt are in shared memory
         fence_after_sync();
@@ -177,20 +185,21 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
     for (int kt = 0; kt < tiles; ++kt) {
       const int buf = kt & 1;
       float s[IG][CW], dw[CW];
-      w.wait(&s_done, kt & 1, 0x21);
+      w.wait(&s_done[buf], (kt >> 1) & 1, 0x21);
       fence_after_sync();
+      const uint32_t soff = buf * SBUF;
 #pragma unroll
       for (int g = 0; g < IG; ++g) {
-        if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld4(tS + lane_off + g * KT + CW * part, s[g]);
+        if (pg.k16_start[g + 1] > pg.k16_start[g]) tmem_ld4(tS + soff + lane_off + g * KT + CW * part, s[g]);
         else {
 #pragma unroll
           for (int x = 0; x < CW; ++x) s[g][x] = 0.f;
         }
       }
-      tmem_ld4(tW + lane_off + CW * part, dw);
+      tmem_ld4(tW + soff + lane_off + CW * part, dw);
       tmem_ld_wait();
       fence_before_sync();
-      warp_arrive(&s_free, lane);
+      warp_arrive(&s_free[buf], lane);
       const bool warp_active = 32 * (warp & 3) + 31 >= kt * KT;
       if (kt >= 2) w.wait(&ds_done[buf], ((kt - 2) >> 1) & 1, 0x22);
       unsigned char* dsb = DS + buf * IG * TILE_BYTES;
