@@ -8,6 +8,7 @@ import pytest
 import torch
 
 from oal_b200 import synthetic
+from oracle import oal_oracle as orc
 from tests.helpers import ERR, assert_close, oracle_dense, run_operator
 
 pytestmark = pytest.mark.gpu
@@ -213,3 +214,33 @@ def test_more_than_eight_groups_uses_pair_kernels_bf16_tensorcore():
     case = synthetic.qwen_head_case(8, batch=1, n=300, hq=2, hkv=1, g=16, bf16=True, outlier_scale=4.0)
     res = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
     assert_close(res, oracle_dense(case), TOL_BF16, label="bf16 G=16")
+
+
+@pytest.mark.parametrize("shape", [
+    # B, Hq, Hkv, N, D, Dv, G: one head per KV head, 16 heads per KV head, odd batch, ragged N, small D / Dv,
+    # group counts on both sides of the 4-group build
+    (1, 4, 4, 300, 64, 64, 3), (3, 6, 2, 257, 64, 64, 5), (2, 32, 2, 130, 64, 64, 8), (1, 2, 1, 511, 64, 32, 7),
+    (2, 8, 8, 129, 48, 64, 4), (2, 3, 1, 200, 64, 64, 1), (1, 16, 4, 384, 64, 64, 6),
+])
+def test_odd_shapes_bf16_tensorcore(shape):
+    import oal_b200
+
+    B, Hq, Hkv, N, D, Dv, G = shape
+    g = torch.Generator().manual_seed(B * 1000 + N)
+    q = torch.randn(B, Hq, N, D, generator=g).bfloat16().float()
+    k = torch.randn(B, Hkv, N, D, generator=g).bfloat16().float()
+    v = torch.randn(B, Hkv, N, Dv, generator=g).bfloat16().float()
+    groups = torch.stack([torch.randperm(D, generator=g) % G for _ in range(Hq)]).to(torch.int32)
+    factor = torch.rand(Hq, (G + 1) * (G + 2) // 2, generator=g) * 0.9 + 0.1
+    dout = torch.randn(B, Hq, N, Dv, generator=g).bfloat16().float()
+    qc, kc, vc = (t.cuda().bfloat16().requires_grad_() for t in (q, k, v))
+    fc = factor.cuda().requires_grad_()
+    out = oal_b200.oal_attention(qc, kc, vc, groups.cuda(), fc, precision="bf16_tensorcore", output_dtype=torch.float32)
+    out.backward(dout.cuda())
+    qd, kd, vd = (t.double().requires_grad_() for t in (q, k, v))
+    fd = factor.double().requires_grad_()
+    a, b, c = orc.expand_factor(fd, Hq, 1e-6)
+    want, _, _ = orc.dense_forward(qd, kd, vd, groups, a, b, c, scale=D ** -0.5)
+    want.backward(dout.double())
+    for got, ref in ((out, want.detach()), (qc.grad, qd.grad), (kc.grad, kd.grad), (vc.grad, vd.grad), (fc.grad, fd.grad)):
+        assert ERR(got.float().cpu(), ref) < 2e-2      # bf16 io tolerance
