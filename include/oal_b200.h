@@ -183,6 +183,22 @@ int oal_forward_static_scratch(const OalProblem* problem, const void* q, const v
                                const float* coef_b, const float* coef_c, void* out, float* num, float* den,
                                void* saved_state, int32_t* status, void* stream);
 
+/*
+ * Layer prologue fused into one pass per tensor (replaces the reshape / transpose / rotary / contiguous
+ * sequence of qwen_lora_experiment/attention/common.py:550-572).  bf16 only, head dimension 64.
+ *   oal_rope_pack: q_flat [B, N, Hq*64], k_flat, v_flat [B, N, Hkv*64] (projection outputs) ->
+ *     q, k rotated by position and v copied, all head-first [B, H, N, 64] contiguous, as oal_forward
+ *     reads them.  cos, sin: fp32 [N, 64], rotate-half convention (32 frequencies repeated twice).
+ *   oal_rope_unpack_grad: the transpose of that map, for the backward: gradients in head-first layout ->
+ *     gradients of the projection outputs.
+ * Any of the three tensors may be NULL (skipped).
+ */
+int oal_rope_pack(const void* q_flat, const void* k_flat, const void* v_flat, const float* cos, const float* sin,
+                  void* q, void* k, void* v, int batch, int seq_len, int q_heads, int kv_heads, void* stream);
+int oal_rope_unpack_grad(const void* dq, const void* dk, const void* dv, const float* cos, const float* sin,
+                         void* dq_flat, void* dk_flat, void* dv_flat, int batch, int seq_len, int q_heads,
+                         int kv_heads, void* stream);
+
 /* Text of the last error returned on the calling thread (host pointer, never NULL). */
 const char* oal_last_error_string(void);
 

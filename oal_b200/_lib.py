@@ -38,6 +38,8 @@ EXPORTED_SYMBOLS = (
     "oal_forward_static_scratch",
     "oal_forward_local_state",
     "oal_backward_local_state",
+    "oal_rope_pack",
+    "oal_rope_unpack_grad",
 )
 
 
@@ -92,6 +94,11 @@ def load() -> ctypes.CDLL:
     lib.oal_backward.argtypes = [pp, vp, vp, vp, i32p, i32p, f32p, f32p, f32p, f32p, f32p, vp, vp, f32p,
                                  f32p, vp, vp, vp, f32p, f32p, f32p, f32p, vp, ctypes.c_size_t, i32p, vp]
     lib.oal_backward.restype = ctypes.c_int
+    ci = ctypes.c_int
+    lib.oal_rope_pack.argtypes = [vp, vp, vp, f32p, f32p, vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.oal_rope_pack.restype = ctypes.c_int
+    lib.oal_rope_unpack_grad.argtypes = [vp, vp, vp, f32p, f32p, vp, vp, vp, ci, ci, ci, ci, vp]
+    lib.oal_rope_unpack_grad.restype = ctypes.c_int
     lib.oal_selftest_umma.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp, f32p, i32p, vp]
     lib.oal_selftest_umma.restype = ctypes.c_int
     lib.oal_launch_count.restype = ctypes.c_int64

@@ -57,15 +57,68 @@ def apply_rotary_pos_emb(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, si
     return q * cos + rot(q) * sin, k * cos + rot(k) * sin
 
 
+class _RopePackFunction(torch.autograd.Function):
+    """Rotary embedding of q and k fused with the move to the head-first layout (one CUDA pass per
+    tensor in each direction); v is moved only.  bf16 CUDA tensors, head dimension 64."""
+
+    @staticmethod
+    def forward(ctx, q_flat, k_flat, v_flat, cos, sin, q_heads: int, kv_heads: int):
+        from . import _lib
+        from .hd_block_gemm_autograd import _stream_ptr
+
+        b, n, _ = q_flat.shape
+        q_flat, k_flat, v_flat = q_flat.contiguous(), k_flat.contiguous(), v_flat.contiguous()
+        cos, sin = cos.float().contiguous(), sin.float().contiguous()
+        q = torch.empty(b, q_heads, n, 64, dtype=q_flat.dtype, device=q_flat.device)
+        k = torch.empty(b, kv_heads, n, 64, dtype=q_flat.dtype, device=q_flat.device)
+        v = torch.empty(b, kv_heads, n, 64, dtype=q_flat.dtype, device=q_flat.device)
+        _lib.check(_lib.load().oal_rope_pack(_lib.ptr(q_flat), _lib.ptr(k_flat), _lib.ptr(v_flat), _lib.ptr(cos),
+                                             _lib.ptr(sin), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), b, n, q_heads,
+                                             kv_heads, _stream_ptr(q_flat.device)))
+        ctx.save_for_backward(cos, sin)
+        ctx.geometry = (b, n, q_heads, kv_heads)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        from . import _lib
+        from .hd_block_gemm_autograd import _stream_ptr
+
+        cos, sin = ctx.saved_tensors
+        b, n, hq, hkv = ctx.geometry
+        mk = lambda g, h: None if g is None else torch.empty(b, n, h * 64, dtype=g.dtype, device=g.device)
+        dq, dk, dv = (None if g is None else g.contiguous() for g in (dq, dk, dv))
+        dq_flat, dk_flat, dv_flat = mk(dq, hq), mk(dk, hkv), mk(dv, hkv)
+        dev = next(g for g in (dq, dk, dv) if g is not None).device
+        _lib.check(_lib.load().oal_rope_unpack_grad(_lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(cos),
+                                                    _lib.ptr(sin), _lib.ptr(dq_flat), _lib.ptr(dk_flat),
+                                                    _lib.ptr(dv_flat), b, n, hq, hkv, _stream_ptr(dev)))
+        return dq_flat, dk_flat, dv_flat, None, None, None, None
+
+
+def _fused_prologue_applies(hidden_states: torch.Tensor, geometry: ModelGeometry) -> bool:
+    return hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16 and geometry.head_dim == 64
+
+
 def project_qkv_and_apply_rope(*, q_proj: nn.Module, k_proj: nn.Module, v_proj: nn.Module,
-                               hidden_states: torch.Tensor, position_embeddings, geometry: ModelGeometry = QWEN_GEOMETRY):
-    """Project q/k/v, reshape to native heads, rotate q and k only; returns contiguous head-first tensors."""
+                               hidden_states: torch.Tensor, position_embeddings, geometry: ModelGeometry = QWEN_GEOMETRY,
+                               fused: bool | None = None):
+    """Project q/k/v, reshape to native heads, rotate q and k only; returns contiguous head-first tensors.
+
+    ``fused`` (default: whenever the tensors are bf16 on CUDA) does the rotation and the layout move in the
+    library's single-pass kernels instead of torch's element-wise sequence.
+    """
     if hidden_states.dim() != 3 or hidden_states.shape[-1] != geometry.hidden_size:
         raise AttentionContractError(f"hidden_states must be [B, N, {geometry.hidden_size}], got {tuple(hidden_states.shape)}")
     b, n, _ = hidden_states.shape
     cos, sin = position_embeddings
     if cos.shape != (n, geometry.head_dim) or sin.shape != cos.shape:
         raise AttentionContractError(f"position embeddings must be [{n}, {geometry.head_dim}]")
+    if fused is None:
+        fused = _fused_prologue_applies(hidden_states, geometry)
+    if fused:
+        return _RopePackFunction.apply(q_proj(hidden_states), k_proj(hidden_states), v_proj(hidden_states), cos, sin,
+                                       geometry.num_query_heads, geometry.num_kv_heads)
     q = q_proj(hidden_states).reshape(b, n, geometry.num_query_heads, geometry.head_dim).transpose(1, 2)
     k = k_proj(hidden_states).reshape(b, n, geometry.num_kv_heads, geometry.head_dim).transpose(1, 2)
     v = v_proj(hidden_states).reshape(b, n, geometry.num_kv_heads, geometry.head_dim).transpose(1, 2)

@@ -221,6 +221,40 @@ oal::PairArgs base_args(const OalProblem* p, const void* q, const void* k, const
 
 extern "C" {
 
+int oal_rope_pack(const void* q_flat, const void* k_flat, const void* v_flat, const float* cosv, const float* sinv,
+                  void* q, void* k, void* v, int batch, int seq_len, int q_heads, int kv_heads, void* stream) {
+  if (batch < 0 || seq_len < 0 || q_heads < 1 || kv_heads < 1) return fail(OAL_ERR_ARGUMENT, "oal_rope_pack: bad geometry");
+  if ((q_flat || k_flat) && (!cosv || !sinv)) return fail(OAL_ERR_ARGUMENT, "oal_rope_pack: cos / sin are required");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSuccess;
+  LaunchScope scope("rope_pack", st, (q_flat ? 1 : 0) + (k_flat ? 1 : 0) + (v_flat ? 1 : 0));
+  if (q_flat && (e = oal::rope_to_heads(q_flat, q, cosv, sinv, batch, seq_len, q_heads, true, st)) != cudaSuccess)
+    return fail_cuda(e, "rotary pack kernel (q)");
+  if (k_flat && (e = oal::rope_to_heads(k_flat, k, cosv, sinv, batch, seq_len, kv_heads, true, st)) != cudaSuccess)
+    return fail_cuda(e, "rotary pack kernel (k)");
+  if (v_flat && (e = oal::rope_to_heads(v_flat, v, nullptr, nullptr, batch, seq_len, kv_heads, false, st)) != cudaSuccess)
+    return fail_cuda(e, "pack kernel (v)");
+  return OAL_OK;
+}
+
+int oal_rope_unpack_grad(const void* dq, const void* dk, const void* dv, const float* cosv, const float* sinv,
+                         void* dq_flat, void* dk_flat, void* dv_flat, int batch, int seq_len, int q_heads,
+                         int kv_heads, void* stream) {
+  if (batch < 0 || seq_len < 0 || q_heads < 1 || kv_heads < 1)
+    return fail(OAL_ERR_ARGUMENT, "oal_rope_unpack_grad: bad geometry");
+  if ((dq || dk) && (!cosv || !sinv)) return fail(OAL_ERR_ARGUMENT, "oal_rope_unpack_grad: cos / sin are required");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSuccess;
+  LaunchScope scope("rope_unpack_grad", st, (dq ? 1 : 0) + (dk ? 1 : 0) + (dv ? 1 : 0));
+  if (dq && (e = oal::rope_to_flat(dq, dq_flat, cosv, sinv, batch, seq_len, q_heads, true, st)) != cudaSuccess)
+    return fail_cuda(e, "rotary unpack kernel (dq)");
+  if (dk && (e = oal::rope_to_flat(dk, dk_flat, cosv, sinv, batch, seq_len, kv_heads, true, st)) != cudaSuccess)
+    return fail_cuda(e, "rotary unpack kernel (dk)");
+  if (dv && (e = oal::rope_to_flat(dv, dv_flat, nullptr, nullptr, batch, seq_len, kv_heads, false, st)) != cudaSuccess)
+    return fail_cuda(e, "unpack kernel (dv)");
+  return OAL_OK;
+}
+
 const char* oal_last_error_string(void) { return g_error; }
 
 const char* oal_version_string(void) { return "oal_b200 0.1 sm_100a"; }

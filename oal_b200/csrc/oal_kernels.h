@@ -42,6 +42,12 @@ cudaError_t reduce_coefs(const float* p0, int tiles0, const float* extra, int B,
                          float* dA, float* dB, float* dC, cudaStream_t st);
 
 // ---- tensor-core state kernels (oal_state.cu) ---------------------------------------
+// rotary embedding fused with the layout move between [B, N, H, 64] and [B, H, N, 64] (bf16)
+cudaError_t rope_to_heads(const void* src, void* dst, const float* cosv, const float* sinv, int B, int N, int H,
+                          bool rotate, cudaStream_t st);
+cudaError_t rope_to_flat(const void* src, void* dst, const float* cosv, const float* sinv, int B, int N, int H,
+                         bool rotate, cudaStream_t st);
+
 size_t state_rows();                       // feature rows of the running state (2432)
 size_t state_image_bytes_per_chunk();      // bytes of one bf16 state image [19 slabs][10][128][8]
 size_t state_slab_image_bytes();           // bytes of one slab image [10][128][8] bf16

@@ -84,3 +84,36 @@ def test_layer_matches_dense_oracle_and_reuses_its_prepared_call():
     before = len(cache._entries[0])
     layer(x.detach().requires_grad_(), pe)
     assert len(cache._entries[0]) == before == 1
+
+
+@pytest.mark.gpu
+def test_fused_rope_prologue_matches_the_elementwise_statement_forward_and_backward():
+    torch.manual_seed(11)
+    geo = shell.ModelGeometry(num_layers=1, hidden_size=6 * 64, num_query_heads=6, num_kv_heads=2, head_dim=64)
+    b, n = 2, 203
+    lin = lambda o: torch.nn.Linear(geo.hidden_size, o, bias=True, dtype=torch.bfloat16, device="cuda")
+    qp, kp, vp = lin(384), lin(128), lin(128)
+    x = (torch.randn(b, n, geo.hidden_size, device="cuda")).to(torch.bfloat16)
+    pe = shell.rope_tables(n, 64, device="cuda")
+    outs = {}
+    for fused in (True, False):
+        xi = x.clone().requires_grad_()
+        q, k, v = shell.project_qkv_and_apply_rope(q_proj=qp, k_proj=kp, v_proj=vp, hidden_states=xi,
+                                                   position_embeddings=pe, geometry=geo, fused=fused)
+        assert q.shape == (b, 6, n, 64) and k.shape == (b, 2, n, 64) and v.shape == (b, 2, n, 64)
+        assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+        g = torch.Generator(device="cuda").manual_seed(3)
+        gq, gk, gv = (torch.randn(t.shape, generator=g, device="cuda").to(torch.bfloat16) for t in (q, k, v))
+        torch.autograd.backward([q, k, v], [gq, gk, gv])
+        outs[fused] = [t.detach().float() for t in (q, k, v, xi.grad)]
+    # fp64 statement of the rotation on the same projections
+    with torch.no_grad():
+        qf = qp(x).double().reshape(b, n, 6, 64).transpose(1, 2)
+        cos, sin = pe[0].double(), pe[1].double()
+        rot = torch.cat((-qf[..., 32:], qf[..., :32]), -1)
+        want_q = qf * cos + rot * sin
+    err = lambda a, r: float((a.double() - r.double()).abs().max() / r.double().abs().max())
+    assert err(outs[True][0], want_q) < 1e-2            # one bf16 rounding
+    assert torch.equal(outs[True][2], outs[False][2])   # v is only moved
+    for fused_t, plain_t in zip(outs[True], outs[False]):
+        assert err(fused_t, plain_t) < 2e-2             # the element-wise path rounds to bf16 after every step
