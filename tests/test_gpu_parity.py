@@ -244,3 +244,42 @@ def test_odd_shapes_bf16_tensorcore(shape):
     want.backward(dout.double())
     for got, ref in ((out, want.detach()), (qc.grad, qd.grad), (kc.grad, kd.grad), (vc.grad, vd.grad), (fc.grad, fd.grad)):
         assert ERR(got.float().cpu(), ref) < 2e-2      # bf16 io tolerance
+
+
+def _headline_inputs(batch=1, n=4096):
+    case = synthetic.qwen_head_case(5, batch=batch, n=n, hq=14, hkv=2, g=8, bf16=True, with_grad=False)
+    dev = lambda t: t.cuda().bfloat16()
+    return dev(case.q), dev(case.k), dev(case.v), case.dim_groups.cuda(), case.factor.cuda(), case.scale
+
+
+def test_full_size_causality_bf16_tensorcore():
+    """Size-independent property at the headline length: outputs up to token t do not depend on later tokens."""
+    import oal_b200
+
+    q, k, v, groups, factor, scale = _headline_inputs()
+    cut = 2500                                     # inside chunk 19, not on a chunk boundary
+    out_a = oal_b200.oal_attention(q, k, v, groups, factor, scale=scale, precision="bf16_tensorcore")
+    q2, k2, v2 = q.clone(), k.clone(), v.clone()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for t in (q2, k2, v2):
+        t[:, :, cut:] = torch.randn(t[:, :, cut:].shape, generator=g, device="cuda").to(t.dtype)
+    out_b = oal_b200.oal_attention(q2, k2, v2, groups, factor, scale=scale, precision="bf16_tensorcore")
+    assert torch.equal(out_a[:, :, :cut], out_b[:, :, :cut])
+    assert not torch.equal(out_a[:, :, cut:], out_b[:, :, cut:])
+
+
+def test_full_size_numerator_is_linear_in_v_and_denominator_ignores_it():
+    import oal_b200
+
+    q, k, v, groups, factor, scale = _headline_inputs()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    v2 = torch.randn(v.shape, generator=g, device="cuda").to(v.dtype)
+    vs = (v.float() + v2.float()).to(v.dtype)       # the sum, rounded to bf16 like any input
+    run = lambda vv: oal_b200.oal_attention(q, k, vv, groups, factor, scale=scale, precision="bf16_tensorcore",
+                                            return_unnormalized=True)
+    _, n1, d1 = run(v)
+    _, n2, d2 = run(v2)
+    _, ns, ds = run(vs)
+    assert torch.equal(d1, d2) and torch.equal(d1, ds)
+    # bf16 rounding of v1 + v2 is the only difference between the two sides
+    assert ERR(ns, n1 + n2) < 1e-2
