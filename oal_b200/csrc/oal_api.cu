@@ -115,8 +115,31 @@ int chunk_count(const OalProblem* p) { return (p->seq_len + kChunk - 1) / kChunk
 struct ForwardSpaceTC {
   float* coef_table;
   float* ds;
+  void *qimg, *kimg, *uimg;        // operand images of the intra-chunk kernels (at most 8 groups per head)
   size_t bytes;
 };
+
+// q / k image slot of one (batch, query head, chunk) and the three image buffers of a problem
+size_t intra_image_stride(const OalProblem* p) {
+  return p->groups <= 4 ? oal::pad_image_bytes_g4(p->padded_slabs) : oal::pad_image_bytes(p->padded_slabs);
+}
+void take_intra_images(Carver& c, const OalProblem* p, void*& qimg, void*& kimg, void*& uimg) {
+  qimg = kimg = uimg = nullptr;
+  if (p->groups > 8) return;
+  const size_t items = (size_t)p->batch * p->q_heads * chunk_count(p);
+  qimg = c.take<char>(items * intra_image_stride(p));
+  kimg = c.take<char>(items * intra_image_stride(p));
+  uimg = c.take<char>((size_t)p->batch * p->kv_heads * chunk_count(p) * oal::state_slab_image_bytes());
+}
+int make_intra_images(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
+                      const int32_t* group_start, void* qimg, void* kimg, void* uimg, int32_t* status,
+                      cudaStream_t st) {
+  LaunchScope scope("pad_images", st);
+  cudaError_t e = (p->groups <= 4 ? oal::pad_images_g4 : oal::pad_images)(
+      q, k, v, dim_perm, group_start, qimg, kimg, uimg, status, p->batch, p->q_heads, p->kv_heads, p->seq_len,
+      chunk_count(p), p->padded_slabs, st);
+  return e == cudaSuccess ? OAL_OK : fail_cuda(e, "operand image kernel");
+}
 
 ForwardSpaceTC carve_forward_tc(const OalProblem* p, void* ws) {
   Carver c(ws);
@@ -124,6 +147,7 @@ ForwardSpaceTC carve_forward_tc(const OalProblem* p, void* ws) {
   const size_t units = (size_t)p->batch * p->kv_heads;
   s.coef_table = c.take<float>((size_t)p->q_heads * oal::state_rows());
   s.ds = c.take<float>(units * chunk_count(p) * oal::state_rows() * oal::EP);
+  take_intra_images(c, p, s.qimg, s.kimg, s.uimg);
   s.bytes = c.off;
   return s;
 }
@@ -144,6 +168,7 @@ struct BackwardSpaceTC {
   float* slots;
   float *dq_cross, *dk_cross, *dv_cross;
   float *dk_part, *dv_part;      // per-query-head intra-chunk shares of dk / dv
+  void *qimg, *kimg, *uimg;      // operand images of the intra-chunk kernels
   size_t bytes;
 };
 
@@ -168,6 +193,7 @@ BackwardSpaceTC carve_backward_tc(const OalProblem* p, void* ws) {
   s.dv_cross = c.take<float>(krows * oal::VD);
   s.dk_part = c.take<float>(qrows * oal::HD);
   s.dv_part = c.take<float>(qrows * oal::VD);
+  take_intra_images(c, p, s.qimg, s.kimg, s.uimg);
   s.bytes = c.off;
   return s;
 }
@@ -350,9 +376,11 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
                         p->q_heads / p->kv_heads, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
   if (p->groups <= 8) {
+    if (int rc = make_intra_images(p, q, k, v, dim_perm, group_start, s.qimg, s.kimg, s.uimg, status, st)) return rc;
     { LaunchScope scope("intra_forward", st);
       e = (p->groups <= 4 ? oal::intra_forward_g4 : oal::intra_forward)(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
-                             p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor, st); }
+                             p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor,
+                             s.qimg, s.kimg, s.uimg, st); }
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
     return OAL_OK;
   }
@@ -427,6 +455,10 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
                               grad_num, grad_den, s, status, st);
     if (rc) return rc;
   }
+  if (tc_intra) {
+    rc = make_intra_images(p, q, k, v, dim_perm, group_start, s.qimg, s.kimg, s.uimg, status, st);
+    if (rc) return rc;
+  }
   if (want_k || want_v) {
     { LaunchScope scope("state_scan_reverse", st);
       e = oal::state_scan(s.dcarry, s.dt_img, dstate_in, nullptr, units, nb, 1, st); }
@@ -446,7 +478,8 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
       { LaunchScope scope("intra_backward_q", st);
         e = (p->groups <= 4 ? oal::intra_backward_q_g4 : oal::intra_backward_q)(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_q ? dq : nullptr,
                                   want_q ? s.dq_cross : nullptr, want_c ? s.coef_pairs : nullptr, status, p->batch,
-                                  p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->scale, st); }
+                                  p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->scale, s.qimg, s.kimg, s.uimg,
+                                  (int)intra_image_stride(p), st); }
       if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward query-side kernel");
     } else {
       a.dq = want_q ? dq : nullptr;
@@ -483,7 +516,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
         e = (p->groups <= 4 ? oal::intra_backward_kv_g4 : oal::intra_backward_kv)(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_k ? dk : nullptr,
                                    want_v ? dv : nullptr, want_k ? s.dk_cross : nullptr, want_v ? s.dv_cross : nullptr,
                                    s.dk_part, s.dv_part, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
-                                   p->groups, p->scale, st); }
+                                   p->groups, p->scale, s.qimg, s.kimg, s.uimg, (int)intra_image_stride(p), st); }
       if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward key/value-side kernel");
     } else {
       a.dq = nullptr; a.dq_init = nullptr; a.coef_partial = nullptr;
@@ -622,7 +655,8 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
   if (p->groups <= 8) {
     { LaunchScope scope("intra_forward", st);
       e = (p->groups <= 4 ? oal::intra_forward_g4 : oal::intra_forward)(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
-                             p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor, st); }
+                             p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor,
+                             nullptr, nullptr, nullptr, st); }     // no scratch for images: built inside the kernel
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
     return OAL_OK;
   }

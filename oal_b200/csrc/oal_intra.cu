@@ -26,7 +26,73 @@ struct IntraFwdArgs {
   int N, Hq, Hkv, G, out_dt;
   int slabs;            // upper bound on the padded 16-dim slabs of any head (image size)
   float scale, floor;
+  // operand images made by pad_images (null: build them here from q, k, v)
+  const unsigned char *qimg, *kimg, *uimg;
 };
+
+// ---------------------------------------------------------------------------
+// pad_images: the padded q / k operand images of every (batch, query head, chunk) and the [v | 1]
+// image of every (batch, KV head, chunk), written once to HBM so that the intra-chunk kernels fetch
+// them with bulk copies instead of gathering them again in each of the three kernels.
+//   qimg, kimg: [B*Hq*NB][slabs * 4096 bytes]   uimg: [B*Hkv*NB][SLAB_S_BYTES]
+// ---------------------------------------------------------------------------
+struct PadArgs {
+  const __nv_bfloat16 *q, *k, *v;
+  const int32_t *dim_perm, *group_start;
+  unsigned char *qimg, *kimg, *uimg;
+  int32_t* status;
+  int N, NB, Hq, Hkv, slabs;
+};
+
+__global__ void __launch_bounds__(256) pad_images_kernel(const PadArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  uint32_t* stage_a = reinterpret_cast<uint32_t*>(smem);      // raw q tile, row pitch 33 words
+  uint32_t* stage_b = stage_a + STAGE_WORDS;                  // raw k tile
+  __shared__ PaddedGroups pg;
+  const int tid = threadIdx.x;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int rep = a.Hq / a.Hkv, kvh = h / rep;
+  const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
+  // the raw tiles are on their way while the layout is worked out
+  for (int x = tid; x < 2 * CT * 8; x += 256) {
+    const int which = x >= CT * 8, xx = x - which * CT * 8;
+    const int r = xx >> 3, seg = xx & 7, i = c * CT + r;
+    uint4 t = make_uint4(0u, 0u, 0u, 0u);
+    if (i < a.N) t = *reinterpret_cast<const uint4*>((which ? a.k + koff * HD : a.q + qoff * HD) + (size_t)i * HD + seg * 8);
+    uint32_t* d = (which ? stage_b : stage_a) + r * 33 + seg * 4;
+    d[0] = t.x; d[1] = t.y; d[2] = t.z; d[3] = t.w;
+  }
+  load_group_layout(pg, a.dim_perm, a.group_start, h, tid, 256);     // its barriers also cover the staging stores
+  const int nslab = pg.k16_start[IG];
+  if (nslab > a.slabs) {            // the consumer kernels refuse this head too
+    if (tid == 0) atomicOr(a.status, OAL_STATUS_BAD_LAYOUT);
+    return;
+  }
+  const size_t item = (size_t)(b * a.Hq + h) * a.NB + c;
+  const size_t img_bytes = (size_t)a.slabs * 4096;
+  const int per_img = 2 * nslab * CT;
+  for (int x = tid; x < 2 * per_img; x += 256) {       // gather straight into the images in HBM, 16 bytes per thread
+    const int which = x >= per_img, xx = x - which * per_img;
+    const int c8 = xx >> 7, r = xx & 127;
+    const unsigned short* raw = reinterpret_cast<const unsigned short*>(which ? stage_b : stage_a);
+    unsigned short e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int sd = pg.src[c8 * 8 + j];
+      e[j] = sd >= 0 ? raw[r * 66 + sd] : (unsigned short)0;
+    }
+    reinterpret_cast<uint4*>((which ? a.kimg : a.qimg) + item * img_bytes)[xx] =
+        make_uint4(e[0] | ((uint32_t)e[1] << 16), e[2] | ((uint32_t)e[3] << 16), e[4] | ((uint32_t)e[5] << 16),
+                   e[6] | ((uint32_t)e[7] << 16));
+  }
+  if (h % rep == 0) {
+    uint4* du = reinterpret_cast<uint4*>(a.uimg + ((size_t)(b * a.Hkv + kvh) * a.NB + c) * SLAB_S_BYTES);
+    for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
+      const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
+      du[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
+    }
+  }
+}
 
 constexpr int W_BYTES = (KT / 8) * CT * 16;              // 4096: one bf16 weight tile [2][128 rows][8 keys]
 __host__ __device__ constexpr int fwd_smem_bytes(int slabs) {
@@ -42,7 +108,7 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
   unsigned char* Wbuf = Uimg + SLAB_S_BYTES;
   uint32_t* stage = reinterpret_cast<uint32_t*>(Wbuf + 2 * W_BYTES);
   __shared__ PaddedGroups pg;
-  __shared__ uint64_t s_done, w_done[2];
+  __shared__ uint64_t s_done, w_done[2], imgfull;
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
   __shared__ float den_s[CT];
@@ -55,6 +121,7 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
     mbar_init(&s_done, 1);
     mbar_init(&w_done[0], 1);
     mbar_init(&w_done[1], 1);
+    mbar_init(&imgfull, 1);
     mbar_fence_init();
     dead = 0;
   }
@@ -62,17 +129,29 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
   const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
   // a head with more padded slabs than the caller announced would not fit the images: refuse it
   const bool bad = pg.k16_start[IG] > a.slabs;
-  if (!bad) {
-    // second staging area: the U image, which is built right after
-    build_padded_images(Qimg, Kimg, stage, reinterpret_cast<uint32_t*>(Uimg), a.q + qoff * HD, a.k + koff * HD, c * CT,
-                        a.N, pg, tid, 256);
-  } else if (tid == 0) {
-    atomicOr(a.status, OAL_STATUS_BAD_LAYOUT);
+  const bool prebuilt = a.qimg != nullptr;
+  if (prebuilt) {
+    // the images were made by pad_images: three bulk copies, awaited by the thread that issues the MMAs
+    if (tid == 0 && !bad) {
+      const uint32_t bytes = (uint32_t)pg.k16_start[IG] * 4096u;
+      const size_t item = (size_t)(b * a.Hq + h) * gridDim.x + c;
+      mbar_arrive_expect_tx(&imgfull, 2 * bytes + SLAB_S_BYTES);
+      bulk_g2s(Qimg, a.qimg + item * (size_t)img_bytes, bytes, &imgfull);
+      bulk_g2s(Kimg, a.kimg + item * (size_t)img_bytes, bytes, &imgfull);
+      bulk_g2s(Uimg, a.uimg + ((size_t)(b * a.Hkv + kvh) * gridDim.x + c) * SLAB_S_BYTES, SLAB_S_BYTES, &imgfull);
+    }
+  } else {
+    if (!bad) {
+      // second staging area: the U image, which is built right after
+      build_padded_images(Qimg, Kimg, stage, reinterpret_cast<uint32_t*>(Uimg), a.q + qoff * HD, a.k + koff * HD, c * CT,
+                          a.N, pg, tid, 256);
+    }
+    for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
+      const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
+      reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
+    }
   }
-  for (int idx = tid; idx < (EP / 8) * CT; idx += 256) {
-    const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
-    reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
-  }
+  if (bad && tid == 0) atomicOr(a.status, OAL_STATUS_BAD_LAYOUT);
   fence_async_smem();
   fence_before_sync();
   __syncthreads();
@@ -84,6 +163,10 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
   const uint32_t idesc_y = instr_desc_bf16(128, EP, 0, 1);
   const int tiles = bad ? 0 : min(CT / KT, (a.N - c * CT + KT - 1) / KT);
   if (tid == 0 && !bad) {
+    if (prebuilt) {
+      w.wait(&imgfull, 0, 0x15);
+      fence_after_sync();
+    }
     issue_group_scores(tS, q_addr, k_addr, 0, pg);
     mma_commit(&s_done);
   }
@@ -233,7 +316,8 @@ __global__ void __launch_bounds__(256, 2) intra_fwd_kernel(const IntraFwdArgs a)
 cudaError_t OAL_INTRA_NAME(intra_forward)(const void* q, const void* k, const void* v, const int32_t* dim_perm,
                           const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* out,
                           float* num, float* den, int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G,
-                          int out_dt, int slabs, float scale, float floor_v, cudaStream_t st) {
+                          int out_dt, int slabs, float scale, float floor_v, const void* qimg, const void* kimg,
+                          const void* uimg, cudaStream_t st) {
   if (slabs < 1 || slabs > DP_MAX / 16) slabs = DP_MAX / 16;
   const int smem = fwd_smem_bytes(slabs);
   cudaError_t e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -241,8 +325,29 @@ cudaError_t OAL_INTRA_NAME(intra_forward)(const void* q, const void* k, const vo
   if (e != cudaSuccess) return e;
   IntraFwdArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
                  static_cast<const __nv_bfloat16*>(v), dim_perm, group_start, A, Bc, Cc, out, num, den, status,
-                 N, Hq, Hkv, G, out_dt, slabs, scale, floor_v};
+                 N, Hq, Hkv, G, out_dt, slabs, scale, floor_v, static_cast<const unsigned char*>(qimg),
+                 static_cast<const unsigned char*>(kimg), static_cast<const unsigned char*>(uimg)};
   intra_fwd_kernel<<<dim3(NB, Hq, B), 256, smem, st>>>(a);
+  return cudaGetLastError();
+}
+
+// Bytes of one q (or k) image slot for a given slab bound, and the pad_images launcher.
+size_t OAL_INTRA_NAME(pad_image_bytes)(int slabs) {
+  if (slabs < 1 || slabs > DP_MAX / 16) slabs = DP_MAX / 16;
+  return (size_t)slabs * 4096;
+}
+
+cudaError_t OAL_INTRA_NAME(pad_images)(const void* q, const void* k, const void* v, const int32_t* dim_perm,
+                                       const int32_t* group_start, void* qimg, void* kimg, void* uimg,
+                                       int32_t* status, int B, int Hq, int Hkv, int N, int NB, int slabs,
+                                       cudaStream_t st) {
+  if (slabs < 1 || slabs > DP_MAX / 16) slabs = DP_MAX / 16;
+  const int smem = 2 * STAGE_BYTES;
+  cudaError_t e = cudaSuccess;
+  PadArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+            static_cast<const __nv_bfloat16*>(v), dim_perm, group_start, static_cast<unsigned char*>(qimg),
+            static_cast<unsigned char*>(kimg), static_cast<unsigned char*>(uimg), status, N, NB, Hq, Hkv, slabs};
+  pad_images_kernel<<<dim3(NB, Hq, B), 256, smem, st>>>(a);
   return cudaGetLastError();
 }
 

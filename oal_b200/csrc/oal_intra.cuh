@@ -29,10 +29,10 @@ struct PaddedGroups {
   f32x2 B2[IG], C2[IG * IG];
 };
 
-__device__ __forceinline__ void load_padded_groups(PaddedGroups& pg, const int32_t* dim_perm,
-                                                   const int32_t* group_start, const float* A, const float* Bc,
-                                                   const float* Cc, int G, int h, float bscale, float cdiag,
-                                                   float coff, int tid, int nthreads) {
+// Layout part: first slab of every group and the source dimension of every padded position.
+// Contains two block-wide barriers.
+__device__ __forceinline__ void load_group_layout(PaddedGroups& pg, const int32_t* dim_perm, const int32_t* group_start,
+                                                  int h, int tid, int nthreads) {
   if (tid == 0) {
     int acc = 0;
     for (int g = 0; g < IG; ++g) {
@@ -41,16 +41,6 @@ __device__ __forceinline__ void load_padded_groups(PaddedGroups& pg, const int32
       acc += (n + 15) >> 4;
     }
     pg.k16_start[IG] = acc;
-    pg.A = A[h];
-  }
-  for (int x = tid; x < IG; x += nthreads) {
-    const float v = x < G ? bscale * Bc[h * G + x] : 0.f;
-    pg.B2[x] = ((f32x2)__float_as_uint(v) << 32) | __float_as_uint(v);
-  }
-  for (int x = tid; x < IG * IG; x += nthreads) {
-    const int g = x / IG, g2 = x % IG;
-    const float v = (g < G && g2 < G) ? (g == g2 ? cdiag : coff) * Cc[((size_t)h * G + g) * G + g2] : 0.f;
-    pg.C2[x] = ((f32x2)__float_as_uint(v) << 32) | __float_as_uint(v);
   }
   __syncthreads();
   for (int p = tid; p < DP_MAX; p += nthreads) {
@@ -61,6 +51,23 @@ __device__ __forceinline__ void load_padded_groups(PaddedGroups& pg, const int32
     pg.src[p] = (p < 16 * pg.k16_start[IG] && t < n) ? (short)dim_perm[h * HD + s0 + t] : (short)-1;
   }
   __syncthreads();
+}
+
+__device__ __forceinline__ void load_padded_groups(PaddedGroups& pg, const int32_t* dim_perm,
+                                                   const int32_t* group_start, const float* A, const float* Bc,
+                                                   const float* Cc, int G, int h, float bscale, float cdiag,
+                                                   float coff, int tid, int nthreads) {
+  if (tid == 0) pg.A = A[h];
+  for (int x = tid; x < IG; x += nthreads) {
+    const float v = x < G ? bscale * Bc[h * G + x] : 0.f;
+    pg.B2[x] = ((f32x2)__float_as_uint(v) << 32) | __float_as_uint(v);
+  }
+  for (int x = tid; x < IG * IG; x += nthreads) {
+    const int g = x / IG, g2 = x % IG;
+    const float v = (g < G && g2 < G) ? (g == g2 ? cdiag : coff) * Cc[((size_t)h * G + g) * G + g2] : 0.f;
+    pg.C2[x] = ((f32x2)__float_as_uint(v) << 32) | __float_as_uint(v);
+  }
+  load_group_layout(pg, dim_perm, group_start, h, tid, nthreads);
 }
 
 constexpr int STAGE_WORDS = CT * 33;      // raw 128 x 64 bf16 tile, row pitch 33 words (conflict-free column walks)

@@ -61,7 +61,31 @@ struct IntraBwdArgs {
   int32_t* status;
   int N, NB, Hq, Hkv, G;
   float scale;
+  // padded q / k operand images and [v | 1] images made by pad_images, and the bytes of one q / k slot
+  const unsigned char *qimg, *kimg, *uimg;
+  int img_stride;
 };
+
+// All operand images of one CTA arrive by bulk copy on one barrier: G (hi, lo), q, k, [v | 1].
+// A head whose padded layout does not fit the image slots is refused (status word) and copies nothing.
+__device__ __forceinline__ bool fetch_images(const IntraBwdArgs& a, const PaddedGroups& pg, unsigned char* Qimg,
+                                             unsigned char* Kimg, unsigned char* Uimg, unsigned char* Gimg,
+                                             uint64_t* bar, int b, int h, int kvh, int c) {
+  const uint32_t bytes = (uint32_t)pg.k16_start[IG] * 4096u;
+  if (bytes > (uint32_t)a.img_stride) {
+    atomicOr(a.status, OAL_STATUS_BAD_LAYOUT);
+    return false;
+  }
+  const size_t item = (size_t)(b * a.Hq + h) * a.NB + c;
+  const unsigned char* gsrc = reinterpret_cast<const unsigned char*>(a.gimg) + item * SLAB_S_BYTES;
+  mbar_arrive_expect_tx(bar, 3 * SLAB_S_BYTES + 2 * bytes);
+  bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, bar);
+  bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, bar);
+  bulk_g2s(Qimg, a.qimg + item * (size_t)a.img_stride, bytes, bar);
+  bulk_g2s(Kimg, a.kimg + item * (size_t)a.img_stride, bytes, bar);
+  bulk_g2s(Uimg, a.uimg + ((size_t)(b * a.Hkv + kvh) * a.NB + c) * SLAB_S_BYTES, SLAB_S_BYTES, bar);
+  return true;
+}
 
 // scores -> (ds_g tiles, w) for 8 columns of one row.  ss = scale * s.
 struct PairOut {
@@ -84,6 +108,7 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
   __shared__ uint64_t s_done[2], s_free[2], ds_ready[2], ds_done[2], gfull;
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
+  __shared__ bool bad;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (a.Hq / a.Hkv);
@@ -105,25 +130,14 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_q_kernel(const IntraBwdAr
   }
   load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 2.f, 2.f, tid, BT_ALL);
   const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
-  if (tid == 0) {
-    const unsigned char* gsrc =
-        reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.Hq + h) * a.NB + c) * SLAB_S_BYTES;
-    mbar_arrive_expect_tx(&gfull, 2 * SLAB_S_BYTES);
-    bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, &gfull);
-    bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
-  }
-  // the ds tile buffers are idle during set-up: use them as the staging area of the image builds
-  // staging: the ds tile buffers and the U image are still idle (U is built right after)
-  build_padded_images(Qimg, Kimg, reinterpret_cast<uint32_t*>(DS), reinterpret_cast<uint32_t*>(Uimg), a.q + qoff * HD,
-                      a.k + koff * HD, c * CT, a.N, pg, tid, BT_ALL);
-  for (int idx = tid; idx < (EP / 8) * CT; idx += BT_ALL) {
-    const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
-    reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
-  }
-  fence_async_smem();
+  if (tid == 0) bad = !fetch_images(a, pg, Qimg, Kimg, Uimg, Gimg, &gfull, b, h, kvh, c);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
+  if (bad) {                        // refused layout: nothing was fetched, nothing is computed
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
+    return;
+  }
   Waiter w{&dead};
   // two score buffers (S_g tiles + dW tile each): the MMAs of tile kt+2 start as soon as every warp has
   // read tile kt, so a warp never waits for scores after its combine
@@ -359,6 +373,7 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
   __shared__ uint64_t s_done, s_free, ds_ready[2], ds_done[2], gfull;
   __shared__ uint32_t tmem_base;
   __shared__ int dead;
+  __shared__ bool bad;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (a.Hq / a.Hkv);
@@ -378,23 +393,14 @@ __global__ void __launch_bounds__(BT_ALL, 1) intra_bwd_kv_kernel(const IntraBwdA
   }
   load_padded_groups(pg, a.dim_perm, a.group_start, a.A, a.Bc, a.Cc, a.G, h, 1.f, 1.f, 1.f, tid, BT_ALL);
   const size_t koff = (size_t)(b * a.Hkv + kvh) * a.N, qoff = (size_t)(b * a.Hq + h) * a.N;
-  if (tid == 0) {
-    const unsigned char* gsrc =
-        reinterpret_cast<const unsigned char*>(a.gimg) + ((size_t)(b * a.Hq + h) * a.NB + c) * SLAB_S_BYTES;
-    mbar_arrive_expect_tx(&gfull, 2 * SLAB_S_BYTES);
-    bulk_g2s(Gimg, gsrc, SLAB_S_BYTES, &gfull);
-    bulk_g2s(Gimg + SLAB_S_BYTES, gsrc + a.gimg_lo_offset, SLAB_S_BYTES, &gfull);
-  }
-  build_padded_images(Kimg, Qimg, reinterpret_cast<uint32_t*>(DS), reinterpret_cast<uint32_t*>(Uimg), a.k + koff * HD,
-                      a.q + qoff * HD, c * CT, a.N, pg, tid, BT_ALL);
-  for (int idx = tid; idx < (EP / 8) * CT; idx += BT_ALL) {
-    const int ec = idx >> 7, t = idx & 127, j = c * CT + t;
-    reinterpret_cast<uint4*>(Uimg)[idx] = u_image_chunk(a.v + (koff + j) * VD, ec, j < a.N);
-  }
-  fence_async_smem();
+  if (tid == 0) bad = !fetch_images(a, pg, Qimg, Kimg, Uimg, Gimg, &gfull, b, h, kvh, c);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
+  if (bad) {                        // refused layout: nothing was fetched, nothing is computed
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
+    return;
+  }
   Waiter w{&dead};
   const uint32_t tS = tmem_base, tW = tmem_base + IG * KT, tK = tmem_base + IG * KT + KT, tU = tK + DP_MAX;
   const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
@@ -584,7 +590,8 @@ __global__ void __launch_bounds__(256) kv_head_reduce_kernel(const float* part, 
 cudaError_t OAL_INTRA_NAME(intra_backward_q)(const void* q, const void* k, const void* v, const void* gimg, const int32_t* dim_perm,
                              const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dq,
                              const float* dq_init, float* coef_partial, int32_t* status, int B, int Hq, int Hkv,
-                             int N, int NB, int G, float scale, cudaStream_t st) {
+                             int N, int NB, int G, float scale, const void* qimg, const void* kimg,
+                             const void* uimg, int img_stride, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(intra_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BQ_SMEM);
   if (e != cudaSuccess) return e;
   IntraBwdArgs a{};
@@ -594,6 +601,8 @@ cudaError_t OAL_INTRA_NAME(intra_backward_q)(const void* q, const void* k, const
   a.dq = dq; a.dq_init = dq_init; a.coef_partial = coef_partial; a.status = status;
   a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv; a.G = G; a.scale = scale;
   a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
+  a.qimg = static_cast<const unsigned char*>(qimg); a.kimg = static_cast<const unsigned char*>(kimg);
+  a.uimg = static_cast<const unsigned char*>(uimg); a.img_stride = img_stride;
   intra_bwd_q_kernel<<<dim3(NB, Hq, B), BT_ALL, BQ_SMEM, st>>>(a);
   return cudaGetLastError();
 }
@@ -602,7 +611,7 @@ cudaError_t OAL_INTRA_NAME(intra_backward_kv)(const void* q, const void* k, cons
                               const int32_t* group_start, const float* A, const float* Bc, const float* Cc, void* dk,
                               void* dv, const float* dk_cross, const float* dv_cross, float* dk_part, float* dv_part,
                               int32_t* status, int B, int Hq, int Hkv, int N, int NB, int G, float scale,
-                              cudaStream_t st) {
+                              const void* qimg, const void* kimg, const void* uimg, int img_stride, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(intra_bwd_kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BKV_SMEM);
   if (e != cudaSuccess) return e;
   IntraBwdArgs a{};
@@ -612,6 +621,8 @@ cudaError_t OAL_INTRA_NAME(intra_backward_kv)(const void* q, const void* k, cons
   a.dk_part = dk ? dk_part : nullptr; a.dv_part = dv ? dv_part : nullptr; a.status = status;
   a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv; a.G = G; a.scale = scale;
   a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
+  a.qimg = static_cast<const unsigned char*>(qimg); a.kimg = static_cast<const unsigned char*>(kimg);
+  a.uimg = static_cast<const unsigned char*>(uimg); a.img_stride = img_stride;
   intra_bwd_kv_kernel<<<dim3(NB, Hq, B), BT_ALL, BKV_SMEM, st>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
