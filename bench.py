@@ -393,9 +393,9 @@ def run_gpu_arm(args) -> None:
         # DRAM bytes (read + write) per launch of each kernel from the committed ncu capture of one batch
         # row (profiles/bench_headline_bf16_tensorcore.md, section 2); traffic grows in proportion to the
         # batch, so a launch of this workload moves batch x these bytes
-        ncu_dram_mb_per_row = {"intra_backward_q": 42.86, "intra_backward_kv": 27.98, "dstate_heads": 49.71,
-                               "feature_grad_q": 41.79, "cross_read_q": 32.48, "intra_forward": 24.40,
-                               "state_update": 2.97, "feature_grad_k": 27.09, "cross_read_k": 26.01}
+        ncu_dram_mb_per_row = {"intra_backward_q": 65.81, "intra_backward_kv": 51.17, "dstate_heads": 48.97,
+                               "feature_grad_q": 41.84, "cross_read_q": 32.48, "intra_forward": 46.08,
+                               "state_update": 2.99, "feature_grad_k": 27.09, "cross_read_k": 26.01}
         roofline = None
         if tc:
             # the dominant kernel by device time
