@@ -8,7 +8,7 @@
 #include <string>
 #include <vector>
 
-#include "oal_common.cuh"
+#include "oal_intra.cuh"
 #include "oal_kernels.h"
 
 namespace {
@@ -115,30 +115,18 @@ int chunk_count(const OalProblem* p) { return (p->seq_len + kChunk - 1) / kChunk
 struct ForwardSpaceTC {
   float* coef_table;
   float* ds;
-  void *qimg, *kimg, *uimg;        // operand images of the intra-chunk kernels (at most 8 groups per head)
   size_t bytes;
 };
 
-// q / k image slot of one (batch, query head, chunk) and the three image buffers of a problem
-size_t intra_image_stride(const OalProblem* p) {
-  return p->groups <= 4 ? oal::pad_image_bytes_g4(p->padded_slabs) : oal::pad_image_bytes(p->padded_slabs);
-}
-void take_intra_images(Carver& c, const OalProblem* p, void*& qimg, void*& kimg, void*& uimg) {
-  qimg = kimg = uimg = nullptr;
-  if (p->groups > 8) return;
-  const size_t items = (size_t)p->batch * p->q_heads * chunk_count(p);
-  qimg = c.take<char>(items * intra_image_stride(p));
-  kimg = c.take<char>(items * intra_image_stride(p));
-  uimg = c.take<char>((size_t)p->batch * p->kv_heads * chunk_count(p) * oal::state_slab_image_bytes());
-}
-int make_intra_images(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
-                      const int32_t* group_start, void* qimg, void* kimg, void* uimg, int32_t* status,
-                      cudaStream_t st) {
-  LaunchScope scope("pad_images", st);
-  cudaError_t e = (p->groups <= 4 ? oal::pad_images_g4 : oal::pad_images)(
-      q, k, v, dim_perm, group_start, qimg, kimg, uimg, status, p->batch, p->q_heads, p->kv_heads, p->seq_len,
-      chunk_count(p), p->padded_slabs, st);
-  return e == cudaSuccess ? OAL_OK : fail_cuda(e, "operand image kernel");
+// the intra-chunk term runs on the tensor cores for heads with at most 8 groups (else token-pair kernels)
+bool tc_intra(const OalProblem* p) { return p->groups + 1 <= oal::intra_coef_terms(); }
+
+int make_head_factors(const OalProblem* p, const int32_t* dim_perm, const int32_t* group_start, const float* coef_a,
+                      const float* coef_b, const float* coef_c, void* factors, cudaStream_t st) {
+  LaunchScope scope("head_factors", st);
+  cudaError_t e = oal::build_head_factors(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups,
+                                          p->scale, factors, st);
+  return e == cudaSuccess ? OAL_OK : fail_cuda(e, "head factor kernel");
 }
 
 ForwardSpaceTC carve_forward_tc(const OalProblem* p, void* ws) {
@@ -147,13 +135,19 @@ ForwardSpaceTC carve_forward_tc(const OalProblem* p, void* ws) {
   const size_t units = (size_t)p->batch * p->kv_heads;
   s.coef_table = c.take<float>((size_t)p->q_heads * oal::state_rows());
   s.ds = c.take<float>(units * chunk_count(p) * oal::state_rows() * oal::EP);
-  take_intra_images(c, p, s.qimg, s.kimg, s.uimg);
   s.bytes = c.off;
   return s;
 }
 
-size_t saved_state_bytes_tc(const OalProblem* p) {
-  return (size_t)p->batch * p->kv_heads * chunk_count(p) * oal::state_image_bytes_per_chunk();
+// The buffer the forward hands to the backward: the bf16 carry images of every chunk, then the per-head
+// factor table of the intra-chunk kernels (the backward of the same call sees the same coefficients,
+// so it does not factor them again).
+size_t saved_images_bytes_tc(const OalProblem* p) {
+  return align_up((size_t)p->batch * p->kv_heads * chunk_count(p) * oal::state_image_bytes_per_chunk());
+}
+size_t saved_state_bytes_tc(const OalProblem* p) { return saved_images_bytes_tc(p) + oal::head_factor_bytes(p->q_heads); }
+void* saved_factors(const OalProblem* p, const void* saved_state) {
+  return const_cast<char*>(static_cast<const char*>(saved_state)) + saved_images_bytes_tc(p);
 }
 
 struct BackwardSpaceTC {
@@ -168,7 +162,6 @@ struct BackwardSpaceTC {
   float* slots;
   float *dq_cross, *dk_cross, *dv_cross;
   float *dk_part, *dv_part;      // per-query-head intra-chunk shares of dk / dv
-  void *qimg, *kimg, *uimg;      // operand images of the intra-chunk kernels
   size_t bytes;
 };
 
@@ -193,7 +186,6 @@ BackwardSpaceTC carve_backward_tc(const OalProblem* p, void* ws) {
   s.dv_cross = c.take<float>(krows * oal::VD);
   s.dk_part = c.take<float>(qrows * oal::HD);
   s.dv_part = c.take<float>(qrows * oal::VD);
-  take_intra_images(c, p, s.qimg, s.kimg, s.uimg);
   s.bytes = c.off;
   return s;
 }
@@ -211,7 +203,7 @@ int backward_state_stage(const OalProblem* p, const void* q, const int32_t* dim_
   { LaunchScope scope("norm_vjp", st);
     // the fp32 rows of g are read by the token-pair kernels only (heads with more than 8 groups)
     e = oal::norm_vjp_image(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor,
-                            p->groups <= 8 ? nullptr : s.g, s.gimg,
+                            tc_intra(p) ? nullptr : s.g, s.gimg,
                             p->batch * p->q_heads, p->seq_len, nb, st); }
   if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
   { LaunchScope scope("coef_table", st);
@@ -375,12 +367,12 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
     e = oal::cross_read(true, q, saved_state, s.coef_table, num, den, p->batch, p->q_heads,
                         p->q_heads / p->kv_heads, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
-  if (p->groups <= 8) {
-    if (int rc = make_intra_images(p, q, k, v, dim_perm, group_start, s.qimg, s.kimg, s.uimg, status, st)) return rc;
+  if (tc_intra(p)) {
+    void* factors = saved_factors(p, saved_state);
+    if (int rc2 = make_head_factors(p, dim_perm, group_start, coef_a, coef_b, coef_c, factors, st)) return rc2;
     { LaunchScope scope("intra_forward", st);
-      e = (p->groups <= 4 ? oal::intra_forward_g4 : oal::intra_forward)(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
-                             p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor,
-                             s.qimg, s.kimg, s.uimg, st); }
+      e = oal::intra_forward(q, k, v, factors, out, num, den, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
+                             p->out_dtype, p->floor, st); }
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
     return OAL_OK;
   }
@@ -448,17 +440,14 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
   const int nb = chunk_count(p), units = p->batch * p->kv_heads, rep = p->q_heads / p->kv_heads;
   const bool want_q = mask & OAL_GRAD_Q, want_k = mask & OAL_GRAD_K, want_v = mask & OAL_GRAD_V;
   const bool want_c = mask & OAL_GRAD_COEF;
-  const bool tc_intra = p->groups <= 8;      // intra-chunk term on the tensor cores (else token-pair kernels)
+  const bool tc = tc_intra(p);                // intra-chunk term on the tensor cores (else token-pair kernels)
   cudaError_t e;
   if (!(mask & OAL_GRAD_REUSE_STATE_STAGE)) {
     rc = backward_state_stage(p, q, dim_perm, group_start, coef_a, coef_b, coef_c, num, den, saved_state, grad_out,
                               grad_num, grad_den, s, status, st);
     if (rc) return rc;
   }
-  if (tc_intra) {
-    rc = make_intra_images(p, q, k, v, dim_perm, group_start, s.qimg, s.kimg, s.uimg, status, st);
-    if (rc) return rc;
-  }
+  const void* factors = saved_factors(p, saved_state);      // written by the forward of this call
   if (want_k || want_v) {
     { LaunchScope scope("state_scan_reverse", st);
       e = oal::state_scan(s.dcarry, s.dt_img, dstate_in, nullptr, units, nb, 1, st); }
@@ -474,12 +463,11 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
                               rep, p->seq_len, nb, status, st); }
       if (e != cudaSuccess) return fail_cuda(e, "query feature gradient kernel");
     }
-    if (tc_intra) {
+    if (tc) {
       { LaunchScope scope("intra_backward_q", st);
-        e = (p->groups <= 4 ? oal::intra_backward_q_g4 : oal::intra_backward_q)(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_q ? dq : nullptr,
-                                  want_q ? s.dq_cross : nullptr, want_c ? s.coef_pairs : nullptr, status, p->batch,
-                                  p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->scale, s.qimg, s.kimg, s.uimg,
-                                  (int)intra_image_stride(p), st); }
+        e = oal::intra_backward_q(q, k, v, s.gimg, factors, want_q ? dq : nullptr, want_q ? s.dq_cross : nullptr,
+                                  want_c ? s.coef_pairs : nullptr, status, p->batch, p->q_heads, p->kv_heads,
+                                  p->seq_len, nb, st); }
       if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward query-side kernel");
     } else {
       a.dq = want_q ? dq : nullptr;
@@ -493,8 +481,11 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
         e = oal::dcoef_reduce(s.dcoef_partial, 2 * p->batch * nb, p->q_heads, dim_perm, group_start, s.dcoef, s.slots, st); }
       if (e != cudaSuccess) return fail_cuda(e, "coefficient gradient reduction kernels");
       { LaunchScope scope("reduce_coefs", st);
-        e = oal::reduce_coefs(s.coef_pairs, tc_intra ? nb : oal::pairs_tiles(p->seq_len), s.slots, p->batch,
-                              p->q_heads, p->groups, d_coef_a, d_coef_b, d_coef_c, st); }
+        const int rm = oal::intra_coef_terms();
+        e = tc ? oal::intra_coef_finish(s.coef_pairs, nb, rm * (rm + 1) / 2 + rm + 1, rm, factors, s.slots, p->batch,
+                                        p->q_heads, p->groups, d_coef_a, d_coef_b, d_coef_c, st)
+               : oal::reduce_coefs(s.coef_pairs, oal::pairs_tiles(p->seq_len), s.slots, p->batch, p->q_heads,
+                                   p->groups, d_coef_a, d_coef_b, d_coef_c, st); }
       if (e != cudaSuccess) return fail_cuda(e, "coefficient reduction kernel");
     }
   }
@@ -511,12 +502,11 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
                             nb, status, st); }
       if (e != cudaSuccess) return fail_cuda(e, "key cross read kernel");
     }
-    if (tc_intra) {
+    if (tc) {
       { LaunchScope scope("intra_backward_kv", st, 1 + (want_k ? 1 : 0) + (want_v ? 1 : 0));
-        e = (p->groups <= 4 ? oal::intra_backward_kv_g4 : oal::intra_backward_kv)(q, k, v, s.gimg, dim_perm, group_start, coef_a, coef_b, coef_c, want_k ? dk : nullptr,
-                                   want_v ? dv : nullptr, want_k ? s.dk_cross : nullptr, want_v ? s.dv_cross : nullptr,
-                                   s.dk_part, s.dv_part, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
-                                   p->groups, p->scale, s.qimg, s.kimg, s.uimg, (int)intra_image_stride(p), st); }
+        e = oal::intra_backward_kv(q, k, v, s.gimg, factors, want_k ? dk : nullptr, want_v ? dv : nullptr,
+                                   want_k ? s.dk_cross : nullptr, want_v ? s.dv_cross : nullptr, s.dk_part, s.dv_part,
+                                   status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb, st); }
       if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward key/value-side kernel");
     } else {
       a.dq = nullptr; a.dq_init = nullptr; a.coef_partial = nullptr;
@@ -639,6 +629,7 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
   if (rc) return rc;
   float* coef_table = scratch;
   float* ds = scratch + kStaticTableFloats;
+  void* factors = saved_factors(p, saved_state);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   { LaunchScope scope("coef_table", st);
@@ -652,11 +643,11 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
     e = oal::cross_read(true, q, saved_state, coef_table, num, den, p->batch, p->q_heads, p->q_heads / p->kv_heads,
                         p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
-  if (p->groups <= 8) {
+  if (tc_intra(p)) {
+    if (int rc2 = make_head_factors(p, dim_perm, group_start, coef_a, coef_b, coef_c, factors, st)) return rc2;
     { LaunchScope scope("intra_forward", st);
-      e = (p->groups <= 4 ? oal::intra_forward_g4 : oal::intra_forward)(q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, out, num, den, status, p->batch,
-                             p->q_heads, p->kv_heads, p->seq_len, nb, p->groups, p->out_dtype, p->padded_slabs, p->scale, p->floor,
-                             nullptr, nullptr, nullptr, st); }     // no scratch for images: built inside the kernel
+      e = oal::intra_forward(q, k, v, factors, out, num, den, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
+                             p->out_dtype, p->floor, st); }
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
     return OAL_OK;
   }

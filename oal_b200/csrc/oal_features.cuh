@@ -286,6 +286,7 @@ __device__ __forceinline__ void load_row_bf16(float (&x)[HD], const __nv_bfloat1
 struct Waiter {
   int* dead;          // shared flag: a wait expired somewhere in this CTA (holds the site id, >= 1)
   __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity, int site = 1) {
+    if (umma::mbar_test(bar, parity)) return;           // already complete: the common case costs one probe
     if (*reinterpret_cast<volatile int*>(dead)) return;
     if (!umma::mbar_wait(bar, parity)) *reinterpret_cast<volatile int*>(dead) = site;
   }

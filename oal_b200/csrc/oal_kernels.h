@@ -77,34 +77,27 @@ cudaError_t norm_vjp_image(const void* grad_out, int out_dt, const float* grad_n
                            int N, int NB, cudaStream_t st);
 
 
-// ---- tensor-core intra-chunk kernels (oal_intra.cu, oal_intra_bwd.cu) ----
-// pad_images writes the padded q / k operand images of every (batch, query head, chunk) and the [v | 1]
-// image of every (batch, KV head, chunk) once; the three kernels fetch them with bulk copies.
-// intra_forward also accepts null images and then builds them itself.
-#define OAL_INTRA_DECLS(SUFFIX)                                                                                        \
-  size_t pad_image_bytes##SUFFIX(int slabs);                                                                           \
-  cudaError_t pad_images##SUFFIX(const void* q, const void* k, const void* v, const int32_t* dim_perm,                 \
-                                 const int32_t* group_start, void* qimg, void* kimg, void* uimg, int32_t* status,     \
-                                 int B, int Hq, int Hkv, int N, int NB, int slabs, cudaStream_t st);                   \
-  cudaError_t intra_forward##SUFFIX(const void* q, const void* k, const void* v, const int32_t* dim_perm,              \
-                                    const int32_t* group_start, const float* A, const float* Bc, const float* Cc,     \
-                                    void* out, float* num, float* den, int32_t* status, int B, int Hq, int Hkv,       \
-                                    int N, int NB, int G, int out_dt, int slabs, float scale, float floor_v,           \
-                                    const void* qimg, const void* kimg, const void* uimg, cudaStream_t st);            \
-  cudaError_t intra_backward_q##SUFFIX(const void* q, const void* k, const void* v, const void* gimg,                  \
-                                       const int32_t* dim_perm, const int32_t* group_start, const float* A,           \
-                                       const float* Bc, const float* Cc, void* dq, const float* dq_init,              \
-                                       float* coef_partial, int32_t* status, int B, int Hq, int Hkv, int N, int NB,   \
-                                       int G, float scale, const void* qimg, const void* kimg, const void* uimg,      \
-                                       int img_stride, cudaStream_t st);                                               \
-  cudaError_t intra_backward_kv##SUFFIX(const void* q, const void* k, const void* v, const void* gimg,                 \
-                                        const int32_t* dim_perm, const int32_t* group_start, const float* A,          \
-                                        const float* Bc, const float* Cc, void* dk, void* dv, const float* dk_cross,  \
-                                        const float* dv_cross, float* dk_part, float* dv_part, int32_t* status,       \
-                                        int B, int Hq, int Hkv, int N, int NB, int G, float scale, const void* qimg,  \
-                                        const void* kimg, const void* uimg, int img_stride, cudaStream_t st);
-OAL_INTRA_DECLS()          // at most 8 groups per head
-OAL_INTRA_DECLS(_g4)       // the same kernels compiled for at most 4 groups per head
-#undef OAL_INTRA_DECLS
+// ---- factored intra-chunk weight (oal_factor.cu) -----------------------------------------
+// Per-head table of the factored quadratic form (c_r, l_r[d], back-transform, sign split).
+size_t head_factor_bytes(int Hq);
+cudaError_t build_head_factors(const int32_t* dim_perm, const int32_t* group_start, const float* A, const float* Bc,
+                               const float* Cc, int Hq, int G, float scale, void* table, cudaStream_t st);
+// dA, dB, dC = back-transformed sum of the query-side partial sums [B][Hq][tiles][nu_stride] (rm terms,
+// upper triangle) + extra ([Hq][NCOEF] slots of the cross-chunk term, or null).
+cudaError_t intra_coef_finish(const float* partial, int tiles, int nu_stride, int rm, const void* table,
+                              const float* extra, int B, int Hq, int G, float* dA, float* dB, float* dC,
+                              cudaStream_t st);
+
+// ---- tensor-core intra-chunk kernels (oal_intra.cu, oal_intra_bwd.cu): heads with at most 8 groups ----
+int intra_coef_terms();          // terms per head this build handles (rows of the partial-sum triangle)
+cudaError_t intra_forward(const void* q, const void* k, const void* v, const void* factors, void* out, float* num,
+                          float* den, int32_t* status, int B, int Hq, int Hkv, int N, int NB, int out_dt,
+                          float floor_v, cudaStream_t st);
+cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const void* gimg, const void* factors,
+                             void* dq, const float* dq_init, float* coef_partial, int32_t* status, int B, int Hq,
+                             int Hkv, int N, int NB, cudaStream_t st);
+cudaError_t intra_backward_kv(const void* q, const void* k, const void* v, const void* gimg, const void* factors,
+                              void* dk, void* dv, const float* dk_cross, const float* dv_cross, float* dk_part,
+                              float* dv_part, int32_t* status, int B, int Hq, int Hkv, int N, int NB, cudaStream_t st);
 
 }  // namespace oal

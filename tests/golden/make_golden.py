@@ -1,10 +1,10 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE itself.
 
 Run once in a container that has the reference checkout (it is imported from
-``--reference``, default /root/reference); the produced files are committed and
+the directory given with ``--reference``); the produced files are committed and
 the test-suite never needs the reference again.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <checkout of wuqianyue09/OAL> [--only name,name]
 
 Outputs
   kat_two_groups.json, kat_different_active_group_counts.json
@@ -22,6 +22,19 @@ Outputs
       outputs / gradients of the reference's own chunked production path
       (``hd_attention.grouped_causal_attention(precision="fp32_ieee")``, CPU)
       and of the fp64 dense statement, stored for every 64th token only.
+  config2_rows.npz
+      the benchmarked configuration itself (B=4, 14 query / 2 KV heads, N=4096,
+      G=8, the inputs of ``bench.py`` rank 0): every 64th token of batch rows 0
+      and 3, all 14 heads, from the reference's chunked fp32 path and from the
+      fp64 dense statement; dfactor over the whole batch.
+  sweep_rows.npz
+      one cell per group count G in {1, 4, 8, 16} of the sequence-length x
+      group-count sweep at N=4096 (B=1, 14 / 2 heads): every 128th token, both
+      references.
+  long_rows.npz
+      the sequence-parallel configuration (B=1, 14 / 2 heads, N=32768, chunk 64):
+      every 1024th token of the reference's chunked fp32 path (the quadratic dense
+      statement is not evaluated at this length).
 """
 
 from __future__ import annotations
@@ -184,15 +197,115 @@ def emit_qwen_rows():
     _save("qwen_n4096_rows", case, arrays, dict(row_stride=np.array(stride)))
 
 
+def _hd_reference(case, token_block=64):
+    """The reference's own chunked production path on the CPU in fp32 (forward + autograd backward)."""
+    from oal_attention.hd_attention import grouped_causal_attention
+
+    q, k, v = (t.clone().requires_grad_() for t in (case.q, case.k, case.v))
+    factor = case.factor.clone().requires_grad_()
+    out, num, den = grouped_causal_attention(q, k, v, case.dim_groups, factor, scale=case.scale,
+                                             kernel_eps=case.kernel_eps, token_block=token_block,
+                                             feature_wave_blocks=4, precision="fp32_ieee",
+                                             backward_schedule="shared_wave")
+    out.backward(case.grad_out)
+    return dict(out=out.detach(), num=num.detach(), den=den.detach(), dq=q.grad, dk=k.grad, dv=v.grad,
+                dfactor=factor.grad)
+
+
+def _dense_by_head(case, batch_rows=None):
+    """fp64 dense statement one (batch row, query head) at a time: O(N^2) memory per call only."""
+    from oracle import oal_oracle as orc
+
+    B, hq, n, _ = case.q.shape
+    hkv = case.k.shape[1]
+    rep = hq // hkv
+    a, b, c = orc.expand_factor(case.factor, hq, case.kernel_eps)
+    res = {name: torch.zeros_like(t, dtype=torch.float64)
+           for name, t in dict(out=case.q, num=case.q, dq=case.q, dk=case.k, dv=case.v).items()}
+    res["den"] = torch.zeros(B, hq, n, 1, dtype=torch.float64)
+    res["dA"], res["dB"], res["dC"] = torch.zeros_like(a), torch.zeros_like(b), torch.zeros_like(c)
+    for bi in (range(B) if batch_rows is None else batch_rows):
+        for h in range(hq):
+            kv = h // rep
+            r = orc.dense_backward(case.q[bi:bi + 1, h:h + 1].double(), case.k[bi:bi + 1, kv:kv + 1].double(),
+                                   case.v[bi:bi + 1, kv:kv + 1].double(), case.dim_groups, a[h:h + 1],
+                                   b[h:h + 1], c[h:h + 1], scale=case.scale,
+                                   grad_out=case.grad_out[bi:bi + 1, h:h + 1].double())
+            for name in ("out", "num", "den", "dq"):
+                res[name][bi, h] = r[name][0, 0]
+            res["dk"][bi, kv] += r["dk"][0, 0]
+            res["dv"][bi, kv] += r["dv"][0, 0]
+            res["dA"][h] += r["dA"][0]
+            res["dB"][h] += r["dB"][0]
+            res["dC"][h] += r["dC"][0]
+            print(f"  dense row {bi} head {h} done", flush=True)
+    factor = case.factor.double().clone().requires_grad_()
+    fa, fb, fc = orc.expand_factor(factor, hq, case.kernel_eps)
+    ((fa * res["dA"]).sum() + (fb * res["dB"]).sum() + (fc * res["dC"]).sum()).backward()
+    res["dfactor"] = factor.grad
+    return res
+
+
+def _rows(res, stride, batch_rows=None):
+    out = {}
+    for name, t in res.items():
+        if t.ndim == 4:
+            t = t[:, :, ::stride]
+            if batch_rows is not None:
+                t = t[list(batch_rows)]
+        out[name] = t
+    return out
+
+
+def emit_config2_rows():
+    """The benchmarked configuration: the inputs bench.py gives rank 0 (seed 0), both references."""
+    case = synthetic.qwen_head_case(0, batch=4, n=4096, hq=14, hkv=2, g=8, bf16=True)
+    stride, keep = 64, (0, 3)
+    arrays = {}
+    for name, t in _rows(_hd_reference(case), stride, keep).items():
+        arrays[f"hd_{name}"] = t
+    print("config2: reference chunked path done", flush=True)
+    for name, t in _rows(_dense_by_head(case), stride, keep).items():
+        arrays[f"dense_{name}"] = t
+    _save("config2_rows", case, arrays, dict(row_stride=np.array(stride), batch_rows=np.array(keep)))
+
+
+def emit_sweep_rows():
+    """One cell per group count of the N x G sweep at N = 4096 (B=1, 14 / 2 heads)."""
+    stride = 128
+    arrays, digests = {}, []
+    for g in (1, 4, 8, 16):
+        case = synthetic.qwen_head_case(40 + g, batch=1, n=4096, hq=14, hkv=2, g=g, bf16=True)
+        for name, t in _rows(_hd_reference(case), stride).items():
+            arrays[f"g{g}_hd_{name}"] = _np(t)
+        print(f"sweep G={g}: reference chunked path done", flush=True)
+        for name, t in _rows(_dense_by_head(case), stride).items():
+            arrays[f"g{g}_dense_{name}"] = _np(t)
+        digests.append(synthetic.tensor_digest(case.q, case.k, case.v, case.dim_groups))
+    arrays["input_digests"] = np.frombuffer("".join(digests).encode(), dtype=np.uint8)
+    arrays["row_stride"] = np.array(stride)
+    np.savez_compressed(HERE / "sweep_rows.npz", **arrays)
+    print("wrote sweep_rows.npz:", {k: v.shape for k, v in arrays.items()})
+
+
+def emit_long_rows():
+    """Sequence-parallel configuration (N = 32768): every 1024th token of the reference's chunked path."""
+    case = synthetic.qwen_head_case(7, batch=1, n=32768, hq=14, hkv=2, g=8, bf16=True)
+    stride = 1024
+    arrays = {f"hd_{name}": t for name, t in _rows(_hd_reference(case), stride).items()}
+    _save("long_rows", case, arrays, dict(row_stride=np.array(stride)))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True)
     ap.add_argument("--only", default="")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     torch.set_num_threads(8)
     todo = dict(kats=lambda: emit_kats(Path(args.reference)), config1=emit_config1, mixed=emit_mixed,
-                qwen_small=emit_qwen_small, qwen_rows=emit_qwen_rows)
+                qwen_small=emit_qwen_small, qwen_rows=emit_qwen_rows, config2_rows=emit_config2_rows,
+                sweep_rows=emit_sweep_rows, long_rows=emit_long_rows)
     for name, fn in todo.items():
         if args.only and name not in args.only.split(","):
             continue
