@@ -57,7 +57,7 @@ enum {
   OAL_STATUS_DENOMINATOR = 2,    /* denominator <= 0                                        */
   OAL_STATUS_WAIT_TIMEOUT = 4,   /* a bounded mbarrier wait inside a kernel gave up; bits 8..15
                                     then hold the id of the wait site                       */
-  OAL_STATUS_BAD_LAYOUT = 8      /* a head needs more padded slabs than problem.padded_slabs */
+  OAL_STATUS_BAD_LAYOUT = 8      /* reserved (no kernel raises it)                          */
 };
 
 /* gradient request mask, same order as the reference's requested_gradient_mask
@@ -84,8 +84,8 @@ typedef struct OalProblem {
   int32_t grad_mask;    /* OAL_GRAD_* bits requested from oal_backward                  */
   float scale;          /* q is multiplied by this before anything else                 */
   float floor;          /* normalisation floor: out = num / max(den, floor)             */
-  int32_t padded_slabs; /* upper bound over heads of sum_g ceil(|group g| / 16), 4..11, or 0 when
-                           unknown (then 11 is assumed); sizes shared-memory operand images  */
+  int32_t padded_slabs; /* unused (earlier builds sized shared-memory images with it); kept so that the
+                           struct layout does not change: pass 0                             */
 } OalProblem;
 
 /* Bytes of workspace oal_forward (phase 0) / oal_backward (phase 1) need, and
@@ -213,6 +213,15 @@ const char* oal_last_error_string(void);
  */
 int oal_selftest_umma(int mode, int n, int k, const void* a, const void* b, float* d, int32_t* status,
                       void* stream);
+
+/*
+ * Self-test of the bounded-wait path every tensor-core kernel relies on (no counterpart in the reference,
+ * which has no device-side waits).  One warp waits on a barrier that nothing arrives on, with a limit of
+ * `limit_clocks` SM clocks (1 .. 1 000 000, i.e. at most about half a millisecond); the wait gives up and
+ * the kernel ORs OAL_STATUS_WAIT_TIMEOUT | (0x7E << 8) into *status and returns normally, exactly as the
+ * production kernels do after their 50 M-clock limit.  Nothing hangs or faults; the context stays usable.
+ */
+int oal_selftest_wait_timeout(int64_t limit_clocks, int32_t* status, void* stream);
 
 /*
  * Launch accounting and opt-in per-kernel timing (thin counterpart of the reference's stage

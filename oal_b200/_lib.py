@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "oal_last_error_string",
     "oal_version_string",
     "oal_selftest_umma",
+    "oal_selftest_wait_timeout",
     "oal_launch_count",
     "oal_profile_enable",
     "oal_profile_report",
@@ -101,6 +102,8 @@ def load() -> ctypes.CDLL:
     lib.oal_rope_unpack_grad.restype = ctypes.c_int
     lib.oal_selftest_umma.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp, f32p, i32p, vp]
     lib.oal_selftest_umma.restype = ctypes.c_int
+    lib.oal_selftest_wait_timeout.argtypes = [ctypes.c_int64, i32p, vp]
+    lib.oal_selftest_wait_timeout.restype = ctypes.c_int
     lib.oal_launch_count.restype = ctypes.c_int64
     lib.oal_profile_enable.argtypes = [ctypes.c_int]
     lib.oal_profile_enable.restype = None
@@ -114,6 +117,15 @@ def load() -> ctypes.CDLL:
 
 def ptr(t: torch.Tensor | None):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def device_guard(t: torch.Tensor):
+    """Context manager that makes ``t``'s CUDA device current for the duration of a library call.
+
+    The kernels launch on the calling thread's current device while the stream that is passed in
+    belongs to the tensors' device; the reference is plain torch code and follows the tensors, so
+    every entry into the library goes through this guard."""
+    return torch.cuda.device(t.device)
 
 
 def check(rc: int) -> None:

@@ -72,9 +72,11 @@ class _RopePackFunction(torch.autograd.Function):
         q = torch.empty(b, q_heads, n, 64, dtype=q_flat.dtype, device=q_flat.device)
         k = torch.empty(b, kv_heads, n, 64, dtype=q_flat.dtype, device=q_flat.device)
         v = torch.empty(b, kv_heads, n, 64, dtype=q_flat.dtype, device=q_flat.device)
-        _lib.check(_lib.load().oal_rope_pack(_lib.ptr(q_flat), _lib.ptr(k_flat), _lib.ptr(v_flat), _lib.ptr(cos),
-                                             _lib.ptr(sin), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), b, n, q_heads,
-                                             kv_heads, _stream_ptr(q_flat.device)))
+        with _lib.device_guard(q_flat):
+            rc = _lib.load().oal_rope_pack(_lib.ptr(q_flat), _lib.ptr(k_flat), _lib.ptr(v_flat), _lib.ptr(cos),
+                                           _lib.ptr(sin), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), b, n, q_heads,
+                                           kv_heads, _stream_ptr(q_flat.device))
+        _lib.check(rc)
         ctx.save_for_backward(cos, sin)
         ctx.geometry = (b, n, q_heads, kv_heads)
         return q, k, v
@@ -90,9 +92,11 @@ class _RopePackFunction(torch.autograd.Function):
         dq, dk, dv = (None if g is None else g.contiguous() for g in (dq, dk, dv))
         dq_flat, dk_flat, dv_flat = mk(dq, hq), mk(dk, hkv), mk(dv, hkv)
         dev = next(g for g in (dq, dk, dv) if g is not None).device
-        _lib.check(_lib.load().oal_rope_unpack_grad(_lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(cos),
-                                                    _lib.ptr(sin), _lib.ptr(dq_flat), _lib.ptr(dk_flat),
-                                                    _lib.ptr(dv_flat), b, n, hq, hkv, _stream_ptr(dev)))
+        with torch.cuda.device(dev):
+            rc = _lib.load().oal_rope_unpack_grad(_lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(cos),
+                                                  _lib.ptr(sin), _lib.ptr(dq_flat), _lib.ptr(dk_flat),
+                                                  _lib.ptr(dv_flat), b, n, hq, hkv, _stream_ptr(dev))
+        _lib.check(rc)
         return dq_flat, dk_flat, dv_flat, None, None, None, None
 
 

@@ -41,9 +41,10 @@ struct LaunchScope {
   cudaStream_t st;
   bool timed = false;
   ProfEntry entry{};
-  LaunchScope(const char* name, cudaStream_t stream, int launches = 1) : st(stream) {
+  // `timing`: false for entry points that promise to make no allocating call (event creation is one)
+  LaunchScope(const char* name, cudaStream_t stream, int launches = 1, bool timing = true) : st(stream) {
     g_launches += launches;
-    if (!g_prof_enabled.load()) return;
+    if (!timing || !g_prof_enabled.load()) return;
     entry.name = name;
     if (cudaEventCreate(&entry.start) != cudaSuccess || cudaEventCreate(&entry.stop) != cudaSuccess) return;
     timed = true;
@@ -122,8 +123,8 @@ struct ForwardSpaceTC {
 bool tc_intra(const OalProblem* p) { return p->groups + 1 <= oal::intra_coef_terms(); }
 
 int make_head_factors(const OalProblem* p, const int32_t* dim_perm, const int32_t* group_start, const float* coef_a,
-                      const float* coef_b, const float* coef_c, void* factors, cudaStream_t st) {
-  LaunchScope scope("head_factors", st);
+                      const float* coef_b, const float* coef_c, void* factors, cudaStream_t st, bool timing = true) {
+  LaunchScope scope("head_factors", st, 1, timing);
   cudaError_t e = oal::build_head_factors(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups,
                                           p->scale, factors, st);
   return e == cudaSuccess ? OAL_OK : fail_cuda(e, "head factor kernel");
@@ -139,15 +140,19 @@ ForwardSpaceTC carve_forward_tc(const OalProblem* p, void* ws) {
   return s;
 }
 
-// The buffer the forward hands to the backward: the bf16 carry images of every chunk, then the per-head
-// factor table of the intra-chunk kernels (the backward of the same call sees the same coefficients,
-// so it does not factor them again).
+// The buffer the forward hands to the backward: the bf16 carry images of every chunk (the MMA operand),
+// the images of their rounding remainders (read only by the coefficient-gradient dot products), then the
+// per-head factor table of the intra-chunk kernels (the backward of the same call sees the same
+// coefficients, so it does not factor them again).
 size_t saved_images_bytes_tc(const OalProblem* p) {
   return align_up((size_t)p->batch * p->kv_heads * chunk_count(p) * oal::state_image_bytes_per_chunk());
 }
-size_t saved_state_bytes_tc(const OalProblem* p) { return saved_images_bytes_tc(p) + oal::head_factor_bytes(p->q_heads); }
-void* saved_factors(const OalProblem* p, const void* saved_state) {
+size_t saved_state_bytes_tc(const OalProblem* p) { return 2 * saved_images_bytes_tc(p) + oal::head_factor_bytes(p->q_heads); }
+void* saved_remainders(const OalProblem* p, const void* saved_state) {
   return const_cast<char*>(static_cast<const char*>(saved_state)) + saved_images_bytes_tc(p);
+}
+void* saved_factors(const OalProblem* p, const void* saved_state) {
+  return const_cast<char*>(static_cast<const char*>(saved_state)) + 2 * saved_images_bytes_tc(p);
 }
 
 struct BackwardSpaceTC {
@@ -211,7 +216,8 @@ int backward_state_stage(const OalProblem* p, const void* q, const int32_t* dim_
   if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
   if (mask & (OAL_GRAD_K | OAL_GRAD_V | OAL_GRAD_COEF)) {
     { LaunchScope scope("dstate_heads", st);
-      e = oal::dstate_heads(q, s.gimg, want_c ? saved_state : nullptr, s.coef_table, s.dcarry,
+      e = oal::dstate_heads(q, s.gimg, want_c ? saved_state : nullptr, want_c ? saved_remainders(p, saved_state) : nullptr,
+                            s.coef_table, s.dcarry,
                             want_c ? s.dcoef_partial : nullptr, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
                             p->scale, status, st); }
     if (e != cudaSuccess) return fail_cuda(e, "state gradient kernel");
@@ -361,7 +367,7 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
   if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
   { LaunchScope scope("state_update", st); e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
-  { LaunchScope scope("state_scan", st); e = oal::state_scan(s.ds, saved_state, state_in, nullptr, units, nb, 0, st); }
+  { LaunchScope scope("state_scan", st); e = oal::state_scan(s.ds, saved_state, saved_remainders(p, saved_state), state_in, nullptr, units, nb, 0, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state scan kernel");
   { LaunchScope scope("cross_read_q", st);
     e = oal::cross_read(true, q, saved_state, s.coef_table, num, den, p->batch, p->q_heads,
@@ -450,7 +456,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
   const void* factors = saved_factors(p, saved_state);      // written by the forward of this call
   if (want_k || want_v) {
     { LaunchScope scope("state_scan_reverse", st);
-      e = oal::state_scan(s.dcarry, s.dt_img, dstate_in, nullptr, units, nb, 1, st); }
+      e = oal::state_scan(s.dcarry, s.dt_img, nullptr, dstate_in, nullptr, units, nb, 1, st); }
     if (e != cudaSuccess) return fail_cuda(e, "reverse state scan kernel");
   }
   oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
@@ -536,7 +542,7 @@ int oal_forward_local_state(const OalProblem* p, const void* k, const void* v, f
   cudaError_t e;
   { LaunchScope scope("state_update", st); e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
-  { LaunchScope scope("state_total", st); e = oal::state_scan(s.ds, nullptr, nullptr, state_total, units, nb, 0, st); }
+  { LaunchScope scope("state_total", st); e = oal::state_scan(s.ds, nullptr, nullptr, nullptr, state_total, units, nb, 0, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state total kernel");
   return OAL_OK;
 }
@@ -562,7 +568,7 @@ int oal_backward_local_state(const OalProblem* p, const void* q, const int32_t* 
   if (rc) return rc;
   cudaError_t e;
   { LaunchScope scope("state_total", st);
-    e = oal::state_scan(s.dcarry, nullptr, nullptr, dstate_total, p->batch * p->kv_heads, chunk_count(p), 1, st); }
+    e = oal::state_scan(s.dcarry, nullptr, nullptr, nullptr, dstate_total, p->batch * p->kv_heads, chunk_count(p), 1, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state gradient total kernel");
   return OAL_OK;
 }
@@ -632,20 +638,20 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
   void* factors = saved_factors(p, saved_state);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  { LaunchScope scope("coef_table", st);
+  { LaunchScope scope("coef_table", st, 1, false);
     e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, p->scale, coef_table, st); }
   if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
-  { LaunchScope scope("state_update", st); e = oal::state_update(k, v, ds, units, p->seq_len, nb, status, st); }
+  { LaunchScope scope("state_update", st, 1, false); e = oal::state_update(k, v, ds, units, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
-  { LaunchScope scope("state_scan", st); e = oal::state_scan(ds, saved_state, nullptr, nullptr, units, nb, 0, st); }
+  { LaunchScope scope("state_scan", st, 1, false); e = oal::state_scan(ds, saved_state, saved_remainders(p, saved_state), nullptr, nullptr, units, nb, 0, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state scan kernel");
-  { LaunchScope scope("cross_read_q", st);
+  { LaunchScope scope("cross_read_q", st, 1, false);
     e = oal::cross_read(true, q, saved_state, coef_table, num, den, p->batch, p->q_heads, p->q_heads / p->kv_heads,
                         p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
   if (tc_intra(p)) {
-    if (int rc2 = make_head_factors(p, dim_perm, group_start, coef_a, coef_b, coef_c, factors, st)) return rc2;
-    { LaunchScope scope("intra_forward", st);
+    if (int rc2 = make_head_factors(p, dim_perm, group_start, coef_a, coef_b, coef_c, factors, st, false)) return rc2;
+    { LaunchScope scope("intra_forward", st, 1, false);
       e = oal::intra_forward(q, k, v, factors, out, num, den, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
                              p->out_dtype, p->floor, st); }
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
@@ -654,7 +660,7 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
   oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
   a.window = kChunk;
   a.out = out; a.num = num; a.den = den; a.accumulate = 1;
-  { LaunchScope scope("pairs_forward", st); e = oal::pairs_forward(a, st); }
+  { LaunchScope scope("pairs_forward", st, 1, false); e = oal::pairs_forward(a, st); }
   if (e != cudaSuccess) return fail_cuda(e, "forward pair kernel");
   return OAL_OK;
 }

@@ -302,11 +302,14 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_q_kernel(const IntraBwd
 // ---------------------------------------------------------------------------
 // key / value side: one CTA per (chunk, query head, batch row); rows are keys
 // ---------------------------------------------------------------------------
-// shared memory: Ka | Qimg | G hi | G lo | 3 stacks | U   (G lo and U are dead once dW is complete)
+// shared memory: Ka | Qimg | G hi | G lo | 3 stacks | 2 remainder stacks | U   (G lo and U are dead once dW
+// is complete).  The stack is carried as value + remainder here too: its rounding acts like a perturbation
+// of the query rows that is the same for every key, and with large cancelling dimensions that alone costs
+// dk / dv more than the tolerance.
 // tensor memory: U (16 R columns) | dW^T (128) | dk (64) | dU (80) | one P tile (8 R) | one W^T tile (8)
-constexpr int BKV_SMEM = XA_BYTES + X_BYTES + SLAB_S_BYTES + 3 * ST_BYTES + 2 * SLAB_S_BYTES;
+constexpr int BKV_SMEM = XA_BYTES + X_BYTES + SLAB_S_BYTES + 3 * ST_BYTES + 2 * STLO_BYTES + 2 * SLAB_S_BYTES;
 static_assert(RM * KT + CT + HD + EP + P_COLS + KT / 2 <= 512, "tensor-memory columns of the key/value-side kernel");
-static_assert(2 * STAGE_OUT_FLOATS * 4 <= XA_BYTES + X_BYTES + SLAB_S_BYTES + 3 * ST_BYTES, "staging tiles");
+static_assert(2 * STAGE_OUT_FLOATS * 4 <= XA_BYTES + X_BYTES + 2 * SLAB_S_BYTES + 3 * ST_BYTES, "staging tiles");
 
 __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
@@ -315,7 +318,8 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
   unsigned char* Ghi = Qimg + X_BYTES;
   unsigned char* Glo = Ghi + SLAB_S_BYTES;                // dead once dW is complete
   unsigned char* St = Glo + SLAB_S_BYTES;                 // 3 x ST_BYTES: stacked scaled query tiles
-  unsigned char* Uimg = St + 3 * ST_BYTES;                // dead once dW is complete
+  unsigned char* Lo = St + 3 * ST_BYTES;                  // 2 x STLO_BYTES
+  unsigned char* Uimg = Lo + 2 * STLO_BYTES;              // dead once dW is complete
   __shared__ HeadFactorS hf;
   __shared__ uint64_t gfull, dw_done, u_done, u_free, p_ready, p_done, st_ready[3];
   __shared__ uint32_t tmem_base;
@@ -349,7 +353,8 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
   const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
   const int rank = hf.rank, rpos = hf.rpos;
   for (int s = 0; s < 3; ++s) init_stack_constants(St + s * ST_BYTES, hf, tid, CTHREADS);
-  if (tid < CTHREADS && (tid >> 7) < tiles) build_stack_piece(St + (tid >> 7) * ST_BYTES, Qimg, (tid >> 7) * KT, hf, tid & 127);
+  if ((tid >> 7) < tiles)
+    build_stack_piece(St + (tid >> 7) * ST_BYTES, Qimg, (tid >> 7) * KT, hf, tid & 127, Lo + (tid >> 7) * STLO_BYTES);
   fence_async_smem();
   fence_before_sync();
   __syncthreads();
@@ -358,7 +363,7 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
   const uint32_t tU = tmem_base, tW = tmem_base + RM * KT, tK = tW + CT, tV = tK + HD, tP = tV + EP, tWt = tP + P_COLS;
   const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
 
-  const uint32_t k_addr = smem_u32(Ka), st_addr = smem_u32(St), g_addr = smem_u32(Ghi);
+  const uint32_t k_addr = smem_u32(Ka), st_addr = smem_u32(St), g_addr = smem_u32(Ghi), lo_addr = smem_u32(Lo);
   const uint32_t idesc_du = instr_desc_bf16(128, EP, 0, 1);
   if (issuer) {
     if (lane == 0) {
@@ -367,7 +372,7 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
       // dW^T[j, i] = [v|1]_j . g_i: rows from the U image, columns from the hi and lo images of G
       issue_dw(tW, smem_u32(Uimg), false, g_addr, true);
       mma_commit(&dw_done);
-      issue_stack_scores(tU, k_addr, st_addr, rank);
+      issue_stack_scores(tU, k_addr, st_addr, rank, lo_addr);
       mma_commit(&u_done);
     }
     __syncwarp();
@@ -393,7 +398,7 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
         w.wait(&u_free, qt & 1, 0x31);
         if (qt + 1 >= 2) w.wait(&st_ready[(qt + 1) % 3], ((qt - 1) / 3) & 1, 0x32);
         fence_after_sync();
-        issue_stack_scores(tU, k_addr, st_addr + ((qt + 1) % 3) * ST_BYTES, rank);
+        issue_stack_scores(tU, k_addr, st_addr + ((qt + 1) % 3) * ST_BYTES, rank, lo_addr + ((qt + 1) & 1) * STLO_BYTES);
         mma_commit(&u_done);
       }
       __syncwarp();
@@ -448,7 +453,8 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
     warp_arrive(&p_ready, lane);
     // stack of tile qt + 2 into the slot whose last reader was the dk MMA of tile qt - 1 (complete: see above)
     if (qt + 2 < tiles) {
-      if (half == (qt & 1)) build_stack_piece(St + ((qt + 2) % 3) * ST_BYTES, Qimg, (qt + 2) * KT, hf, tid & 127);
+      if (half == (qt & 1))
+        build_stack_piece(St + ((qt + 2) % 3) * ST_BYTES, Qimg, (qt + 2) * KT, hf, tid & 127, Lo + (qt & 1) * STLO_BYTES);
       fence_async_smem();
       warp_arrive(&st_ready[(qt + 2) % 3], lane);
     }

@@ -57,14 +57,16 @@ cudaError_t build_coef_table(const int32_t* dim_perm, const int32_t* group_start
                              cudaStream_t st);
 cudaError_t state_update(const void* k, const void* v, float* ds, int units, int N, int NB, int32_t* status,
                          cudaStream_t st);
-cudaError_t state_scan(const float* ds, void* image, const float* state_in, float* state_total, int units,
-                       int NB, int reverse, cudaStream_t st);
+// image_lo: optional second image holding bf16(state - bf16(state))
+cudaError_t state_scan(const float* ds, void* image, void* image_lo, const float* state_in, float* state_total,
+                       int units, int NB, int reverse, cudaStream_t st);
 cudaError_t cross_read(bool query, const void* x, const void* image, const float* coef_table, float* out64,
                        float* out1, int B, int H, int rep, int N, int NB, int32_t* status, cudaStream_t st);
 
 
 // ---- tensor-core backward kernels (oal_state_bwd.cu) ----------------------------------
-cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img, const float* coef_table,
+// carry_img / carry_lo: the saved state image and its remainder image (both or neither)
+cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img, const void* carry_lo, const float* coef_table,
                          float* dcarry, float* dcoef_partial, int B, int Hq, int Hkv, int N, int NB, float scale,
                          int32_t* status, cudaStream_t st);
 cudaError_t feature_grad(bool query, const void* x, const void* gimg, const void* v, const void* image,

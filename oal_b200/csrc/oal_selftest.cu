@@ -105,8 +105,33 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
   if (warp == 0) tmem_dealloc(tmem_base, 512);
 }
 
+// One warp waits on an mbarrier that nothing ever arrives on, with a short limit: the wait gives up,
+// the kernel records the status word exactly as the production kernels do (timeout flag + site id)
+// and returns normally.  Nothing hangs, traps or faults; the context stays usable.
+constexpr int SELFTEST_WAIT_SITE = 0x7E;
+__global__ void __launch_bounds__(32) wait_timeout_selftest_kernel(long long limit_clocks, int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int dead;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    dead = 0;
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) {
+    if (!mbar_wait(&bar, 0, limit_clocks)) dead = SELFTEST_WAIT_SITE;
+    if (dead) atomicOr(status, OAL_STATUS_WAIT_TIMEOUT | ((dead & 0xFF) << 8));
+  }
+}
+
 }  // namespace
 }  // namespace oal
+
+extern "C" int oal_selftest_wait_timeout(int64_t limit_clocks, int32_t* status, void* stream) {
+  if (!status || limit_clocks < 1 || limit_clocks > 1000000) return OAL_ERR_ARGUMENT;
+  oal::wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>((long long)limit_clocks, status);
+  return cudaGetLastError() == cudaSuccess ? OAL_OK : OAL_ERR_CUDA;
+}
 
 extern "C" int oal_selftest_umma(int mode, int n, int k, const void* a, const void* b, float* d,
                                  int32_t* status, void* stream) {

@@ -148,9 +148,11 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) state_update_kernel(const Stat
 // result stored as the bf16 MMA operand image  [u][c][slab][e/8][128 rows][8 e].
 //   thread = (feature row f, e chunk): grid (F_ROWS*10/256, units)
 // ---------------------------------------------------------------------------
+// image_lo (optional): a second image of the rounding remainders, bf16(state - bf16(state)); the
+// coefficient-gradient dot products of the backward read state = image + image_lo.
 __global__ void __launch_bounds__(256) state_scan_kernel(const float* ds, __nv_bfloat16* image,
-                                                         const float* state_in, float* state_total, int NB,
-                                                         int reverse) {
+                                                         __nv_bfloat16* image_lo, const float* state_in,
+                                                         float* state_total, int NB, int reverse) {
   const int x = blockIdx.x * 256 + threadIdx.x;     // 0 .. F_ROWS*10
   const int u = blockIdx.y;
   if (x >= F_ROWS * (EP / 8)) return;
@@ -174,7 +176,15 @@ __global__ void __launch_bounds__(256) state_scan_kernel(const float* ds, __nv_b
     if (image) {
       uint4 o = make_uint4(pack_bf16(run[0], run[1]), pack_bf16(run[2], run[3]), pack_bf16(run[4], run[5]),
                            pack_bf16(run[6], run[7]));
-      reinterpret_cast<uint4*>(image)[((((size_t)u * NB + c) * F_SLABS + slab) * (EP / 8) + ec) * 128 + fr] = o;
+      const size_t at = ((((size_t)u * NB + c) * F_SLABS + slab) * (EP / 8) + ec) * 128 + fr;
+      reinterpret_cast<uint4*>(image)[at] = o;
+      if (image_lo) {
+        const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+        uint32_t l[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) l[k] = pack_bf16(run[2 * k] - bf16_lo(w[k]), run[2 * k + 1] - bf16_hi(w[k]));
+        reinterpret_cast<uint4*>(image_lo)[at] = make_uint4(l[0], l[1], l[2], l[3]);
+      }
     }
     run[0] += a0.x; run[1] += a0.y; run[2] += a0.z; run[3] += a0.w;
     run[4] += a1.x; run[5] += a1.y; run[6] += a1.z; run[7] += a1.w;
@@ -410,10 +420,10 @@ cudaError_t state_update(const void* k, const void* v, float* ds, int units, int
   return cudaGetLastError();
 }
 
-cudaError_t state_scan(const float* ds, void* image, const float* state_in, float* state_total, int units,
-                       int NB, int reverse, cudaStream_t st) {
+cudaError_t state_scan(const float* ds, void* image, void* image_lo, const float* state_in, float* state_total,
+                       int units, int NB, int reverse, cudaStream_t st) {
   state_scan_kernel<<<dim3((F_ROWS * (EP / 8) + 255) / 256, units), 256, 0, st>>>(
-      ds, static_cast<__nv_bfloat16*>(image), state_in, state_total, NB, reverse);
+      ds, static_cast<__nv_bfloat16*>(image), static_cast<__nv_bfloat16*>(image_lo), state_in, state_total, NB, reverse);
   return cudaGetLastError();
 }
 

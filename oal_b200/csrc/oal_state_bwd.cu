@@ -35,7 +35,9 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4 t, float (&o)[8]) {
 struct DStateArgs {
   const __nv_bfloat16* q;          // [B,Hq,N,64]
   const __nv_bfloat16* gimg;       // [B*Hq, NB, 10, 128, 8]
-  const __nv_bfloat16* carry_img;  // [units, NB, 17, 10, 128, 8] or null (no coefficient gradients)
+  const __nv_bfloat16* carry_img;  // [units, NB, 19, 10, 128, 8] or null (no coefficient gradients)
+  const __nv_bfloat16* carry_lo;   // same layout: bf16(state - bf16(state)); the dot products below see hi + lo,
+                                   // because they are sums of strongly cancelling terms
   const float* coef_table;         // [Hq, F_ROWS]
   float* dcarry;                   // [units, NB] chunks of F_ROWS x EP floats in state_inc_offset order
   float* dcoef_partial;            // [B, NB, 2 column halves, Hq, F_ROWS] or null
@@ -164,9 +166,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
     const int fr = 32 * (warp & 3) + lane, ch = (warp - DS_GEN_WARPS) >> 2, col0 = ch * DS_COLS;
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
     float acc[DS_COLS];            // this thread's part of the dCarry row, summed over the heads of the item
-    uint4 cpk[DS_COLS / 8];
+    uint4 cpk[DS_COLS / 8], cpl[DS_COLS / 8];
 #pragma unroll
-    for (int e = 0; e < DS_COLS / 8; ++e) cpk[e] = make_uint4(0u, 0u, 0u, 0u);
+    for (int e = 0; e < DS_COLS / 8; ++e) cpk[e] = cpl[e] = make_uint4(0u, 0u, 0u, 0u);
     DsCursor d, dn;
     d.start(a.NB, a.Hkv, rep);
     dn = d;
@@ -182,8 +184,13 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
       if (d.hh == 0 && a.carry_img) {
         const uint4* cp = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(a.carry_img) +
                                                          (((size_t)d.u * a.NB + d.c) * F_SLABS + d.slab) * SLAB_S_BYTES);
+        const uint4* cl = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(a.carry_lo) +
+                                                         (((size_t)d.u * a.NB + d.c) * F_SLABS + d.slab) * SLAB_S_BYTES);
 #pragma unroll
-        for (int e = 0; e < DS_COLS / 8; ++e) cpk[e] = cp[(col0 / 8 + e) * 128 + fr];
+        for (int e = 0; e < DS_COLS / 8; ++e) {
+          cpk[e] = cp[(col0 / 8 + e) * 128 + fr];
+          cpl[e] = cl[(col0 / 8 + e) * 128 + fr];
+        }
       }
       w.wait(&mma_done[s], use & 1, 0x32);
       fence_after_sync();
@@ -200,11 +207,12 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
       for (int r = 0; r < DS_COLS / 8; ++r) {
         tmem_ld_wait();
         if (r + 1 < DS_COLS / 8) tmem_ld8(tz + lane_off + 8 * (r + 1), z[(r + 1) & 1]);
-        float c0[8];
+        float c0[8], c1[8];
         unpack_bf16x8(cpk[r], c0);
+        unpack_bf16x8(cpl[r], c1);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          dot[j & 3] = fmaf(z[r & 1][j], c0[j], dot[j & 3]);
+          dot[j & 3] = fmaf(z[r & 1][j], c0[j] + c1[j], dot[j & 3]);
           acc[8 * r + j] = fmaf(cf, z[r & 1][j], acc[8 * r + j]);
         }
       }
@@ -723,7 +731,7 @@ __global__ void __launch_bounds__(256) norm_vjp_image_kernel(const void* grad_ou
 
 }  // namespace
 
-cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img, const float* coef_table,
+cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img, const void* carry_lo, const float* coef_table,
                          float* dcarry, float* dcoef_partial, int B, int Hq, int Hkv, int N, int NB, float scale,
                          int32_t* status, cudaStream_t st) {
   const int smem = DS_RING * SLAB_A_BYTES + DS_GRING * SLAB_S_BYTES;
@@ -734,7 +742,8 @@ cudaError_t dstate_heads(const void* q, const void* gimg, const void* carry_img,
   if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
   const int items = F_SLABS * NB * B * Hkv;
   DStateArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(gimg),
-               static_cast<const __nv_bfloat16*>(carry_img), coef_table, dcarry, dcoef_partial, N, NB, Hq, Hkv,
+               static_cast<const __nv_bfloat16*>(carry_img), static_cast<const __nv_bfloat16*>(carry_lo), coef_table,
+               dcarry, dcoef_partial, N, NB, Hq, Hkv,
                B * Hkv, scale, status};
   dstate_heads_kernel<<<items < sms ? items : sms, DS_THREADS, smem, st>>>(a);
   return cudaGetLastError();

@@ -186,7 +186,8 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // Wait for the phase with the given parity.  The wait is bounded (about 25 ms of
 // SM clocks, far longer than any kernel of this library runs): on expiry it returns false and the caller records
 // OAL_STATUS_WAIT_TIMEOUT and leaves its loops; it never spins forever.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+constexpr long long MBAR_WAIT_LIMIT_CLOCKS = 50000000LL;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit = MBAR_WAIT_LIMIT_CLOCKS) {
   const uint32_t addr = smem_u32(bar);
   long long t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
@@ -209,7 +210,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if ((spin & 15) == 0) {
       const long long now = clock64();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > 50000000LL) return false;
+      else if (now - t0 > limit) return false;
     }
   }
 }

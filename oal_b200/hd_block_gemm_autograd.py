@@ -15,6 +15,8 @@ the adapters, as in the reference (hd_block_gemm_adapters.py:278-301).
 from __future__ import annotations
 
 import ctypes
+import itertools
+import threading
 from dataclasses import dataclass
 from typing import Any
 
@@ -74,13 +76,13 @@ def _pad_last(t: torch.Tensor) -> torch.Tensor:
     return t if d == _lib.HEAD_DIM else F.pad(t, (0, _lib.HEAD_DIM - d)).contiguous()
 
 
-def _raise_for_bits(bits: int) -> None:
+def _raise_for_bits(bits: int, where: str = "") -> None:
     if bits & _lib.STATUS_WAIT_TIMEOUT:
-        raise RuntimeError(f"oal_b200 kernel gave up on a bounded wait (device status word {bits:#x})")
+        raise RuntimeError(f"oal_b200 kernel gave up on a bounded wait (device status word {bits:#x}){where}")
     if bits & _lib.STATUS_BAD_LAYOUT:
-        raise ValueError("problem.padded_slabs is smaller than a head's padded group layout")
+        raise ValueError(f"a head's group layout does not fit the kernels{where}")
     if bits & (_lib.STATUS_NONFINITE | _lib.STATUS_DENOMINATOR):
-        raise RuntimeError(f"{_DENOMINATOR_ERROR} (device status {bits})")
+        raise RuntimeError(f"{_DENOMINATOR_ERROR} (device status {bits}){where}")
 
 
 def raise_on_status(status: torch.Tensor) -> None:
@@ -93,39 +95,80 @@ def raise_on_status(status: torch.Tensor) -> None:
 # assertion can poison a CUDA context ... until a safe asynchronous status mechanism is available"
 # (hd_block_gemm_runtime.py:395-398).  The status word is that mechanism: when autograd will run a
 # backward anyway, the forward only queues an asynchronous copy of its status word to pinned host
-# memory; it is examined (without blocking unless asked) when the backward starts, at the next call
-# of the operator, or by ``check_pending_status(block=True)``.  Forward-only calls stay eager.
-_PENDING: list = []
+# memory and hands the (host word, event) pair to the caller.  The backward of the same call examines
+# exactly that pair before it launches anything (waiting for the event only if the forward has not
+# finished yet, which is rare: the host runs ahead of the GPU by less than a layer), so an error is
+# raised inside the step that produced it and names its call.  Pairs nobody claimed (forward-only use
+# under autograd, the backward's own status word) stay on a per-device list that is drained without
+# blocking at every entry and completely by ``check_pending_status(block=True)``.
+_PENDING: dict = {}
+_PENDING_LOCK = threading.Lock()
+_CALL_IDS = itertools.count(1)
 
 
-def defer_status(status: torch.Tensor) -> None:
+@dataclass
+class PendingStatus:
+    host: torch.Tensor
+    event: torch.cuda.Event
+    call_id: int
+    what: str
+    done: bool = False
+
+    def check(self, block: bool) -> bool:
+        """Raise if the word reports a problem; returns False when it is not yet known (non-blocking)."""
+        if self.done:
+            return True
+        if not self.event.query():
+            if not block:
+                return False
+            self.event.synchronize()
+        self.done = True
+        _raise_for_bits(int(self.host[0]), f" [{self.what}, call {self.call_id}]")
+        return True
+
+
+def defer_status(status: torch.Tensor, what: str = "forward") -> PendingStatus:
     host = torch.empty(1, dtype=torch.int32, pin_memory=True)
     host.copy_(status, non_blocking=True)
     event = torch.cuda.Event()
     event.record(torch.cuda.current_stream(status.device))
-    _PENDING.append((host, event))
+    entry = PendingStatus(host, event, next(_CALL_IDS), what)
+    with _PENDING_LOCK:
+        _PENDING.setdefault(status.device.index, []).append(entry)
+    return entry
 
 
-def check_pending_status(block: bool = False) -> None:
-    """Raise for any finished call whose device status word reported a problem."""
-    while _PENDING:
-        host, event = _PENDING[0]
-        if not block and not event.query():
-            return
-        if block:
-            event.synchronize()
-        _PENDING.pop(0)
-        _raise_for_bits(int(host[0]))
+def check_pending_status(block: bool = False, device=None) -> None:
+    """Raise for any finished call whose device status word reported a problem.
+
+    ``device``: a torch device / index, or None for every device.  With ``block`` the queues are
+    drained completely (call it before an optimizer step when a forward ran without its backward)."""
+    with _PENDING_LOCK:
+        keys = list(_PENDING) if device is None else [torch.device(device).index if not isinstance(device, int) else device]
+    for key in keys:
+        while True:
+            with _PENDING_LOCK:
+                queue = _PENDING.get(key) or []
+                entry = queue[0] if queue else None
+            if entry is None:
+                break
+            if not entry.done and not block and not entry.event.query():
+                break
+            with _PENDING_LOCK:
+                if queue and queue[0] is entry:
+                    queue.pop(0)
+            entry.check(block=True)
 
 
 def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: float,
                  plan: HDParallelBlockPlan, *, state_in=None, check=True):
     """Launch the forward kernels.  Returns (out, num, den[B,Hq,N,1], saved_state, padded q,k,v).
 
-    ``check``: True = synchronise and raise on the status word now; "defer" = queue it."""
+    ``check``: True = synchronise and raise on the status word now; "defer" = queue it (the queued
+    entry is left in ``forward_impl.last_pending`` for the caller that owns the backward)."""
     if q.device.type != "cuda":
         raise RuntimeError("oal_b200 runs on CUDA tensors only (there is no CPU path)")
-    check_pending_status()
+    check_pending_status(device=q.device)
     lib = _lib.load()
     B, Hq, Hkv, N, D, Dv = plan.geometry
     qp, kp, vp = _pad_last(q), _pad_last(k), _pad_last(v)
@@ -143,14 +186,16 @@ def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: flo
     saved = (torch.empty(plan.saved_state_bytes, dtype=torch.uint8, device=dev)
              if plan.saved_state_bytes else None)
     a32, b32, c32 = (t.detach().to(torch.float32).contiguous() for t in (a, b, c))
-    rc = lib.oal_forward(ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(kp), _lib.ptr(vp),
-                         _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start), _lib.ptr(a32),
-                         _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(out), _lib.ptr(num), _lib.ptr(den),
-                         _lib.ptr(saved), _lib.ptr(state_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status),
-                         _stream_ptr(dev))
+    with _lib.device_guard(qp):
+        rc = lib.oal_forward(ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(kp), _lib.ptr(vp),
+                             _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start), _lib.ptr(a32),
+                             _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(out), _lib.ptr(num), _lib.ptr(den),
+                             _lib.ptr(saved), _lib.ptr(state_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status),
+                             _stream_ptr(dev))
     _lib.check(rc)
+    forward_impl.last_pending = None
     if check == "defer":
-        defer_status(status)
+        forward_impl.last_pending = defer_status(status, "forward")
     elif check:
         raise_on_status(status)
     if Dv != _lib.HEAD_DIM:
@@ -160,25 +205,11 @@ def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: flo
     return out, num, den.view(B, Hq, N, 1), saved, (qp, kp, vp, a32, b32, c32)
 
 
-def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scale, floor,
-                  plan: HDParallelBlockPlan, mask, grad_out, grad_num, grad_den, *, dstate_in=None,
-                  workspace=None, reuse_state_stage=False):
-    """Launch the backward kernels; returns (dq, dk, dv, dA, dB, dC) with None where not requested.
-
-    ``workspace`` / ``reuse_state_stage``: sequence parallelism passes the workspace that
-    ``oal_backward_local_state`` has just filled so that stage is not computed twice."""
-    lib = _lib.load()
-    check_pending_status()
-    qp, kp, vp, a32, b32, c32 = saved_inputs
-    B, Hq, Hkv, N, D, Dv = plan.geometry
-    dev = qp.device
+def backward_operands(plan: HDParallelBlockPlan, num, den, grad_out, grad_num, grad_den):
+    """Kernel-side dtype of out and the padded, contiguous (num, den, grad_out, grad_num, grad_den)
+    the backward entry points read: every [.., Dv] tensor is zero-padded to 64 columns."""
     out_dtype = getattr(torch, plan.output_dtype)
     kernel_out = out_dtype if out_dtype != torch.float64 else torch.float32
-    bits = _grad_bits(mask)
-    problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=qp.dtype, out_dtype=kernel_out,
-                           precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
-                           floor=float(floor),
-                           grad_mask=bits | (_lib.GRAD_REUSE_STATE_STAGE if reuse_state_stage else 0))
 
     def prep(gt, dtype, width):
         if gt is None:
@@ -188,10 +219,31 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
             gt = F.pad(gt, (0, width - gt.shape[-1]))
         return gt.contiguous()
 
-    go = prep(grad_out, kernel_out, _lib.HEAD_DIM)
-    gn = prep(grad_num, torch.float32, _lib.HEAD_DIM)
-    gd = prep(grad_den, torch.float32, 1)
-    num_p = num if num.shape[-1] == _lib.HEAD_DIM else F.pad(num, (0, _lib.HEAD_DIM - num.shape[-1])).contiguous()
+    return (kernel_out, prep(num, torch.float32, _lib.HEAD_DIM), den.contiguous(),
+            prep(grad_out, kernel_out, _lib.HEAD_DIM), prep(grad_num, torch.float32, _lib.HEAD_DIM),
+            prep(grad_den, torch.float32, 1))
+
+
+def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scale, floor,
+                  plan: HDParallelBlockPlan, mask, grad_out, grad_num, grad_den, *, dstate_in=None,
+                  workspace=None, reuse_state_stage=False, forward_status: "PendingStatus | None" = None):
+    """Launch the backward kernels; returns (dq, dk, dv, dA, dB, dC) with None where not requested.
+
+    ``workspace`` / ``reuse_state_stage``: sequence parallelism passes the workspace that
+    ``oal_backward_local_state`` has just filled so that stage is not computed twice."""
+    lib = _lib.load()
+    qp, kp, vp, a32, b32, c32 = saved_inputs
+    B, Hq, Hkv, N, D, Dv = plan.geometry
+    dev = qp.device
+    if forward_status is not None:
+        forward_status.check(block=True)       # this call's own forward: raise here, before anything launches
+    check_pending_status(device=dev)
+    kernel_out, num_p, den_c, go, gn, gd = backward_operands(plan, num, den, grad_out, grad_num, grad_den)
+    bits = _grad_bits(mask)
+    problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=qp.dtype, out_dtype=kernel_out,
+                           precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
+                           floor=float(floor),
+                           grad_mask=bits | (_lib.GRAD_REUSE_STATE_STAGE if reuse_state_stage else 0))
     G = tables.group_count
     dq = torch.empty_like(qp) if bits & _lib.GRAD_Q else None
     dk = torch.empty_like(kp) if bits & _lib.GRAD_K else None
@@ -202,15 +254,16 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     ws = workspace if workspace is not None else torch.empty(max(plan.backward_workspace_bytes, 16),
                                                              dtype=torch.uint8, device=dev)
-    rc = lib.oal_backward(ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(kp), _lib.ptr(vp),
-                          _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start), _lib.ptr(a32),
-                          _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(num_p), _lib.ptr(den.contiguous()),
-                          _lib.ptr(saved_state), _lib.ptr(go), _lib.ptr(gn), _lib.ptr(gd), _lib.ptr(dq),
-                          _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dA), _lib.ptr(dB), _lib.ptr(dC),
-                          _lib.ptr(dstate_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status), _stream_ptr(dev))
+    with _lib.device_guard(qp):
+        rc = lib.oal_backward(ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(kp), _lib.ptr(vp),
+                              _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start), _lib.ptr(a32),
+                              _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(num_p), _lib.ptr(den_c),
+                              _lib.ptr(saved_state), _lib.ptr(go), _lib.ptr(gn), _lib.ptr(gd), _lib.ptr(dq),
+                              _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dA), _lib.ptr(dB), _lib.ptr(dC),
+                              _lib.ptr(dstate_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status), _stream_ptr(dev))
     _lib.check(rc)
     if plan.precision == "bf16_tensorcore":
-        defer_status(status)         # only a bounded wait that gave up can set it here
+        defer_status(status, "backward")         # only a bounded wait that gave up can set it here
     if D != _lib.HEAD_DIM:
         dq = None if dq is None else dq[..., :D].contiguous()
         dk = None if dk is None else dk[..., :D].contiguous()
@@ -231,6 +284,7 @@ class _HDParallelBlockGemmFunction(torch.autograd.Function):
         ctx.set_materialize_grads(False)
         out, num, den, saved_state, padded = forward_impl(q, k, v, a, b, c, tables, scale, eps, plan,
                                                           check="defer" if any(mask) else True)
+        ctx.forward_status = forward_impl.last_pending
         ctx.tables, ctx.scale, ctx.eps, ctx.plan, ctx.mask = tables, float(scale), float(eps), plan, mask
         ctx.input_dtypes = tuple(t.dtype for t in (q, k, v, a, b, c))
         ctx.has_state = saved_state is not None
@@ -253,7 +307,7 @@ class _HDParallelBlockGemmFunction(torch.autograd.Function):
             return (None,) * 10
         dq, dk, dv, dA, dB, dC = backward_impl(padded, num, den, state, ctx.tables, ctx.scale, ctx.eps,
                                                ctx.plan, mask, grad_output, grad_numerator,
-                                               grad_denominator)
+                                               grad_denominator, forward_status=ctx.forward_status)
         grads = [dq, dk, dv, dA, dB, dC]
         result = []
         for requested, g, dtype in zip(mask, grads, ctx.input_dtypes):

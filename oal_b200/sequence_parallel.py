@@ -31,6 +31,8 @@ from .hd_block_gemm_autograd import (
     _pad_last,
     _stream_ptr,
     backward_impl,
+    backward_operands,
+    defer_status,
     forward_impl,
 )
 
@@ -53,18 +55,21 @@ def exclusive_prefix_over_ranks(local: torch.Tensor, group=None, *, reverse: boo
     return total
 
 
-def local_state_total(k: torch.Tensor, v: torch.Tensor, plan) -> torch.Tensor:
+def local_state_total(k: torch.Tensor, v: torch.Tensor, plan, groups: int = 1) -> torch.Tensor:
     """fp32 ``[B*Hkv, 2432, 80]``: this rank's contribution to the running state."""
     lib = _lib.load()
     B, Hq, Hkv, N, D, Dv = plan.geometry
     kp, vp = _pad_last(k), _pad_last(v)
-    problem = make_problem(plan.geometry, groups=1, io_dtype=k.dtype, out_dtype=k.dtype,
+    problem = make_problem(plan.geometry, groups=groups, io_dtype=k.dtype, out_dtype=k.dtype,
                            precision=plan.precision, chunk=plan.chunk_tokens, scale=1.0, floor=1e-38)
     total = torch.empty(B * Hkv, _lib.STATE_ROWS, _lib.E_PAD, dtype=torch.float32, device=k.device)
-    ws = torch.empty(max(plan.forward_workspace_bytes, 16), dtype=torch.uint8, device=k.device)
+    ws = torch.empty(max(_lib.workspace_bytes(problem, 0), 16), dtype=torch.uint8, device=k.device)
     status = torch.zeros(1, dtype=torch.int32, device=k.device)
-    _lib.check(lib.oal_forward_local_state(ctypes.byref(problem), _lib.ptr(kp), _lib.ptr(vp), _lib.ptr(total),
-                                           _lib.ptr(ws), ws.numel(), _lib.ptr(status), _stream_ptr(k.device)))
+    with _lib.device_guard(kp):
+        rc = lib.oal_forward_local_state(ctypes.byref(problem), _lib.ptr(kp), _lib.ptr(vp), _lib.ptr(total),
+                                         _lib.ptr(ws), ws.numel(), _lib.ptr(status), _stream_ptr(k.device))
+    _lib.check(rc)
+    defer_status(status, "forward state stage")      # a bounded wait that gave up in state_update
     return total
 
 
@@ -74,20 +79,22 @@ def local_dstate_total(saved_inputs, num, den, saved_state, tables, scale, floor
     lib = _lib.load()
     qp, kp, vp, a32, b32, c32 = saved_inputs
     B, Hq, Hkv, N, D, Dv = plan.geometry
-    out_dtype = getattr(torch, plan.output_dtype)
-    problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=qp.dtype, out_dtype=out_dtype,
+    # the same padded operands and kernel-side output dtype as the backward proper: the stage it leaves in
+    # the workspace is reused there
+    kernel_out, num_p, den_c, go, gn, gd = backward_operands(plan, num, den, grad_out, grad_num, grad_den)
+    problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=qp.dtype, out_dtype=kernel_out,
                            precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
                            floor=float(floor), grad_mask=_grad_bits(mask))
     total = torch.empty(B * Hkv, _lib.STATE_ROWS, _lib.E_PAD, dtype=torch.float32, device=qp.device)
     status = torch.zeros(1, dtype=torch.int32, device=qp.device)
-    go = None if grad_out is None else grad_out.to(out_dtype).contiguous()
-    gn = None if grad_num is None else grad_num.float().contiguous()
-    gd = None if grad_den is None else grad_den.float().contiguous()
-    _lib.check(lib.oal_backward_local_state(
-        ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start),
-        _lib.ptr(a32), _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(num), _lib.ptr(den.contiguous()),
-        _lib.ptr(saved_state), _lib.ptr(go), _lib.ptr(gn), _lib.ptr(gd), _lib.ptr(total), _lib.ptr(workspace),
-        workspace.numel(), _lib.ptr(status), _stream_ptr(qp.device)))
+    with _lib.device_guard(qp):
+        rc = lib.oal_backward_local_state(
+            ctypes.byref(problem), _lib.ptr(qp), _lib.ptr(tables.dim_perm), _lib.ptr(tables.group_start),
+            _lib.ptr(a32), _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(num_p), _lib.ptr(den_c),
+            _lib.ptr(saved_state), _lib.ptr(go), _lib.ptr(gn), _lib.ptr(gd), _lib.ptr(total), _lib.ptr(workspace),
+            workspace.numel(), _lib.ptr(status), _stream_ptr(qp.device))
+    _lib.check(rc)
+    defer_status(status, "backward state stage")     # a bounded wait that gave up in dstate_heads
     return total
 
 
@@ -97,10 +104,11 @@ class _SequenceParallelFunction(torch.autograd.Function):
         plan = prepared.plan
         mask = tuple(bool(x) for x in ctx.needs_input_grad[:6])
         ctx.set_materialize_grads(False)
-        state_in = exclusive_prefix_over_ranks(local_state_total(k, v, plan), group)
+        state_in = exclusive_prefix_over_ranks(local_state_total(k, v, plan, prepared.gmax), group)
         out, num, den, saved_state, padded = forward_impl(q, k, v, a, b, c, prepared.tables, prepared.scale,
                                                           prepared.normalization_floor, plan, state_in=state_in,
                                                           check="defer" if any(mask) else True)
+        ctx.forward_status = forward_impl.last_pending
         ctx.prepared, ctx.group, ctx.mask, ctx.reduce_coef = prepared, group, mask, reduce_coef
         ctx.input_dtypes = tuple(t.dtype for t in (q, k, v, a, b, c))
         if any(mask):
@@ -116,6 +124,8 @@ class _SequenceParallelFunction(torch.autograd.Function):
         prepared, plan, mask = ctx.prepared, ctx.prepared.plan, ctx.mask
         if grad_output is None and grad_numerator is None and grad_denominator is None:
             return (None,) * 9
+        if ctx.forward_status is not None:
+            ctx.forward_status.check(block=True)     # this call's own forward, before anything is launched
         ws = torch.empty(max(plan.backward_workspace_bytes, 16), dtype=torch.uint8, device=num.device)
         local = local_dstate_total(padded, num, den, state, prepared.tables, prepared.scale,
                                    prepared.normalization_floor, plan, mask, grad_output, grad_numerator,
@@ -123,7 +133,8 @@ class _SequenceParallelFunction(torch.autograd.Function):
         dstate_in = exclusive_prefix_over_ranks(local, ctx.group, reverse=True)
         grads = list(backward_impl(padded, num, den, state, prepared.tables, prepared.scale,
                                    prepared.normalization_floor, plan, mask, grad_output, grad_numerator,
-                                   grad_denominator, dstate_in=dstate_in, workspace=ws, reuse_state_stage=True))
+                                   grad_denominator, dstate_in=dstate_in, workspace=ws, reuse_state_stage=True,
+                                   forward_status=ctx.forward_status))
         if ctx.reduce_coef and dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
             for g in grads[3:]:
                 if g is not None:

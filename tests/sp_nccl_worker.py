@@ -1,5 +1,10 @@
-"""torchrun worker of the NCCL sequence-parallel test: every rank scans its half of the sequence,
-rank results are compared with one single-GPU call over the whole sequence."""
+"""torchrun worker of the NCCL sequence-parallel test: every rank scans its share of the sequence;
+rank results are compared with one single-GPU call over the whole sequence and, at the
+sequence-parallel configuration's own length (N = 32768, the default), with the stored rows of the
+reference's chunked fp32 path (tests/golden/long_rows.npz).
+
+    torchrun --nproc-per-node R tests/sp_nccl_worker.py [total sequence length]
+"""
 
 import os
 import sys
@@ -21,8 +26,9 @@ def main():
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=dev)
-    n = 1024 * world
-    case = synthetic.qwen_head_case(12, batch=1, n=n, hq=14, hkv=2, g=8, bf16=True)
+    n = int(sys.argv[1]) if len(sys.argv) > 1 else 32768
+    assert n % world == 0
+    case = synthetic.qwen_head_case(7, batch=1, n=n, hq=14, hkv=2, g=8, bf16=True)
     q, k, v, dout = (t.to(dev, torch.bfloat16) for t in (case.q, case.k, case.v, case.grad_out))
     groups = case.dim_groups.to(dev)
     sl = slice(rank * n // world, (rank + 1) * n // world)
@@ -40,6 +46,22 @@ def main():
                 dq=ERR(qr.grad, qf.grad[:, :, sl]), dk=ERR(kr.grad, kf.grad[:, :, sl]),
                 dv=ERR(vr.grad, vf.grad[:, :, sl]), dfactor=ERR(factor.grad, f2.grad))
     bad = {k_: e for k_, e in errs.items() if not e < 5e-3}
+    if n == 32768:
+        # the reference's own rows (every 1024th token): this rank checks the ones that fall into its range
+        import numpy as np
+
+        with np.load(Path(__file__).resolve().parent / "golden" / "long_rows.npz") as z:
+            gold = {key[3:]: torch.from_numpy(z[key].astype("float64")) for key in z.files if key.startswith("hd_")}
+            stride = int(z["row_stride"])
+        rows = slice(-(-sl.start // stride), -(-sl.stop // stride))
+        mine = dict(out=out, num=num, den=den, dq=qr.grad, dk=kr.grad, dv=vr.grad)
+        for key, t in mine.items():
+            full_scale = gold[key].abs().max().item()
+            got = t.detach().float().cpu()[:, :, (-sl.start % stride)::stride].double()
+            diff = (got - gold[key][:, :, rows]).abs().max().item() / full_scale
+            errs["ref_" + key] = diff
+            if not diff < 2e-2:
+                bad["ref_" + key] = diff
     flag = torch.tensor([len(bad)], device=dev)
     dist.all_reduce(flag)
     if rank == 0:

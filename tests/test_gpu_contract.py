@@ -179,3 +179,62 @@ def test_shared_dim_groups_remain_a_logical_broadcast():
     shared = oal_b200.oal_attention(q, k, v, groups[0].cuda(), factor)
     expanded = oal_b200.oal_attention(q, k, v, groups.cuda(), factor)
     assert torch.equal(shared, expanded)
+
+
+def test_bounded_wait_that_runs_out_reports_a_status_and_leaves_the_context_usable():
+    """A wait with a short limit on a barrier nothing arrives on: the kernel gives up, stores the timeout
+    flag with the wait site's id and returns; the host turns the word into the RuntimeError of the
+    production path, and an ordinary call right afterwards works."""
+    import ctypes
+
+    from oal_b200 import _lib
+    from oal_b200.hd_block_gemm_autograd import _raise_for_bits
+
+    lib = _lib.load()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.oal_selftest_wait_timeout(200_000, _lib.ptr(status), stream) == 0
+    torch.cuda.synchronize()
+    word = int(status.item())
+    assert word == _lib.STATUS_WAIT_TIMEOUT | (0x7E << 8)
+    with pytest.raises(RuntimeError, match="gave up on a bounded wait"):
+        _raise_for_bits(word)
+    assert lib.oal_selftest_wait_timeout(0, _lib.ptr(status), stream) == -1          # limits are validated
+    assert lib.oal_selftest_wait_timeout(10_000_000, _lib.ptr(status), stream) == -1
+    q, k, v = (t.cuda() for t in _case(batch=1))
+    out = oal_b200.oal_attention(q, k, v, _groups().cuda(), _factor().cuda())
+    want, _, _ = _oracle(*_case(batch=1), _groups(), _factor())
+    assert ERR(out, want) < 1e-5
+
+
+def test_every_library_call_runs_under_the_tensors_device(monkeypatch):
+    """The kernels launch on the current device; the wrapper makes the tensors' device current around
+    each call (the reference is plain torch code and follows its tensors)."""
+    from oal_b200 import _lib
+
+    entered = []
+    real = _lib.device_guard
+
+    def counting(t):
+        entered.append(t.device)
+        return real(t)
+
+    monkeypatch.setattr(_lib, "device_guard", counting)
+    q, k, v = (t.cuda().requires_grad_() for t in _case(batch=1))
+    out = oal_b200.oal_attention(q, k, v, _groups().cuda(), _factor().cuda())
+    out.sum().backward()
+    assert len(entered) >= 2 and all(d == q.device for d in entered)
+
+
+def test_operator_on_second_gpu_while_first_is_current():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    q0, k0, v0 = _case(batch=1)
+    with torch.cuda.device(0):
+        q, k, v = (t.to("cuda:1").requires_grad_() for t in (q0, k0, v0))
+        out = oal_b200.oal_attention(q, k, v, _groups().to("cuda:1"), _factor().to("cuda:1"))
+        out.sum().backward()
+        torch.cuda.synchronize("cuda:1")
+    want, _, _ = _oracle(q0, k0, v0, _groups(), _factor())
+    assert out.device == torch.device("cuda:1") and ERR(out, want) < 1e-5
+    assert torch.isfinite(q.grad).all()

@@ -163,24 +163,105 @@ def test_chunked_long_sequence_bf16_tensorcore():
     assert_close(res, oracle_dense(case), TOL_BF16, label="bf16 N=2048")
 
 
-@pytest.mark.parametrize("precision,tol", [("fp32_ieee", TOL_FP32), ("bf16_tensorcore", TOL_BF16)])
-def test_qwen_n4096_rows_against_reference_golden(golden, precision, tol):
+# The fp32_ieee path is compared with the fp64 dense statement at its 1e-4 bar and with the reference's own
+# chunked fp32 rows at the band in which those two references agree with each other (tests/test_oracle.py).
+TOL_FP32_VS_HD = 5e-4
+GRAD_KEYS = ["out", "num", "den", "dq", "dk", "dv", "dfactor"]
+
+
+def _check_rows(res, g, precision, *, stride, batch_rows=None, prefix="", label="", keys=None):
+    """Compare the operator's rows with the stored rows of both references: `dense_*` (fp64 dense
+    statement) and `hd_*` (the reference's chunked fp32 production path)."""
+    keys = keys or GRAD_KEYS
+    def rows(v):
+        if v.ndim != 4:
+            return v
+        v = v[:, :, ::stride]
+        return v if batch_rows is None else v[list(batch_rows)]
+
+    got = {k: rows(v) for k, v in res.items()}
+    dense = {k[len(prefix) + 6:]: v for k, v in g.items() if k.startswith(prefix + "dense_")}
+    hd = {k[len(prefix) + 3:]: v for k, v in g.items() if k.startswith(prefix + "hd_")}
+    bf16 = precision == "bf16_tensorcore"
+    worst = assert_close(got, dense, TOL_BF16 if bf16 else TOL_FP32, keys=[k for k in keys if k in dense],
+                         label=f"{label} {precision} vs dense")
+    worst_hd = assert_close(got, hd, TOL_BF16 if bf16 else TOL_FP32_VS_HD, keys=keys,
+                            label=f"{label} {precision} vs reference chunked path")
+    return worst, worst_hd
+
+
+@pytest.mark.parametrize("precision", ["fp32_ieee", "bf16_tensorcore"])
+def test_qwen_n4096_rows_against_reference_golden(golden, precision):
     """Full headline sequence length for one KV head and its 7 query heads; the golden file keeps
     every 64th token of the fp64 dense statement and of the reference's chunked fp32 path."""
     g = golden("qwen_n4096_rows")
-    stride = int(g["row_stride"])
     case = synthetic.qwen_head_case(1, batch=1, n=4096, hq=7, hkv=1, g=8, bf16=True)
     assert synthetic.tensor_digest(case.q, case.k, case.v, case.dim_groups) == g["input_digest"]
     io = torch.bfloat16 if precision == "bf16_tensorcore" else torch.float32
     res = run_operator(case, precision=precision, io_dtype=io)
-    rows = {k: (v[:, :, ::stride] if v.ndim == 4 else v) for k, v in res.items()}
-    ref = {k[len("dense_"):]: v for k, v in g.items() if k.startswith("dense_")}
-    from oracle import oal_oracle as orc
+    g = dict(g)
     factor = case.factor.double().clone().requires_grad_()
     fa, fb, fc = orc.expand_factor(factor, 7, case.kernel_eps)
-    ((fa * ref["dA"]).sum() + (fb * ref["dB"]).sum() + (fc * ref["dC"]).sum()).backward()
-    ref["dfactor"] = factor.grad
-    assert_close(rows, ref, tol, keys=["out", "num", "den", "dq", "dk", "dv", "dfactor"], label=precision)
+    ((fa * g["dense_dA"]).sum() + (fb * g["dense_dB"]).sum() + (fc * g["dense_dC"]).sum()).backward()
+    g["dense_dfactor"] = factor.grad
+    _check_rows(res, g, precision, stride=int(g["row_stride"]), label="N=4096 one KV head")
+
+
+@pytest.mark.parametrize("precision", ["fp32_ieee", "bf16_tensorcore"])
+def test_benchmarked_configuration_against_reference_golden(golden, precision):
+    """The configuration the benchmark times, with the benchmark's own inputs (rank 0, first input set):
+    B=4, 14 query heads over 2 KV heads, N=4096, G=8.  Stored: every 64th token of batch rows 0 and 3 from
+    both references; dfactor over the whole batch."""
+    g = golden("config2_rows")
+    case = synthetic.qwen_head_case(0, batch=4, n=4096, hq=14, hkv=2, g=8, bf16=True)
+    assert synthetic.tensor_digest(case.q, case.k, case.v, case.dim_groups) == g["input_digest"]
+    io = torch.bfloat16 if precision == "bf16_tensorcore" else torch.float32
+    res = run_operator(case, precision=precision, io_dtype=io)
+    worst, worst_hd = _check_rows(res, g, precision, stride=int(g["row_stride"]),
+                                  batch_rows=[int(b) for b in g["batch_rows"]], label="config 2")
+    print(f"config 2 {precision}: vs dense {worst}; vs reference chunked path {worst_hd}")
+
+
+# Coefficient gradient in the sweep cells whose four x20 outlier channels share ONE group (G = 1, 4, 16; with
+# the 8-group sizes of the headline configuration they are spread over two groups).  There the weight is
+# dominated by C_00 s_0^2 with s_0 ~ 1e3, and because sum_j dW_ij w_ij = 0 for every row (the gradient of a
+# normalised output) dC_00 = sum dW s_0^2 is what is left of terms about a thousand times larger than itself:
+# in the purely intra-chunk case the exact value is 0.04 where single terms reach 1e3.  bf16 operands (features,
+# upstream gradient, state: the same operands the reference's bf16 mode rounds) cannot hold that difference to
+# 2e-2 of its own size; the test bounds the error at the size of the result itself, which still catches any
+# wrong sign, scale or missing term, and holds every other output to the stated tolerance.
+TOL_BF16_DFACTOR_ONE_OUTLIER_GROUP = 0.5
+
+
+@pytest.mark.parametrize("groups", [1, 4, 8, 16])
+def test_sweep_cells_against_reference_golden(golden, groups):
+    """One cell per group count of the N x G sweep at N=4096 (B=1, 14 / 2 heads), tensor-core mode."""
+    g = golden("sweep_rows")
+    case = synthetic.qwen_head_case(40 + groups, batch=1, n=4096, hq=14, hkv=2, g=groups, bf16=True)
+    digests = bytes(g["input_digests"]).decode()
+    slot = [1, 4, 8, 16].index(groups)
+    assert synthetic.tensor_digest(case.q, case.k, case.v, case.dim_groups) == digests[64 * slot:64 * slot + 64]
+    res = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
+    keys = GRAD_KEYS if groups == 8 else [k for k in GRAD_KEYS if k != "dfactor"]
+    worst, worst_hd = _check_rows(res, g, "bf16_tensorcore", stride=int(g["row_stride"]), prefix=f"g{groups}_",
+                                  label=f"sweep G={groups}", keys=keys)
+    err = ERR(res["dfactor"], g[f"g{groups}_dense_dfactor"])
+    assert err <= (TOL_BF16 if groups == 8 else TOL_BF16_DFACTOR_ONE_OUTLIER_GROUP), f"sweep G={groups} dfactor {err}"
+    print(f"sweep G={groups}: vs dense {worst}; vs reference chunked path {worst_hd}; dfactor {err:.2e}")
+
+
+def test_long_sequence_against_reference_golden(golden):
+    """N = 32768 (the sequence-parallel configuration, here on one GPU): every 1024th token of the
+    reference's chunked fp32 path."""
+    g = golden("long_rows")
+    case = synthetic.qwen_head_case(7, batch=1, n=32768, hq=14, hkv=2, g=8, bf16=True)
+    assert synthetic.tensor_digest(case.q, case.k, case.v, case.dim_groups) == g["input_digest"]
+    res = run_operator(case, precision="bf16_tensorcore", io_dtype=torch.bfloat16)
+    stride = int(g["row_stride"])
+    got = {k: (v[:, :, ::stride] if v.ndim == 4 else v) for k, v in res.items()}
+    hd = {k[3:]: v for k, v in g.items() if k.startswith("hd_")}
+    worst = assert_close(got, hd, TOL_BF16, keys=GRAD_KEYS, label="N=32768 vs reference chunked path")
+    print(f"N=32768: {worst}")
 
 
 def test_deferred_status_surfaces_at_backward_or_explicit_check():

@@ -49,8 +49,9 @@ def test_exclusive_prefix_without_process_group_is_zero():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("splits", [(256, 256), (128, 300, 212)])
-def test_rank_emulation_matches_single_call(splits):
+@pytest.mark.parametrize("splits,dv,g", [((256, 256), 64, 8), ((128, 300, 212), 64, 8), ((256, 200), 32, 8),
+                                         ((128, 256), 64, 16)])
+def test_rank_emulation_matches_single_call(splits, dv, g):
     """Run the ranks' kernels one after another on one GPU, passing states by hand: the
     concatenated result must equal one call over the whole sequence (both use the same chunk
     arithmetic only when the split points are chunk-aligned, so compare within tolerance)."""
@@ -62,7 +63,9 @@ def test_rank_emulation_matches_single_call(splits):
     from tests.helpers import ERR
 
     n = sum(splits)
-    case = synthetic.qwen_head_case(9, batch=1, n=n, hq=4, hkv=2, g=8, bf16=True)
+    case = synthetic.qwen_head_case(9, batch=1, n=n, hq=4, hkv=2, g=g, bf16=True,
+                                    outlier_scale=20.0 if g == 8 else 4.0)
+    case.v, case.grad_out = case.v[..., :dv].contiguous(), case.grad_out[..., :dv].contiguous()
     dev = "cuda"
     q, k, v, dout = (t.to(dev, torch.bfloat16) for t in (case.q, case.k, case.v, case.grad_out))
     groups, factor = case.dim_groups.to(dev), case.factor.to(dev).requires_grad_()
@@ -82,9 +85,9 @@ def test_rank_emulation_matches_single_call(splits):
         qr, kr, vr = (t[:, :, sl].contiguous().requires_grad_() for t in (q, k, v))
         prep = prepare_grouped_hd_block_gemm(qr, kr, vr, groups, factor, scale=case.scale,
                                              precision="bf16_tensorcore")
-        ranks.append(dict(q=qr, k=kr, v=vr, prep=prep, sl=sl, total=local_state_total(kr, vr, prep.plan)))
+        ranks.append(dict(q=qr, k=kr, v=vr, prep=prep, sl=sl, total=local_state_total(kr, vr, prep.plan, prep.gmax)))
     a, b, c = (t.detach().contiguous() for t in _expand_factor_coefficients(
-        factor, query_heads=4, gmax=8, kernel_eps=case.kernel_eps, working_dtype=torch.float32))
+        factor, query_heads=4, gmax=g, kernel_eps=case.kernel_eps, working_dtype=torch.float32))
     for r, st in enumerate(ranks):
         state_in = sum((x["total"] for x in ranks[:r]), torch.zeros_like(st["total"]))
         p = st["prep"]
@@ -117,12 +120,16 @@ def _nccl_script():
 
 
 @pytest.mark.gpu
-def test_two_gpu_nccl_sequence_parallel():
-    if torch.cuda.device_count() < 2:
+def test_nccl_sequence_parallel_at_configured_length():
+    """N = 32768 over every GPU of the box (2, 4 or 8 ranks): against the single-GPU call and against the
+    stored rows of the reference's chunked path."""
+    gpus = torch.cuda.device_count()
+    if gpus < 2:
         pytest.skip("needs two GPUs")
+    world = 8 if gpus >= 8 else (4 if gpus >= 4 else 2)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(_nccl_script())]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), str(_nccl_script()), "32768"]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "SP_OK" in res.stdout
