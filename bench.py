@@ -15,8 +15,12 @@ The one JSON line printed by rank 0 carries
              dk, dv inside the timed region
   roofline   the dominant kernel against the measured bf16 tensor peak (MEASURED_PEAKS.json)
   cpu_baseline  the CPU oracle's chunked implementation of the same path on this box's cores
+               (single-rank runs only: under torchrun the other ranks would sit in a barrier meanwhile)
+  strong     the fixed-size split: the one B=4 call of the headline configuration sharded by
+             (batch row, KV head) unit over the ranks (oal_b200.unit_sharding), same timing rules
 --impl reference times that CPU implementation alone (the reference is Python/torch CPU code for
-this path; the oracle restates it), on a bounded sample of the same workload.
+this path; the oracle restates it): every step is one forward + backward over a bounded sample of
+the workload (one batch row, cut shorter if this host is slow), timed for exactly --steps steps.
 """
 
 from __future__ import annotations
@@ -38,6 +42,9 @@ sys.path.insert(0, str(ROOT))
 WORKLOAD = dict(batch=4, hq=14, hkv=2, n=4096, g=8)
 D = 64
 METRIC = "oal_attention_fwd_bwd_tokens_per_s"
+
+
+KERNEL_CHUNK = 128      # tokens per chunk of the state scan the kernels run (the reference's default plan uses 64)
 
 
 def flop_per_token(hq: int, hkv: int, t: int = 64) -> float:
@@ -170,28 +177,50 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # CPU arm: the oracle's chunked implementation (restating the reference's production path)
 # --------------------------------------------------------------------------------------
-def cpu_reference_run(steps: int, warmup: int) -> dict:
+def host_thread_setup() -> dict:
+    """Use every core this process may run on, whatever a launcher put into the environment (torchrun
+    exports OMP_NUM_THREADS=1); returns what was found, for the JSON line."""
+    try:
+        allowed = len(os.sched_getaffinity(0))
+    except AttributeError:
+        allowed = os.cpu_count() or 1
+    info = dict(cpu_count=os.cpu_count(), affinity=allowed, omp_env=os.environ.get("OMP_NUM_THREADS"))
+    torch.set_num_threads(max(1, allowed))
+    info["threads"] = torch.get_num_threads()
+    return info
+
+
+def cpu_reference_run(steps: int, warmup: int, budget_s: float = 150.0) -> dict:
+    """`steps` timed forward + backward passes of the oracle's chunked implementation after `warmup` untimed
+    ones.  A step covers one batch row of the workload; if a probe shows that the whole run would not fit
+    `budget_s`, the row is cut to a shorter prefix (the algorithm is linear in N, tokens/s stays comparable)."""
     from oal_b200 import synthetic
     from oracle import oal_oracle as orc
 
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    sample = dict(batch=1, hq=WORKLOAD["hq"], hkv=WORKLOAD["hkv"], n=WORKLOAD["n"], g=WORKLOAD["g"])
-    case = synthetic.qwen_head_case(0, bf16=True, **sample)
-    a, b, c = orc.expand_factor(case.factor, sample["hq"], case.kernel_eps, torch.float32)
-    times = []
-    for it in range(warmup + steps):
+    host = host_thread_setup()
+    full = dict(batch=1, hq=WORKLOAD["hq"], hkv=WORKLOAD["hkv"], n=WORKLOAD["n"], g=WORKLOAD["g"])
+    case = synthetic.qwen_head_case(0, bf16=True, **full)
+    a, b, c = orc.expand_factor(case.factor, full["hq"], case.kernel_eps, torch.float32)
+
+    def one(n):
         t0 = time.perf_counter()
-        orc.chunked_forward_backward(case.q, case.k, case.v, case.dim_groups, a, b, c, scale=case.scale,
-                                     token_block=64, grad_out=case.grad_out)
-        if it >= warmup:
-            times.append(time.perf_counter() - t0)
-    tokens = sample["batch"] * sample["n"]
-    best, mean = min(times), sum(times) / len(times)
-    return dict(tokens_per_s=tokens / best, mean_s=mean, best_s=best, cores=cores,
-                threads=torch.get_num_threads(),
-                sample=f"one batch row of the workload (B=1, Hq=14, Hkv=2, N=4096, G=8), fp32, chunk 64, "
-                       f"best of {steps} after {warmup} warm-up")
+        orc.chunked_forward_backward(case.q[:, :, :n], case.k[:, :, :n], case.v[:, :, :n], case.dim_groups, a, b, c,
+                                     scale=case.scale, token_block=64, grad_out=case.grad_out[:, :, :n])
+        return time.perf_counter() - t0
+
+    one(256)                                           # first-call costs (thread pool, allocator)
+    per_token = one(512) / 512
+    n = full["n"]
+    while n > 512 and per_token * n * (steps + warmup) > budget_s:
+        n //= 2
+    for _ in range(warmup):
+        one(n)
+    times = [one(n) for _ in range(steps)]
+    mean = sum(times) / len(times)
+    return dict(tokens_per_s=n / mean, mean_s=mean, best_s=min(times), cores=host["affinity"], threads=host["threads"],
+                host=host, steps=steps, warmup=warmup,
+                sample=f"one batch row of the workload (B=1, Hq=14, Hkv=2, N={n} of 4096, G=8), fp32, chunk 64, "
+                       f"mean of {steps} steps after {warmup} warm-up")
 
 
 def cpu_config1_run() -> dict:
@@ -219,12 +248,13 @@ def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    r = cpu_reference_run(max(1, min(args.steps, 3)), max(1, min(args.warmup, 1)))
-    line = dict(metric=METRIC, value=r["tokens_per_s"], unit="tokens/s", n_gpus=args.gpus, steps=args.steps,
-                warmup=args.warmup, ms_per_step=r["best_s"] * 1e3, higher_is_better=True, scaling="weak",
+    r = cpu_reference_run(max(1, args.steps), max(0, args.warmup))
+    line = dict(metric=METRIC, value=r["tokens_per_s"], unit="tokens/s", n_gpus=args.gpus, steps=r["steps"],
+                warmup=r["warmup"], ms_per_step=r["mean_s"] * 1e3, higher_is_better=True, scaling="weak",
                 vs_baseline=None, dtype="f32", data="synthetic", impl="reference",
-                config=dict(workload="qwen2.5-0.5b attention layer shape, causal fwd+bwd, one batch row "
-                                     "(B=1, Hq=14, Hkv=2, N=4096, d=64, G=8)", l2="inputs and state larger than L2"),
+                config=dict(workload="qwen2.5-0.5b attention layer shape, causal fwd+bwd, one batch row per step "
+                                     "(B=1, Hq=14, Hkv=2, N=4096, d=64, G=8)", chunk_tokens=64,
+                            l2="inputs and state larger than L2", host=r["host"]),
                 cpu_baseline=dict(value=r["tokens_per_s"], unit="tokens/s", cores=r["threads"], kind="port",
                                   sample=r["sample"]),
                 e2e=dict(value=r["tokens_per_s"], unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
@@ -307,33 +337,56 @@ def run_gpu_arm(args) -> None:
     clock_summary = clocks.summary()
 
     # ---- end to end through the public call with host tensors: every step copies its q, k, v and upstream
-    # gradient from pinned host memory and its out, dq, dk, dv back to pinned host memory.  Copies run on
-    # their own streams so that step i+1's upload and step i-1's download overlap step i's kernels, as any
-    # input pipeline would; the timed region is wall clock from the first upload to the last download.
+    # gradient from ONE pinned host buffer with one asynchronous copy and its out, dq, dk, dv back to ONE pinned
+    # buffer with one copy (the four results are first packed on the device).  Copies run on their own streams so
+    # that step i+1's upload and step i-1's download overlap step i's kernels, as any input pipeline would; the
+    # timed region is wall clock from the first upload to the last download.
+    names = ("q", "k", "v", "dout")
+    sizes = [sets[0]["host"][n_].numel() for n_ in names]
+    shapes = [tuple(sets[0]["host"][n_].shape) for n_ in names]
+    offs = [0]
+    for z in sizes:
+        offs.append(offs[-1] + z)
+    host_in = []
+    for s_ in sets:                                     # pinned after set_device, one buffer per input set
+        buf = torch.empty(offs[-1], dtype=torch.bfloat16).pin_memory()
+        for n_, o, z in zip(names, offs, sizes):
+            buf[o:o + z].copy_(s_["host"][n_].reshape(-1))
+        host_in.append(buf)
+    out_sizes = [sizes[0], sizes[0], sizes[1], sizes[2]]            # out, dq like q; dk like k; dv like v
+    out_offs = [0]
+    for z in out_sizes:
+        out_offs.append(out_offs[-1] + z)
     copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     compute = torch.cuda.current_stream(dev)
-    dev_in = [{k_: torch.empty_like(v_, device=dev) for k_, v_ in sets[0]["host"].items()} for _ in range(2)]
-    host_out = [[torch.empty_like(sets[0]["host"][n_]).pin_memory() for n_ in ("q", "q", "k", "v")] for _ in range(2)]
+    dev_in = [torch.empty(offs[-1], dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    dev_out = [torch.empty(out_offs[-1], dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    host_out = [torch.empty(out_offs[-1], dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     in_ready = [torch.cuda.Event() for _ in range(2)]
     compute_done = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+
+    def views(buf):
+        return {n_: buf[o:o + z].view(sh) for n_, o, z, sh in zip(names, offs, sizes, shapes)}
 
     def e2e_loop(n_steps):
         for i in range(n_steps):
             slot = i % 2
             with torch.cuda.stream(copy_in):
                 copy_in.wait_event(compute_done[slot])          # the step that last read this slot is finished
-                for k_, v_ in sets[i % 2]["host"].items():
-                    dev_in[slot][k_].copy_(v_, non_blocking=True)
+                dev_in[slot].copy_(host_in[i % 2], non_blocking=True)
                 in_ready[slot].record(copy_in)
             compute.wait_event(in_ready[slot])
+            compute.wait_event(out_done[slot])                  # the download that last read dev_out[slot]
             flush.fill_(i & 0xFF)
-            results = step(dev_in[slot])
+            results = step(views(dev_in[slot]))
+            for r_, o, z in zip(results, out_offs, out_sizes):
+                dev_out[slot][o:o + z].copy_(r_.reshape(-1))
             compute_done[slot].record(compute)
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(compute_done[slot])
-                for dst, src in zip(host_out[slot], results):
-                    dst.copy_(src, non_blocking=True)
-                    src.record_stream(copy_out)
+                host_out[slot].copy_(dev_out[slot], non_blocking=True)
+                out_done[slot].record(copy_out)
         torch.cuda.synchronize()
 
     e2e_loop(2)
@@ -342,8 +395,61 @@ def run_gpu_arm(args) -> None:
     e2e_loop(args.steps)
     e2e_ms = (time.perf_counter() - t0) * 1e3
     barrier()
-    h2d = sum(t.numel() * t.element_size() for t in sets[0]["host"].values())
-    d2h = sum(t.numel() * t.element_size() for t in host_out[0])
+    h2d = host_in[0].numel() * host_in[0].element_size()
+    d2h = host_out[0].numel() * host_out[0].element_size()
+
+    # plain pinned-memory copy bandwidth of this rank's GPU: the floor of any end-to-end number
+    def copy_gbs(dst, src, reps=5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            dst.copy_(src, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        return src.numel() * src.element_size() * reps / (e0.elapsed_time(e1) * 1e-3) / 1e9
+
+    copy_bw = dict(h2d=copy_gbs(dev_in[0], host_in[0]), d2h=copy_gbs(host_out[0], dev_out[0]),
+                   bytes=h2d, note="one rank alone, 64 MiB pinned buffer, 5 back-to-back copies")
+    barrier()
+
+    # ---- fixed-size split: the ONE headline call (B=4, 8 (batch row, KV head) units) sharded over the ranks
+    from oal_b200.unit_sharding import unit_shard
+
+    strong = None
+    try:
+        shard = unit_shard(WORKLOAD["batch"], WORKLOAD["hq"], WORKLOAD["hkv"], rank, world)
+    except ValueError:
+        shard = None
+    if shard is not None and args.batch == WORKLOAD["batch"]:
+        case_s = synthetic.qwen_head_case(0, bf16=True, **WORKLOAD)      # the same inputs on every rank, cut locally
+        qs, ks, vs, ds_ = (t.to(dev, torch.bfloat16) for t in shard.take(case_s.q, case_s.k, case_s.v, case_s.grad_out))
+        factor_s = shard.factor_rows(case_s.factor).to(dev).requires_grad_()
+        prep_s = oal_b200.prepare_grouped_hd_block_gemm(qs.clone().requires_grad_(), ks.clone().requires_grad_(),
+                                                        vs.clone().requires_grad_(), groups, factor_s,
+                                                        scale=case_s.scale, kernel_eps=case_s.kernel_eps,
+                                                        precision=precision, token_block=64, feature_wave_blocks=4)
+
+        def step_s():
+            q_, k_, v_ = (t.detach().requires_grad_() for t in (qs, ks, vs))
+            factor_s.grad = None
+            out_, _, _ = oal_b200.run_prepared_grouped_hd_block_gemm(prep_s, q_, k_, v_, factor_s)
+            out_.backward(ds_)
+
+        for _ in range(max(args.warmup, 3)):
+            step_s()
+        barrier()
+        ev = []
+        for i in range(args.steps):
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step_s()
+            e1.record()
+            ev.append((e0, e1))
+        barrier()
+        strong = sum(a_.elapsed_time(b_) for a_, b_ in ev)
 
     # ---- per-kernel breakdown (separate pass with the library's event pairs switched on)
     _lib.profile_enable(True)
@@ -355,10 +461,10 @@ def run_gpu_arm(args) -> None:
     report = _lib.profile_report()
     _lib.profile_enable(False)
 
-    times = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([total_ms, e2e_ms, strong if strong is not None else -1.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = times.tolist()
+    total_ms, e2e_ms, strong_ms = times.tolist()
     tokens_per_step = w["batch"] * w["n"] * world
     value = tokens_per_step * args.steps / (total_ms * 1e-3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms * 1e-3)
@@ -390,12 +496,15 @@ def run_gpu_arm(args) -> None:
             if name in kernel_flops:
                 kernels[name]["tflops"] = round(kernel_flops[name] / (ms / max(cnt, 1) * 1e-3) / 1e12, 2)
         tc = {n_: k_ for n_, k_ in kernels.items() if n_ in kernel_flops}
-        # DRAM bytes (read + write) per launch of each kernel from the committed ncu capture of one batch
-        # row (profiles/bench_headline_bf16_tensorcore.md, section 2); traffic grows in proportion to the
-        # batch, so a launch of this workload moves batch x these bytes
-        ncu_dram_mb_per_row = {"intra_backward_q": 65.81, "intra_backward_kv": 51.17, "dstate_heads": 48.97,
-                               "feature_grad_q": 41.84, "cross_read_q": 32.48, "intra_forward": 46.08,
-                               "state_update": 2.99, "feature_grad_k": 27.09, "cross_read_k": 26.01}
+        # DRAM bytes (read + write) per launch of each kernel in an ncu capture of ONE batch row, read from the
+        # table that is kept next to the profile summaries; traffic grows in proportion to the batch
+        ncu_dram_mb_per_row = {}
+        table = ROOT / "profiles" / "ncu_dram_traffic_one_batch_row.txt"
+        if table.exists():
+            for ln in table.read_text().splitlines():
+                f_ = ln.split()
+                if len(f_) == 2 and not ln.startswith("#"):
+                    ncu_dram_mb_per_row[f_[0]] = float(f_[1])
         roofline = None
         if tc:
             # the dominant kernel by device time
@@ -406,29 +515,44 @@ def run_gpu_arm(args) -> None:
                             unit="TFLOP/s", frac=round(achieved / peaks["tflops"], 4),
                             traffic=(round(ncu_dram_mb_per_row[top] * 1e6 * w["batch"]) if top in ncu_dram_mb_per_row
                                      else None),
-                            traffic_note="bytes per launch: DRAM read + write of the kernel in the committed ncu "
-                                         "capture of one batch row, times the batch",
+                            traffic_note="bytes per launch: DRAM read + write of the kernel in an ncu capture of one "
+                                         "batch row (table under profiles/), times the batch; null without the table",
                             peak_source=peaks["source"] + " (sustained bf16)",
-                            note="algorithmic MMA FLOPs of the kernel / its mean launch time; the intra-chunk "
-                                 "kernels spend their time in the fp32 combine on the CUDA cores",
+                            note="algorithmic MMA FLOPs of the kernel (unpadded, causal half, chunk 64 as in "
+                                 "flop_per_token) / its mean launch time",
                             frac_of_burst_peak=round(achieved / peaks["tflops_burst"], 4), burst_peak=peaks["tflops_burst"],
                             best_kernel=best, best_kernel_frac=round(tc[best]["tflops"] / peaks["tflops"], 4),
                             whole_step_frac=round(value / world * fpt / 1e12 / peaks["tflops"], 4),
                             whole_step_frac_of_burst_peak=round(value / world * fpt / 1e12 / peaks["tflops_burst"], 4))
-        cpu = cpu_reference_run(2, 1) if world >= 1 and not args.no_cpu_baseline else None
+        # the CPU leg runs on single-rank runs only: under torchrun the other ranks would hold their GPUs in a
+        # barrier for as long as it takes, and the launcher's thread settings are not the host's own
+        cpu = cpu_reference_run(2, 1, budget_s=40.0) if world == 1 and not args.no_cpu_baseline else None
         line = dict(metric=METRIC, value=value, unit="tokens/s", n_gpus=world, steps=args.steps,
                     warmup=max(args.warmup, 3), ms_per_step=total_ms / args.steps, higher_is_better=True,
                     scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
                     config=dict(workload=f"qwen2.5-0.5b attention layer shape, causal fwd+bwd (B={w['batch']} per GPU, "
                                          "Hq=14, Hkv=2, N=4096, d=64, G=8, bf16 io, fp32 state)",
                                 precision=precision, parallelism=f"batch x kv-head units, {world} rank(s), no collective",
+                                chunk_tokens=KERNEL_CHUNK, flop_model_chunk_tokens=64,
                                 l2="256 MiB buffer written between timed steps", flop_per_token=fpt),
-                    e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+                    e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
+                             copies_per_step=dict(h2d=1, d2h=1), copy_gbs=copy_bw,
+                             copy_bound_tokens_per_s=tok * world / max(h2d / (copy_bw["h2d"] * 1e9), d2h / (copy_bw["d2h"] * 1e9)),
+                             note="uploads, kernels and downloads of neighbouring steps overlap; the slowest of the "
+                                  "three bounds a step"),
                     gpu_launches=int(launches), clocks=clock_summary, roofline=roofline, kernels=kernels)
+        if strong_ms > 0:
+            units = WORKLOAD["batch"] * WORKLOAD["hkv"]
+            line["strong"] = dict(tokens_per_s=WORKLOAD["batch"] * WORKLOAD["n"] * args.steps / (strong_ms * 1e-3),
+                                  ms_per_step=strong_ms / args.steps, units_per_rank=units / world,
+                                  workload="the one B=4 call sharded by (batch row, KV head) unit; coefficient "
+                                           "gradients stay per-rank partial sums")
         if cpu:
             line["cpu_baseline"] = dict(value=cpu["tokens_per_s"], unit="tokens/s", cores=cpu["threads"],
-                                        kind="port", sample=cpu["sample"])
+                                        kind="port", sample=cpu["sample"], host=cpu["host"])
             line["cpu_baseline_config1"] = cpu_config1_run()
+        elif world > 1:
+            line["cpu_baseline_note"] = "timed on single-rank runs only (see --gpus 1)"
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -95,12 +95,13 @@ def raise_on_status(status: torch.Tensor) -> None:
 # assertion can poison a CUDA context ... until a safe asynchronous status mechanism is available"
 # (hd_block_gemm_runtime.py:395-398).  The status word is that mechanism: when autograd will run a
 # backward anyway, the forward only queues an asynchronous copy of its status word to pinned host
-# memory and hands the (host word, event) pair to the caller.  The backward of the same call examines
-# exactly that pair before it launches anything (waiting for the event only if the forward has not
-# finished yet, which is rare: the host runs ahead of the GPU by less than a layer), so an error is
-# raised inside the step that produced it and names its call.  Pairs nobody claimed (forward-only use
-# under autograd, the backward's own status word) stay on a per-device list that is drained without
-# blocking at every entry and completely by ``check_pending_status(block=True)``.
+# memory and keeps the (host word, event, call id) entry.  The backward of the same call looks at exactly
+# that entry before it launches anything -- without waiting: the host normally runs ahead of the GPU, and
+# a wait here would serialise host and device in every step (measured: it costs the whole forward time
+# per step and stalls input pipelines).  An entry that is not finished yet stays on a per-device list
+# that every later entry into the library drains without blocking; ``check_pending_status(block=True)``
+# drains it completely and is the call to make before an optimizer step consumes the gradients.  Every
+# error names the call it belongs to.
 _PENDING: dict = {}
 _PENDING_LOCK = threading.Lock()
 _CALL_IDS = itertools.count(1)
@@ -236,7 +237,7 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
     B, Hq, Hkv, N, D, Dv = plan.geometry
     dev = qp.device
     if forward_status is not None:
-        forward_status.check(block=True)       # this call's own forward: raise here, before anything launches
+        forward_status.check(block=False)      # this call's own forward, if it has finished: raise before launching
     check_pending_status(device=dev)
     kernel_out, num_p, den_c, go, gn, gd = backward_operands(plan, num, den, grad_out, grad_num, grad_den)
     bits = _grad_bits(mask)
