@@ -64,9 +64,20 @@ enum {
  * (oal_attention/hd_block_gemm_adapters.py:27-43): q, k, v, A, B, C */
 enum {
   OAL_GRAD_Q = 1, OAL_GRAD_K = 2, OAL_GRAD_V = 4, OAL_GRAD_COEF = 8,
-  /* oal_backward only: the workspace still holds what oal_backward_local_state computed for this
-   * very call (same problem, same workspace, nothing launched on it in between): skip that stage */
+  /* oal_forward / oal_backward: the workspace still holds what oal_forward_local_state /
+   * oal_backward_local_state computed for this very call (same problem, same workspace, nothing
+   * launched on it in between): skip that stage (the chunk-state increments, resp. the
+   * normalisation VJP, dCarry and coefficient partial sums) */
   OAL_GRAD_REUSE_STATE_STAGE = 16
+};
+
+/* OalProblem.flags */
+enum {
+  /* `out` (oal_forward) and `grad_out` (oal_backward) are [B, N, Hq, 64] -- the layout the caller's output
+   * projection reads, replacing its transpose + contiguous copy
+   * (qwen_lora_experiment/attention/common.py:575-596) -- instead of [B, Hq, N, 64].  num and den keep the
+   * head-first layout.  bf16_tensorcore with at most 8 groups per head only. */
+  OAL_FLAG_OUT_TOKEN_MAJOR = 1
 };
 
 typedef struct OalProblem {
@@ -84,8 +95,7 @@ typedef struct OalProblem {
   int32_t grad_mask;    /* OAL_GRAD_* bits requested from oal_backward                  */
   float scale;          /* q is multiplied by this before anything else                 */
   float floor;          /* normalisation floor: out = num / max(den, floor)             */
-  int32_t padded_slabs; /* unused (earlier builds sized shared-memory images with it); kept so that the
-                           struct layout does not change: pass 0                             */
+  int32_t flags;        /* OAL_FLAG_* bits, 0 for the reference's layouts                   */
 } OalProblem;
 
 /* Bytes of workspace oal_forward (phase 0) / oal_backward (phase 1) need, and
@@ -147,8 +157,9 @@ int oal_backward(const OalProblem* problem, const void* q, const void* k, const 
  * increments, the ranks exchange these (one all-gather of batch*kv_heads*OAL_STATE_ROWS*OAL_E_PAD
  * floats), and each rank passes the sum over the ranks before it as `state_in` to oal_forward.
  * Backward mirrors it with the state gradient: oal_backward_local_state, exchange, sum over the
- * ranks after it as `dstate_in` to oal_backward (with OAL_GRAD_REUSE_STATE_STAGE when the same
- * workspace is passed to both calls back to back).
+ * ranks after it as `dstate_in` to oal_backward.  With OAL_GRAD_REUSE_STATE_STAGE in grad_mask the
+ * second call of each pair (oal_forward, oal_backward) reuses what the first left in the same workspace
+ * instead of computing it again.
  *   state_total / dstate_total: fp32 [batch*kv_heads, OAL_STATE_ROWS, OAL_E_PAD]
  *   workspace: oal_workspace_bytes(problem, 0) for the forward call, (problem, 1) for the backward.
  */
@@ -234,6 +245,16 @@ int oal_selftest_wait_timeout(int64_t limit_clocks, int32_t* status, void* strea
 int64_t oal_launch_count(void);
 void oal_profile_enable(int enable);
 int oal_profile_report(char* buffer, size_t capacity);
+
+/*
+ * Inside oal_forward / oal_backward a few kernels that the main chain does not wait for run on two
+ * streams the library owns (created on first use, per device), forked from and joined back into the
+ * caller's stream with events before the call returns: from outside every entry point is work on the one
+ * stream that was passed in.  oal_set_overlap(0) keeps everything on the caller's stream (the per-kernel
+ * times of oal_profile_report are only meaningful that way); the default is 1.  No counterpart in the
+ * reference, which runs one stream.
+ */
+void oal_set_overlap(int enable);
 
 /* Library / build identification: "oal_b200 <version> sm_100a". Host pointer. */
 const char* oal_version_string(void);

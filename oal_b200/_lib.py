@@ -22,6 +22,7 @@ PRECISION_CODES = {"fp32_ieee": 0, "bf16_tensorcore": 1}
 
 GRAD_Q, GRAD_K, GRAD_V, GRAD_COEF, GRAD_REUSE_STATE_STAGE = 1, 2, 4, 8, 16
 STATE_ROWS = 2432
+FLAG_OUT_TOKEN_MAJOR = 1
 STATUS_NONFINITE, STATUS_DENOMINATOR, STATUS_WAIT_TIMEOUT, STATUS_BAD_LAYOUT = 1, 2, 4, 8
 
 # every symbol include/oal_b200.h declares
@@ -36,6 +37,7 @@ EXPORTED_SYMBOLS = (
     "oal_launch_count",
     "oal_profile_enable",
     "oal_profile_report",
+    "oal_set_overlap",
     "oal_forward_static_scratch",
     "oal_forward_local_state",
     "oal_backward_local_state",
@@ -60,7 +62,7 @@ class OalProblem(ctypes.Structure):
         ("grad_mask", ctypes.c_int32),
         ("scale", ctypes.c_float),
         ("floor", ctypes.c_float),
-        ("padded_slabs", ctypes.c_int32),
+        ("flags", ctypes.c_int32),
     ]
 
 
@@ -107,6 +109,8 @@ def load() -> ctypes.CDLL:
     lib.oal_launch_count.restype = ctypes.c_int64
     lib.oal_profile_enable.argtypes = [ctypes.c_int]
     lib.oal_profile_enable.restype = None
+    lib.oal_set_overlap.argtypes = [ctypes.c_int]
+    lib.oal_set_overlap.restype = None
     lib.oal_profile_report.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
     lib.oal_profile_report.restype = ctypes.c_int
     lib.oal_last_error_string.restype = ctypes.c_char_p
@@ -152,6 +156,9 @@ def launch_count() -> int:
 
 
 def profile_enable(on: bool) -> None:
+    """Per-kernel event timing; while it is on, the library's side streams are off so that every kernel
+    runs alone and its time means something."""
+    load().oal_set_overlap(0 if on else 1)
     load().oal_profile_enable(1 if on else 0)
 
 

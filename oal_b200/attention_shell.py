@@ -130,6 +130,14 @@ def project_qkv_and_apply_rope(*, q_proj: nn.Module, k_proj: nn.Module, v_proj: 
     return q.contiguous(), k.contiguous(), v.contiguous()
 
 
+def project_token_major_output(*, token_output: torch.Tensor, o_proj: nn.Module, geometry: ModelGeometry = QWEN_GEOMETRY):
+    """Operator output already in ``[B, N, Hq, D]`` (``output_layout="tokens_first"``): a view and one o_proj."""
+    b, n, h, d = token_output.shape
+    if h != geometry.num_query_heads or d != geometry.head_dim:
+        raise AttentionContractError(f"token_output must be [B, N, {geometry.num_query_heads}, {geometry.head_dim}]")
+    return o_proj(token_output.reshape(b, n, geometry.hidden_size))
+
+
 def restore_and_project_output(*, head_output: torch.Tensor, o_proj: nn.Module, geometry: ModelGeometry = QWEN_GEOMETRY):
     """``[B, Hq, N, D]`` back to ``[B, N, hidden]`` and one o_proj."""
     b, h, n, d = head_output.shape
@@ -141,9 +149,11 @@ def restore_and_project_output(*, head_output: torch.Tensor, o_proj: nn.Module, 
 class PreparedCallCache:
     """Per-layer cache of prepared operator calls (qwen_lora_experiment/attention/hd_runtime.py:37-86)."""
 
-    def __init__(self, *, precision: str = "bf16_tensorcore", kernel_eps: float = 1e-6):
+    def __init__(self, *, precision: str = "bf16_tensorcore", kernel_eps: float = 1e-6,
+                 output_layout: str = "heads_first"):
         self.precision = precision
         self.kernel_eps = kernel_eps
+        self.output_layout = output_layout
         self._entries: dict[object, list] = {}
 
     def grouped(self, q, k, v, dim_groups, factor, *, cache_key):
@@ -154,7 +164,7 @@ class PreparedCallCache:
         prepared = next((p for s, p in entries if s == signature), None)
         if prepared is None:
             prepared = prepare_grouped_hd_block_gemm(q, k, v, dim_groups, factor, kernel_eps=self.kernel_eps,
-                                                     precision=self.precision)
+                                                     precision=self.precision, output_layout=self.output_layout)
             entries.append((signature, prepared))
             if len(entries) > 2:
                 del entries[0]
@@ -203,4 +213,6 @@ class OalAttentionLayer(nn.Module):
                                              hidden_states=hidden_states, position_embeddings=position_embeddings,
                                              geometry=self.geometry)
         out, _, _ = self.cache.grouped(q, k, v, self.dim_groups, self.factor, cache_key=self.layer_id)
+        if self.cache.output_layout == "tokens_first":       # the kernels wrote [B, N, Hq, D]: no restore copy
+            return project_token_major_output(token_output=out, o_proj=self.o_proj, geometry=self.geometry)
         return restore_and_project_output(head_output=out, o_proj=self.o_proj, geometry=self.geometry)

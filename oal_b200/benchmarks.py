@@ -94,13 +94,26 @@ def sequence_parallel(n: int, steps: int, warmup: int) -> None:
 
     if world > 1:
         dist.barrier()
-    ms = torch.tensor([_time_steps(step, steps, warmup)], device=dev, dtype=torch.float64)
+    from .sequence_parallel import exclusive_prefix_over_ranks
+
+    state = torch.zeros(2, _lib.STATE_ROWS, _lib.E_PAD, device=dev)          # what one rank contributes per direction
+
+    def exchange():                                                          # the two collectives of a step, alone
+        exclusive_prefix_over_ranks(state, None)
+        exclusive_prefix_over_ranks(state, None, reverse=True)
+
+    ms = torch.tensor([_time_steps(step, steps, warmup), _time_steps(exchange, steps, warmup)], device=dev,
+                      dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(json.dumps(dict(benchmark="sequence_parallel", n=n, ranks=world, ms_per_step=ms.item(),
-                              tokens_per_s=n / (ms.item() * 1e-3),
-                              exchange_bytes_per_rank_per_direction=2 * _lib.STATE_ROWS * _lib.E_PAD * 4)), flush=True)
+        step_ms, exchange_ms = ms.tolist()
+        print(json.dumps(dict(benchmark="sequence_parallel", n=n, ranks=world, ms_per_step=step_ms,
+                              tokens_per_s=n / (step_ms * 1e-3),
+                              exchange_ms_per_step=exchange_ms, exchange_share=exchange_ms / step_ms,
+                              exchange_bytes_per_rank_per_direction=2 * _lib.STATE_ROWS * _lib.E_PAD * 4,
+                              collective="one all-gather of the range-final fp32 states per direction (NCCL), "
+                                         "summed locally in rank order")), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

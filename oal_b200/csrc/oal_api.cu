@@ -60,6 +60,52 @@ struct LaunchScope {
 
 size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// ---- side streams ------------------------------------------------------------------------------
+// Small kernels that nothing on the main chain waits for (the per-head factor table of the forward, the
+// coefficient-gradient reductions, the reverse state scan and the whole key/value chain of the backward)
+// run on two library-owned streams, forked from and joined back into the caller's stream with events, so
+// every entry point still looks like work on one stream from outside (and can be captured as such).
+// Streams and events are created once per device, on first use; oal_set_overlap(0) keeps everything on
+// the caller's stream (the per-kernel timing of the profile report is only meaningful that way).
+std::atomic<int> g_overlap{1};
+struct SideStreams {
+  cudaStream_t s[2] = {nullptr, nullptr};
+  cudaEvent_t fork = nullptr, join[2] = {nullptr, nullptr};
+  bool ok = false;
+};
+std::mutex g_side_mutex;
+SideStreams g_side[64];
+
+SideStreams* side_streams() {
+  if (!g_overlap.load()) return nullptr;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_side_mutex);
+  SideStreams& x = g_side[dev];
+  if (!x.ok) {
+    bool good = cudaEventCreateWithFlags(&x.fork, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 2 && good; ++i)
+      good = cudaStreamCreateWithFlags(&x.s[i], cudaStreamNonBlocking) == cudaSuccess &&
+             cudaEventCreateWithFlags(&x.join[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!good) return nullptr;
+    x.ok = true;
+  }
+  return &x;
+}
+// side stream i starts after everything queued on `st` so far
+cudaStream_t fork_to(SideStreams* x, int i, cudaStream_t st) {
+  if (!x) return st;
+  if (cudaEventRecord(x->fork, st) != cudaSuccess || cudaStreamWaitEvent(x->s[i], x->fork, 0) != cudaSuccess) return st;
+  return x->s[i];
+}
+// mark the end of what was queued on side stream i; `st` waits for that mark in join_wait
+void join_mark(SideStreams* x, int i, cudaStream_t side, cudaStream_t st) {
+  if (x && side != st) cudaEventRecord(x->join[i], side);
+}
+void join_wait(SideStreams* x, int i, cudaStream_t side, cudaStream_t st) {
+  if (x && side != st) cudaStreamWaitEvent(st, x->join[i], 0);
+}
+
 struct Carver {
   char* base;
   size_t off = 0;
@@ -90,6 +136,10 @@ int check_problem(const OalProblem* p) {
     if (p->chunk != 128) return fail(OAL_ERR_ARGUMENT, "bf16_tensorcore requires chunk == 128");
   }
   if (!(p->floor > 0.f)) return fail(OAL_ERR_ARGUMENT, "floor must be positive");
+  if (p->flags & ~OAL_FLAG_OUT_TOKEN_MAJOR) return fail(OAL_ERR_ARGUMENT, "unknown bits in flags");
+  if ((p->flags & OAL_FLAG_OUT_TOKEN_MAJOR) &&
+      (p->precision != OAL_PRECISION_BF16_TENSORCORE || p->groups + 1 > oal::intra_coef_terms()))
+    return fail(OAL_ERR_ARGUMENT, "token-major out needs bf16_tensorcore and at most 8 groups per head");
   return OAL_OK;
 }
 
@@ -209,7 +259,8 @@ int backward_state_stage(const OalProblem* p, const void* q, const int32_t* dim_
     // the fp32 rows of g are read by the token-pair kernels only (heads with more than 8 groups)
     e = oal::norm_vjp_image(grad_out, p->out_dtype, grad_num, grad_den, num, den, p->floor,
                             tc_intra(p) ? nullptr : s.g, s.gimg,
-                            p->batch * p->q_heads, p->seq_len, nb, st); }
+                            p->batch * p->q_heads, p->seq_len, nb,
+                            (p->flags & OAL_FLAG_OUT_TOKEN_MAJOR) ? p->q_heads : 0, st); }
   if (e != cudaSuccess) return fail_cuda(e, "normalisation VJP kernel");
   { LaunchScope scope("coef_table", st);
     e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, p->scale, s.coef_table, st); }
@@ -362,11 +413,22 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
   if (!saved_state) return fail(OAL_ERR_ARGUMENT, "oal_forward: saved_state is NULL");
   const int units = p->batch * p->kv_heads, nb = chunk_count(p);
   cudaError_t e;
+  // the factor table is needed by the last kernel only: it is computed beside the state kernels
+  SideStreams* side = tc_intra(p) ? side_streams() : nullptr;
+  void* factors = saved_factors(p, saved_state);
+  cudaStream_t s0 = st;
+  if (tc_intra(p)) {
+    s0 = fork_to(side, 0, st);
+    if (int rc2 = make_head_factors(p, dim_perm, group_start, coef_a, coef_b, coef_c, factors, s0)) return rc2;
+    join_mark(side, 0, s0, st);
+  }
   { LaunchScope scope("coef_table", st);
     e = oal::build_coef_table(dim_perm, group_start, coef_a, coef_b, coef_c, p->q_heads, p->groups, p->scale, s.coef_table, st); }
   if (e != cudaSuccess) return fail_cuda(e, "coefficient table kernel");
-  { LaunchScope scope("state_update", st); e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st); }
-  if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
+  if (!(p->grad_mask & OAL_GRAD_REUSE_STATE_STAGE)) {      // else: left in this workspace by oal_forward_local_state
+    { LaunchScope scope("state_update", st); e = oal::state_update(k, v, s.ds, units, p->seq_len, nb, status, st); }
+    if (e != cudaSuccess) return fail_cuda(e, "state update kernel");
+  }
   { LaunchScope scope("state_scan", st); e = oal::state_scan(s.ds, saved_state, saved_remainders(p, saved_state), state_in, nullptr, units, nb, 0, st); }
   if (e != cudaSuccess) return fail_cuda(e, "state scan kernel");
   { LaunchScope scope("cross_read_q", st);
@@ -374,11 +436,10 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
                         p->q_heads / p->kv_heads, p->seq_len, nb, status, st); }
   if (e != cudaSuccess) return fail_cuda(e, "cross read kernel");
   if (tc_intra(p)) {
-    void* factors = saved_factors(p, saved_state);
-    if (int rc2 = make_head_factors(p, dim_perm, group_start, coef_a, coef_b, coef_c, factors, st)) return rc2;
+    join_wait(side, 0, s0, st);
     { LaunchScope scope("intra_forward", st);
       e = oal::intra_forward(q, k, v, factors, out, num, den, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
-                             p->out_dtype, p->floor, st); }
+                             p->out_dtype, p->floor, (p->flags & OAL_FLAG_OUT_TOKEN_MAJOR) != 0, st); }
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
     return OAL_OK;
   }
@@ -389,6 +450,8 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
   if (e != cudaSuccess) return fail_cuda(e, "forward pair kernel");
   return OAL_OK;
 }
+
+void oal_set_overlap(int enable) { g_overlap.store(enable ? 1 : 0); }
 
 int oal_backward(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
                  const int32_t* group_start, const float* coef_a, const float* coef_b, const float* coef_c,
@@ -454,14 +517,38 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
     if (rc) return rc;
   }
   const void* factors = saved_factors(p, saved_state);      // written by the forward of this call
-  if (want_k || want_v) {
-    { LaunchScope scope("state_scan_reverse", st);
-      e = oal::state_scan(s.dcarry, s.dt_img, nullptr, dstate_in, nullptr, units, nb, 1, st); }
-    if (e != cudaSuccess) return fail_cuda(e, "reverse state scan kernel");
-  }
+  // Three chains leave the state stage: the query side (on the caller's stream), the key/value side and
+  // the reduction of the cross-chunk coefficient gradient.  They share no buffer, so the last two run on
+  // the library's side streams and are joined before this function returns.
+  SideStreams* side = side_streams();
+  cudaStream_t skv = (want_k || want_v) ? fork_to(side, 0, st) : st;
+  cudaStream_t sc = want_c ? fork_to(side, 1, st) : st;
   oal::PairArgs a = base_args(p, q, k, v, dim_perm, group_start, coef_a, coef_b, coef_c, status);
   a.window = kChunk;
   a.g = s.g;
+  if (want_c) {
+    { LaunchScope scope("dcoef_reduce", sc, 2);
+      e = oal::dcoef_reduce(s.dcoef_partial, 2 * p->batch * nb, p->q_heads, dim_perm, group_start, s.dcoef, s.slots, sc); }
+    if (e != cudaSuccess) return fail_cuda(e, "coefficient gradient reduction kernels");
+    join_mark(side, 1, sc, st);
+  }
+  if (want_k || want_v) {
+    { LaunchScope scope("state_scan_reverse", skv);
+      e = oal::state_scan(s.dcarry, s.dt_img, nullptr, dstate_in, nullptr, units, nb, 1, skv); }
+    if (e != cudaSuccess) return fail_cuda(e, "reverse state scan kernel");
+    if (want_k) {
+      { LaunchScope scope("feature_grad_k", skv);
+        e = oal::feature_grad(false, k, nullptr, v, s.dt_img, nullptr, s.dk_cross, p->batch, p->kv_heads, 1,
+                              p->seq_len, nb, status, skv); }
+      if (e != cudaSuccess) return fail_cuda(e, "key feature gradient kernel");
+    }
+    if (want_v) {
+      { LaunchScope scope("cross_read_k", skv);
+        e = oal::cross_read(false, k, s.dt_img, nullptr, s.dv_cross, nullptr, p->batch, p->kv_heads, 1, p->seq_len,
+                            nb, status, skv); }
+      if (e != cudaSuccess) return fail_cuda(e, "key cross read kernel");
+    }
+  }
   if (want_q || want_c) {
     if (want_q) {
       { LaunchScope scope("feature_grad_q", st);
@@ -483,9 +570,7 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
       if (e != cudaSuccess) return fail_cuda(e, "backward query-side pair kernel");
     }
     if (want_c) {
-      { LaunchScope scope("dcoef_reduce", st, 2);
-        e = oal::dcoef_reduce(s.dcoef_partial, 2 * p->batch * nb, p->q_heads, dim_perm, group_start, s.dcoef, s.slots, st); }
-      if (e != cudaSuccess) return fail_cuda(e, "coefficient gradient reduction kernels");
+      join_wait(side, 1, sc, st);
       { LaunchScope scope("reduce_coefs", st);
         const int rm = oal::intra_coef_terms();
         e = tc ? oal::intra_coef_finish(s.coef_pairs, nb, rm * (rm + 1) / 2 + rm + 1, rm, factors, s.slots, p->batch,
@@ -494,25 +579,16 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
                                    p->groups, d_coef_a, d_coef_b, d_coef_c, st); }
       if (e != cudaSuccess) return fail_cuda(e, "coefficient reduction kernel");
     }
+  } else if (want_c) {
+    join_wait(side, 1, sc, st);
   }
   if (want_k || want_v) {
-    if (want_k) {
-      { LaunchScope scope("feature_grad_k", st);
-        e = oal::feature_grad(false, k, nullptr, v, s.dt_img, nullptr, s.dk_cross, p->batch, p->kv_heads, 1,
-                              p->seq_len, nb, status, st); }
-      if (e != cudaSuccess) return fail_cuda(e, "key feature gradient kernel");
-    }
-    if (want_v) {
-      { LaunchScope scope("cross_read_k", st);
-        e = oal::cross_read(false, k, s.dt_img, nullptr, s.dv_cross, nullptr, p->batch, p->kv_heads, 1, p->seq_len,
-                            nb, status, st); }
-      if (e != cudaSuccess) return fail_cuda(e, "key cross read kernel");
-    }
+    // the two intra-chunk kernels each fill the machine: the key/value one is queued after the query one
     if (tc) {
-      { LaunchScope scope("intra_backward_kv", st, 1 + (want_k ? 1 : 0) + (want_v ? 1 : 0));
+      { LaunchScope scope("intra_backward_kv", skv, 1 + (want_k ? 1 : 0) + (want_v ? 1 : 0));
         e = oal::intra_backward_kv(q, k, v, s.gimg, factors, want_k ? dk : nullptr, want_v ? dv : nullptr,
                                    want_k ? s.dk_cross : nullptr, want_v ? s.dv_cross : nullptr, s.dk_part, s.dv_part,
-                                   status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb, st); }
+                                   status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb, skv); }
       if (e != cudaSuccess) return fail_cuda(e, "intra-chunk backward key/value-side kernel");
     } else {
       a.dq = nullptr; a.dq_init = nullptr; a.coef_partial = nullptr;
@@ -520,12 +596,13 @@ int oal_backward(const OalProblem* p, const void* q, const void* k, const void* 
       a.dv = want_v ? dv : nullptr;
       a.dk_init = want_k ? s.dk_cross : nullptr;
       a.dv_init = want_v ? s.dv_cross : nullptr;
-      { LaunchScope scope("pairs_backward_kv", st); e = oal::pairs_backward_kv(a, st); }
+      { LaunchScope scope("pairs_backward_kv", skv); e = oal::pairs_backward_kv(a, skv); }
       if (e != cudaSuccess) return fail_cuda(e, "backward key/value-side pair kernel");
     }
+    join_mark(side, 0, skv, st);
+    join_wait(side, 0, skv, st);
   }
   return OAL_OK;
-
 }
 
 int oal_forward_local_state(const OalProblem* p, const void* k, const void* v, float* state_total, void* workspace,
@@ -653,7 +730,7 @@ int oal_forward_static_scratch(const OalProblem* p, const void* q, const void* k
     if (int rc2 = make_head_factors(p, dim_perm, group_start, coef_a, coef_b, coef_c, factors, st, false)) return rc2;
     { LaunchScope scope("intra_forward", st, 1, false);
       e = oal::intra_forward(q, k, v, factors, out, num, den, status, p->batch, p->q_heads, p->kv_heads, p->seq_len, nb,
-                             p->out_dtype, p->floor, st); }
+                             p->out_dtype, p->floor, (p->flags & OAL_FLAG_OUT_TOKEN_MAJOR) != 0, st); }
     if (e != cudaSuccess) return fail_cuda(e, "intra-chunk forward kernel");
     return OAL_OK;
   }

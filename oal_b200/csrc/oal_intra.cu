@@ -26,6 +26,7 @@ struct IntraFwdArgs {
   int32_t* status;
   int N, Hq, Hkv, out_dt;
   float floor;
+  int out_token_major;      // out is [B, N, Hq, 64] instead of [B, Hq, N, 64]
 };
 
 constexpr int FWD_SMEM = XA_BYTES + X_BYTES + SLAB_S_BYTES + 2 * ST_BYTES;
@@ -267,6 +268,7 @@ __global__ void __launch_bounds__(CTHREADS, 2) intra_fwd_kernel(const IntraFwdAr
       if (ii >= a.N) continue;
       const float inv = 1.f / fmaxf(den_s[r], a.floor);
       const size_t oo = (qoff + ii) * VD + seg * 8;
+      const size_t ot = a.out_token_major ? (((size_t)b * a.N + ii) * a.Hq + h) * VD + seg * 8 : oo;
       float* np = a.num + oo;
       const float* sp = stage_out + r * 65 + seg * 8;
       const float n[8] = {sp[0] + o0[it].x, sp[1] + o0[it].y, sp[2] + o0[it].z, sp[3] + o0[it].w,
@@ -278,16 +280,16 @@ __global__ void __launch_bounds__(CTHREADS, 2) intra_fwd_kernel(const IntraFwdAr
       for (int j = 0; j < 8; ++j) fin = fin && finite_f(n[j]);
       if (!fin) flags |= OAL_STATUS_NONFINITE;
       if (a.out_dt == OAL_DTYPE_BF16) {
-        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + oo) =
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + ot) =
             make_uint4(pack_bf16(n[0] * inv, n[1] * inv), pack_bf16(n[2] * inv, n[3] * inv),
                        pack_bf16(n[4] * inv, n[5] * inv), pack_bf16(n[6] * inv, n[7] * inv));
       } else if (a.out_dt == OAL_DTYPE_F32) {
-        float* op = reinterpret_cast<float*>(a.out) + oo;
+        float* op = reinterpret_cast<float*>(a.out) + ot;
         *reinterpret_cast<float4*>(op) = make_float4(n[0] * inv, n[1] * inv, n[2] * inv, n[3] * inv);
         *reinterpret_cast<float4*>(op + 4) = make_float4(n[4] * inv, n[5] * inv, n[6] * inv, n[7] * inv);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) store_elem(a.out, oo + j, a.out_dt, n[j] * inv);
+        for (int j = 0; j < 8; ++j) store_elem(a.out, ot + j, a.out_dt, n[j] * inv);
       }
     }
   }
@@ -301,12 +303,12 @@ __global__ void __launch_bounds__(CTHREADS, 2) intra_fwd_kernel(const IntraFwdAr
 
 cudaError_t OAL_INTRA_NAME(intra_forward)(const void* q, const void* k, const void* v, const void* factors, void* out,
                                           float* num, float* den, int32_t* status, int B, int Hq, int Hkv, int N, int NB,
-                                          int out_dt, float floor_v, cudaStream_t st) {
+                                          int out_dt, float floor_v, bool out_token_major, cudaStream_t st) {
   cudaError_t e = cudaFuncSetAttribute(intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
   if (e != cudaSuccess) return e;
   IntraFwdArgs a{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
                  static_cast<const __nv_bfloat16*>(v), static_cast<const HeadFactor*>(factors), out, num, den, status,
-                 N, Hq, Hkv, out_dt, floor_v};
+                 N, Hq, Hkv, out_dt, floor_v, out_token_major ? 1 : 0};
   intra_fwd_kernel<<<dim3(NB, Hq, B), CTHREADS, FWD_SMEM, st>>>(a);
   return cudaGetLastError();
 }

@@ -165,6 +165,17 @@ __device__ __forceinline__ void build_stack_piece(unsigned char* st, const unsig
   }
 }
 
+// 32 lanes x 32-bit, 4 consecutive columns per thread.
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
+  uint32_t r[4];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(taddr)
+               : "memory");
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // One arrival per warp on an mbarrier after every lane has finished what precedes (shared-memory
 // stores made visible to the async proxy, or tensor-memory loads).
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {

@@ -302,6 +302,7 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_q_kernel(const IntraBwd
 // ---------------------------------------------------------------------------
 // key / value side: one CTA per (chunk, query head, batch row); rows are keys
 // ---------------------------------------------------------------------------
+constexpr int KV_WARPS = 16, KV_THREADS = KV_WARPS * 32;   // 128 key rows x 4 quarters of a 16-query tile
 // shared memory: Ka | Qimg | G hi | G lo | 3 stacks | 2 remainder stacks | U   (G lo and U are dead once dW
 // is complete).  The stack is carried as value + remainder here too: its rounding acts like a perturbation
 // of the query rows that is the same for every key, and with large cancelling dimensions that alone costs
@@ -311,7 +312,7 @@ constexpr int BKV_SMEM = XA_BYTES + X_BYTES + SLAB_S_BYTES + 3 * ST_BYTES + 2 * 
 static_assert(RM * KT + CT + HD + EP + P_COLS + KT / 2 <= 512, "tensor-memory columns of the key/value-side kernel");
 static_assert(2 * STAGE_OUT_FLOATS * 4 <= XA_BYTES + X_BYTES + 2 * SLAB_S_BYTES + 3 * ST_BYTES, "staging tiles");
 
-__global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBwdArgs a) {
+__global__ void __launch_bounds__(KV_THREADS, 1) intra_bwd_kv_kernel(const IntraBwdArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* Ka = smem;                               // augmented k image (rows are keys)
   unsigned char* Qimg = Ka + XA_BYTES;
@@ -327,33 +328,33 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (a.Hq / a.Hkv);
-  const int half = (warp >> 2) & 1, row = 32 * (warp & 3) + lane;       // row = key index inside the chunk
-  const bool issuer = warp == 0;
+  const int part = warp >> 2, row = 32 * (warp & 3) + lane;       // row = key index inside the chunk; part = 4 queries of a tile
+  const bool issuer = warp == 3;        // key rows 96..127 are masked out of most tiles: that warp has the time
   if (warp == 0) tmem_alloc(&tmem_base, 512);
   if (tid == 0) {
     mbar_init(&gfull, 1);
     mbar_init(&dw_done, 1);
     mbar_init(&u_done, 1);
-    mbar_init(&u_free, CWARPS);
-    mbar_init(&p_ready, CWARPS);
+    mbar_init(&u_free, KV_WARPS);
+    mbar_init(&p_ready, KV_WARPS);
     mbar_init(&p_done, 1);
-    for (int s = 0; s < 3; ++s) mbar_init(&st_ready[s], CWARPS);
+    for (int s = 0; s < 3; ++s) mbar_init(&st_ready[s], KV_WARPS);
     mbar_fence_init();
     dead = 0;
   }
   __syncthreads();
   if (tid == 0) fetch_g_images(a, Ghi, Glo, &gfull, b, h, c);
   const size_t qoff = (size_t)(b * a.Hq + h) * a.N, koff = (size_t)(b * a.Hkv + kvh) * a.N;
-  load_head_factor(hf, a.factors, h, tid, CTHREADS);
-  load_operand_image(Ka, a.k + koff * HD, c * CT, a.N, true, tid, CTHREADS);
-  load_operand_image(Qimg, a.q + qoff * HD, c * CT, a.N, false, tid, CTHREADS);
-  load_u_image(Uimg, a.v + koff * VD, c * CT, a.N, tid, CTHREADS);
+  load_head_factor(hf, a.factors, h, tid, KV_THREADS);
+  load_operand_image(Ka, a.k + koff * HD, c * CT, a.N, true, tid, KV_THREADS);
+  load_operand_image(Qimg, a.q + qoff * HD, c * CT, a.N, false, tid, KV_THREADS);
+  load_u_image(Uimg, a.v + koff * VD, c * CT, a.N, tid, KV_THREADS);
   async_copies_wait();
   __syncthreads();
   const int tiles = min(CT / KT, (a.N - c * CT + KT - 1) / KT);
   const int rank = hf.rank, rpos = hf.rpos;
-  for (int s = 0; s < 3; ++s) init_stack_constants(St + s * ST_BYTES, hf, tid, CTHREADS);
-  if ((tid >> 7) < tiles)
+  for (int s = 0; s < 3; ++s) init_stack_constants(St + s * ST_BYTES, hf, tid, KV_THREADS);
+  if (tid < 256 && (tid >> 7) < tiles)
     build_stack_piece(St + (tid >> 7) * ST_BYTES, Qimg, (tid >> 7) * KT, hf, tid & 127, Lo + (tid >> 7) * STLO_BYTES);
   fence_async_smem();
   fence_before_sync();
@@ -381,14 +382,14 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
   for (int qt = 0; qt < tiles; ++qt) {
     // keys of this warp are all later than the tile's queries -> nothing survives the mask
     const bool warp_active = 32 * (warp & 3) <= qt * KT + KT - 1;
-    float u[RM][8], dw[8];
+    float u[RM][4], dw[4];
     w.wait(&u_done, qt & 1, 0x35);
     fence_after_sync();
     if (warp_active) {
 #pragma unroll
       for (int r = 0; r < RM; ++r)
-        if (r < rank) tmem_ld8(tU + lane_off + r * KT + 8 * half, u[r]);
-      tmem_ld8(tW + lane_off + qt * KT + 8 * half, dw);
+        if (r < rank) tmem_ld4(tU + lane_off + r * KT + 4 * part, u[r]);
+      tmem_ld4(tW + lane_off + qt * KT + 4 * part, dw);
       tmem_ld_wait();
     }
     fence_before_sync();
@@ -406,34 +407,35 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
     // one P tile and one W^T tile in tensor memory: the MMAs of the previous tile must have read them
     if (qt >= 1) w.wait(&p_done, (qt - 1) & 1, 0x36);
     fence_after_sync();
-    const uint32_t pt = tP + lane_off;
-    f32x2 wv[4] = {0ull, 0ull, 0ull, 0ull};
+    const uint32_t pt = tP + lane_off + 2 * part;
+    f32x2 wv[2] = {0ull, 0ull};
     if (warp_active) {
-      f32x2 dw2[4], wp[4], wn[4];
-      bool keep[8];
+      f32x2 dw2[2], wp[2], wn[2];
+      bool keep[4];
 #pragma unroll
-      for (int x = 0; x < 8; ++x) keep[x] = qt * KT + 8 * half + x >= row;      // query not earlier than the key
+      for (int x = 0; x < 4; ++x) keep[x] = qt * KT + 4 * part + x >= row;      // query not earlier than the key
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 2; ++j) {
         dw2[j] = f2_pack(keep[2 * j] ? 2.f * dw[2 * j] : 0.f, keep[2 * j + 1] ? 2.f * dw[2 * j + 1] : 0.f);
         wp[j] = wn[j] = 0ull;
       }
 #pragma unroll
       for (int r = 0; r < RM; ++r) {
         if (r < rank) {
-          f32x2 t[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const f32x2 u2 = f2_pack(u[r][2 * j], u[r][2 * j + 1]);
-            t[j] = f2_mul(dw2[j], u2);
-            if (r < rpos) wp[j] = f2_fma(u2, u2, wp[j]);
-            else wn[j] = f2_fma(u2, u2, wn[j]);
-          }
-          store_tile8(pt, r, half, t, r >= rpos);
+          const f32x2 ua = f2_pack(u[r][0], u[r][1]), ub = f2_pack(u[r][2], u[r][3]);
+          const f32x2 ta = f2_mul(dw2[0], ua), tb = f2_mul(dw2[1], ub);
+          if (r < rpos) { wp[0] = f2_fma(ua, ua, wp[0]); wp[1] = f2_fma(ub, ub, wp[1]); }
+          else { wn[0] = f2_fma(ua, ua, wn[0]); wn[1] = f2_fma(ub, ub, wn[1]); }
+          float a0, a1, b0, b1;
+          f2_unpack(ta, a0, a1);
+          f2_unpack(tb, b0, b1);
+          uint32_t lo = pack_bf16(a0, a1), hi = pack_bf16(b0, b1);
+          if (r >= rpos) { lo ^= 0x80008000u; hi ^= 0x80008000u; }
+          tmem_st2(pt + r * (KT / 2), lo, hi);
         }
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < 2; ++j) {
         float p0, p1, n0, n1;
         f2_unpack(wp[j], p0, p1);
         f2_unpack(wn[j], n0, n1);
@@ -442,18 +444,20 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
     } else {
 #pragma unroll
       for (int r = 0; r < RM; ++r)
-        if (r < rank) store_tile8(pt, r, half, wv, false);
+        if (r < rank) tmem_st2(pt + r * (KT / 2), 0u, 0u);
     }
     {
-      const uint4 o = pack_pairs_bf16(wv);
-      tmem_st4(tWt + lane_off + 4 * half, o.x, o.y, o.z, o.w);
+      float a0, a1, b0, b1;
+      f2_unpack(wv[0], a0, a1);
+      f2_unpack(wv[1], b0, b1);
+      tmem_st2(tWt + lane_off + 2 * part, pack_bf16(a0, a1), pack_bf16(b0, b1));
     }
     tmem_st_wait();
     fence_before_sync();
     warp_arrive(&p_ready, lane);
     // stack of tile qt + 2 into the slot whose last reader was the dk MMA of tile qt - 1 (complete: see above)
     if (qt + 2 < tiles) {
-      if (half == (qt & 1))
+      if (part == (qt & 3))
         build_stack_piece(St + ((qt + 2) % 3) * ST_BYTES, Qimg, (qt + 2) * KT, hf, tid & 127, Lo + (qt & 1) * STLO_BYTES);
       fence_async_smem();
       warp_arrive(&st_ready[(qt + 2) % 3], lane);
@@ -478,23 +482,20 @@ __global__ void __launch_bounds__(CTHREADS, 1) intra_bwd_kv_kernel(const IntraBw
   // beyond N are dropped at the write-out
   float* stage_out = reinterpret_cast<float*>(smem);    // two [128][65] fp32 staging tiles: dk, then dv
   {
+    float vv[16];
+    tmem_ld16(tK + lane_off + 16 * part, vv);
+    tmem_ld_wait();
 #pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      float vv[16];
-      tmem_ld16(tK + lane_off + 32 * half + 16 * cc, vv);
-      tmem_ld_wait();
+    for (int x = 0; x < 16; ++x) stage_out[row * 65 + 16 * part + x] = vv[x];
+    tmem_ld16(tV + lane_off + 16 * part, vv);
+    tmem_ld_wait();
 #pragma unroll
-      for (int x = 0; x < 16; ++x) stage_out[row * 65 + 32 * half + 16 * cc + x] = vv[x];
-      tmem_ld16(tV + lane_off + 32 * half + 16 * cc, vv);
-      tmem_ld_wait();
-#pragma unroll
-      for (int x = 0; x < 16; ++x) stage_out[STAGE_OUT_FLOATS + row * 65 + 32 * half + 16 * cc + x] = vv[x];
-    }
+    for (int x = 0; x < 16; ++x) stage_out[STAGE_OUT_FLOATS + row * 65 + 16 * part + x] = vv[x];
   }
   fence_before_sync();
   __syncthreads();
   if (!dead) {
-    for (int x = tid; x < 2 * CT * 16; x += CTHREADS) {   // coalesced write-out, four dims per thread: dk, then dv
+    for (int x = tid; x < 2 * CT * 16; x += KV_THREADS) {   // coalesced write-out, four dims per thread: dk, then dv
       const int which = x >= CT * 16, xx = x - which * CT * 16;
       const int r = xx >> 4, seg = xx & 15, j = c * CT + r;
       float* dst = which ? a.dv_part : a.dk_part;
@@ -561,7 +562,7 @@ cudaError_t OAL_INTRA_NAME(intra_backward_kv)(const void* q, const void* k, cons
   a.dk_part = dk ? dk_part : nullptr; a.dv_part = dv ? dv_part : nullptr; a.status = status;
   a.N = N; a.NB = NB; a.Hq = Hq; a.Hkv = Hkv;
   a.gimg_lo_offset = (size_t)B * Hq * NB * SLAB_S_BYTES;
-  intra_bwd_kv_kernel<<<dim3(NB, Hq, B), CTHREADS, BKV_SMEM, st>>>(a);
+  intra_bwd_kv_kernel<<<dim3(NB, Hq, B), KV_THREADS, BKV_SMEM, st>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const size_t total = (size_t)B * Hkv * N * 16;

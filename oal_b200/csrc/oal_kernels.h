@@ -76,7 +76,7 @@ cudaError_t dcoef_reduce(const float* partial, int outer, int Hq, const int32_t*
                          const int32_t* group_start, float* dcoef, float* slots, cudaStream_t st);
 cudaError_t norm_vjp_image(const void* grad_out, int out_dt, const float* grad_num, const float* grad_den,
                            const float* num, const float* den, float floor_v, float* g, void* gimg, int heads,
-                           int N, int NB, cudaStream_t st);
+                           int N, int NB, int token_major_heads, cudaStream_t st);   // > 0: grad_out is [B, N, Hq, 64]
 
 
 // ---- factored intra-chunk weight (oal_factor.cu) -----------------------------------------
@@ -94,7 +94,7 @@ cudaError_t intra_coef_finish(const float* partial, int tiles, int nu_stride, in
 int intra_coef_terms();          // terms per head this build handles (rows of the partial-sum triangle)
 cudaError_t intra_forward(const void* q, const void* k, const void* v, const void* factors, void* out, float* num,
                           float* den, int32_t* status, int B, int Hq, int Hkv, int N, int NB, int out_dt,
-                          float floor_v, cudaStream_t st);
+                          float floor_v, bool out_token_major, cudaStream_t st);
 cudaError_t intra_backward_q(const void* q, const void* k, const void* v, const void* gimg, const void* factors,
                              void* dq, const float* dq_init, float* coef_partial, int32_t* status, int B, int Hq,
                              int Hkv, int N, int NB, cudaStream_t st);

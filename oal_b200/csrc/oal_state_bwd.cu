@@ -648,7 +648,8 @@ __global__ void dcoef_slots_kernel(const float* dcoef, const int32_t* dim_perm, 
 __global__ void __launch_bounds__(256) norm_vjp_image_kernel(const void* grad_out, int out_dt, const float* grad_num,
                                                              const float* grad_den, const float* num,
                                                              const float* den, float floor_v, float* g,
-                                                             __nv_bfloat16* gimg, int N, int NB, int heads) {
+                                                             __nv_bfloat16* gimg, int N, int NB, int heads,
+                                                             int tm_heads) {
   __shared__ float part[8][32];
   const int ec = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t per_head = (size_t)NB * CT;
@@ -658,6 +659,8 @@ __global__ void __launch_bounds__(256) norm_vjp_image_kernel(const void* grad_ou
   const int cidx = t / CT, tl = t % CT;
   const bool live = t < N;
   const size_t row = bh * N + t;
+  // row of the upstream gradient of out: head-first [B, Hq, N, 64], or token-major [B, N, Hq, 64] (tm_heads = Hq)
+  const size_t grow = tm_heads > 0 ? ((bh / tm_heads) * N + t) * tm_heads + bh % tm_heads : row;
   float gv[8], dot = 0.f, dn = 1.f, dw = 1.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) gv[j] = 0.f;
@@ -667,11 +670,11 @@ __global__ void __launch_bounds__(256) norm_vjp_image_kernel(const void* grad_ou
     if (grad_out) {
       float go[8];
       if (out_dt == OAL_DTYPE_BF16) {
-        const uint4 w = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grad_out) + row * VD + 8 * ec);
+        const uint4 w = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(grad_out) + grow * VD + 8 * ec);
         unpack_bf16x8(w, go);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) go[j] = load_elem(grad_out, row * VD + 8 * ec + j, out_dt);
+        for (int j = 0; j < 8; ++j) go[j] = load_elem(grad_out, grow * VD + 8 * ec + j, out_dt);
       }
       const float4 n0 = *reinterpret_cast<const float4*>(num + row * VD + 8 * ec);
       const float4 n1 = *reinterpret_cast<const float4*>(num + row * VD + 8 * ec + 4);
@@ -785,11 +788,11 @@ cudaError_t dcoef_reduce(const float* partial, int outer, int Hq, const int32_t*
 
 cudaError_t norm_vjp_image(const void* grad_out, int out_dt, const float* grad_num, const float* grad_den,
                            const float* num, const float* den, float floor_v, float* g, void* gimg, int heads,
-                           int N, int NB, cudaStream_t st) {
+                           int N, int NB, int token_major_heads, cudaStream_t st) {
   const size_t rows = (size_t)heads * NB * CT;      // a multiple of 32
   norm_vjp_image_kernel<<<(unsigned)(rows / 32), 256, 0, st>>>(grad_out, out_dt, grad_num, grad_den, num, den,
                                                                    floor_v, g, static_cast<__nv_bfloat16*>(gimg), N,
-                                                                   NB, heads);
+                                                                   NB, heads, token_major_heads);
   return cudaGetLastError();
 }
 

@@ -190,14 +190,14 @@ def _validate_geometry(q, k, v):
 
 def make_problem(geometry, *, groups: int, io_dtype: torch.dtype, out_dtype: torch.dtype, precision: str,
                  chunk: int, scale: float, floor: float, grad_mask: int = 0,
-                 padded_slabs: int = 0) -> _lib.OalProblem:
+                 flags: int = 0) -> _lib.OalProblem:
     """Fill the C struct for a (padded) problem."""
     b, hq, hkv, n, _, _ = geometry
     return _lib.OalProblem(batch=b, q_heads=hq, kv_heads=hkv, seq_len=n, head_dim=_lib.HEAD_DIM,
                            value_dim=_lib.HEAD_DIM, groups=groups, chunk=chunk,
                            io_dtype=_lib.DTYPE_CODES[io_dtype], out_dtype=_lib.DTYPE_CODES[out_dtype],
                            precision=_lib.PRECISION_CODES[precision], grad_mask=grad_mask,
-                           scale=scale, floor=floor, padded_slabs=padded_slabs)
+                           scale=scale, floor=floor, flags=flags)
 
 
 def kernel_chunk_tokens(precision: str) -> int:

@@ -53,6 +53,7 @@ class _PreparedGroupedHdBlockGemm:
     scale: float
     kernel_eps: float
     normalization_floor: float
+    out_token_major: bool = False      # `out` is [B, N, Hq, 64] (an addition: see prepare_grouped_hd_block_gemm)
 
 
 def prepare_grouped_hd_block_gemm(
@@ -89,8 +90,17 @@ def prepare_grouped_hd_block_gemm(
     key_retention: str = "none",
     feature_padding: str = "none",
     output_dtype: torch.dtype | None = None,
+    output_layout: str = "heads_first",
 ) -> _PreparedGroupedHdBlockGemm:
-    """Freeze geometry/groups once for an explicitly repeated workload."""
+    """Freeze geometry/groups once for an explicitly repeated workload.
+
+    ``output_layout`` (an addition to the reference's signature): ``"heads_first"`` returns ``out`` as
+    ``[B, Hq, N, Dv]`` like the reference; ``"tokens_first"`` returns it as ``[B, N, Hq, Dv]``, which the
+    kernels write directly, so the caller's restore step (transpose + contiguous copy,
+    qwen_lora_experiment/attention/common.py:575-596) disappears; the upstream gradient of ``out`` is then
+    expected in that layout too.  Tensor-core precision, Dv = 64 and at most 8 groups per head only."""
+    if output_layout not in ("heads_first", "tokens_first"):
+        raise ValueError("output_layout must be 'heads_first' or 'tokens_first'")
     q, k, v = _validate_qkv(q, k, v)
     factor, gmax = _validate_factor(factor, query_heads=q.shape[1], q_device=q.device)
     working_dtype = _resolve_working_dtype(q.dtype, factor.dtype)
@@ -121,7 +131,7 @@ def prepare_grouped_hd_block_gemm(
     return _PreparedGroupedHdBlockGemm(
         plan=plan, groups=groups, tables=build_group_tables(groups, gmax), gmax=gmax,
         scale=_resolve_scale(scale, q.shape[-1]), kernel_eps=resolved_eps,
-        normalization_floor=_POSITIVE_FP32_FLOOR)
+        normalization_floor=_POSITIVE_FP32_FLOOR, out_token_major=output_layout == "tokens_first")
 
 
 def run_prepared_grouped_hd_block_gemm(prepared, q, k, v, factor):
@@ -148,13 +158,15 @@ def run_prepared_grouped_hd_block_gemm(prepared, q, k, v, factor):
                                           kernel_eps=prepared.kernel_eps, working_dtype=torch.float32)
     return run_grouped_coefficients(q, k, v, a.contiguous(), b.contiguous(), c.contiguous(),
                                     tables=prepared.tables, plan=plan, scale=prepared.scale,
-                                    normalization_floor=prepared.normalization_floor)
+                                    normalization_floor=prepared.normalization_floor,
+                                    out_token_major=prepared.out_token_major)
 
 
-def run_grouped_coefficients(q, k, v, a, b, c, *, tables, plan, scale, normalization_floor):
+def run_grouped_coefficients(q, k, v, a, b, c, *, tables, plan, scale, normalization_floor, out_token_major=False):
     """Enter the kernels with explicit per-head coefficients A [Hq], B [Hq,G], C [Hq,G,G]."""
     run = hd_parallel_block_gemm_autograd if any(plan.requested_gradient_mask) else hd_parallel_block_gemm
-    return run(q, k, v, a, b, c, tables=tables, scale=scale, eps=normalization_floor, plan=plan)
+    return run(q, k, v, a, b, c, tables=tables, scale=scale, eps=normalization_floor, plan=plan,
+               out_token_major=out_token_major)
 
 
 def grouped_causal_attention(q, k, v, dim_groups, factor, **kwargs):

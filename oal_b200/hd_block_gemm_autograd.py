@@ -36,7 +36,6 @@ class GroupTables:
     dim_perm: torch.Tensor      # int32 [Hq, 64]: dims sorted by group id (padded dims first, group 0)
     group_start: torch.Tensor   # int32 [Hq, 17]: group g owns dim_perm[h, start[g]:start[g+1]]
     group_count: int            # G = extent of B / C
-    padded_slabs: int = 0       # max over heads of sum_g ceil(|g| / 16) (0 = unknown)
 
 
 def build_group_tables(groups: torch.Tensor, group_count: int) -> GroupTables:
@@ -50,8 +49,7 @@ def build_group_tables(groups: torch.Tensor, group_count: int) -> GroupTables:
     counts.scatter_add_(1, g64, torch.ones_like(g64))
     start = torch.zeros(hq, _lib.MAX_GROUPS + 1, dtype=torch.int64, device=groups.device)
     start[:, 1:] = counts.cumsum(1)
-    slabs = int(((counts + 15) // 16).sum(1).max().item())
-    return GroupTables(perm.contiguous(), start.to(torch.int32).contiguous(), int(group_count), slabs)
+    return GroupTables(perm.contiguous(), start.to(torch.int32).contiguous(), int(group_count))
 
 
 def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
@@ -162,11 +160,15 @@ def check_pending_status(block: bool = False, device=None) -> None:
 
 
 def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: float,
-                 plan: HDParallelBlockPlan, *, state_in=None, check=True):
+                 plan: HDParallelBlockPlan, *, state_in=None, check=True, workspace=None, reuse_state_stage=False,
+                 out_token_major=False):
     """Launch the forward kernels.  Returns (out, num, den[B,Hq,N,1], saved_state, padded q,k,v).
 
     ``check``: True = synchronise and raise on the status word now; "defer" = queue it (the queued
-    entry is left in ``forward_impl.last_pending`` for the caller that owns the backward)."""
+    entry is left in ``forward_impl.last_pending`` for the caller that owns the backward).
+    ``workspace`` / ``reuse_state_stage``: sequence parallelism passes the workspace in which
+    ``oal_forward_local_state`` has just left the chunk-state increments of this very call.
+    ``out_token_major``: ``out`` comes back as ``[B, N, Hq, 64]`` (what the output projection reads)."""
     if q.device.type != "cuda":
         raise RuntimeError("oal_b200 runs on CUDA tensors only (there is no CPU path)")
     check_pending_status(device=q.device)
@@ -178,12 +180,17 @@ def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: flo
     dev = q.device
     problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=q.dtype, out_dtype=kernel_out,
                            precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
-                           floor=float(floor), padded_slabs=tables.padded_slabs)
-    out = torch.empty(B, Hq, N, _lib.HEAD_DIM, dtype=kernel_out, device=dev)
+                           floor=float(floor), grad_mask=_lib.GRAD_REUSE_STATE_STAGE if reuse_state_stage else 0,
+                           flags=_lib.FLAG_OUT_TOKEN_MAJOR if out_token_major else 0)
+    if out_token_major and Dv != _lib.HEAD_DIM:
+        raise ValueError("the token-major output layout needs value_dimension == 64")
+    out = torch.empty((B, N, Hq, _lib.HEAD_DIM) if out_token_major else (B, Hq, N, _lib.HEAD_DIM),
+                      dtype=kernel_out, device=dev)
     num = torch.empty(B, Hq, N, _lib.HEAD_DIM, dtype=torch.float32, device=dev)
     den = torch.empty(B, Hq, N, dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    ws = torch.empty(max(plan.forward_workspace_bytes, 16), dtype=torch.uint8, device=dev)
+    ws = workspace if workspace is not None else torch.empty(max(plan.forward_workspace_bytes, 16),
+                                                             dtype=torch.uint8, device=dev)
     saved = (torch.empty(plan.saved_state_bytes, dtype=torch.uint8, device=dev)
              if plan.saved_state_bytes else None)
     a32, b32, c32 = (t.detach().to(torch.float32).contiguous() for t in (a, b, c))
@@ -227,7 +234,8 @@ def backward_operands(plan: HDParallelBlockPlan, num, den, grad_out, grad_num, g
 
 def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scale, floor,
                   plan: HDParallelBlockPlan, mask, grad_out, grad_num, grad_den, *, dstate_in=None,
-                  workspace=None, reuse_state_stage=False, forward_status: "PendingStatus | None" = None):
+                  workspace=None, reuse_state_stage=False, forward_status: "PendingStatus | None" = None,
+                  out_token_major=False):
     """Launch the backward kernels; returns (dq, dk, dv, dA, dB, dC) with None where not requested.
 
     ``workspace`` / ``reuse_state_stage``: sequence parallelism passes the workspace that
@@ -244,7 +252,8 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
     problem = make_problem(plan.geometry, groups=tables.group_count, io_dtype=qp.dtype, out_dtype=kernel_out,
                            precision=plan.precision, chunk=plan.chunk_tokens, scale=float(scale),
                            floor=float(floor),
-                           grad_mask=bits | (_lib.GRAD_REUSE_STATE_STAGE if reuse_state_stage else 0))
+                           grad_mask=bits | (_lib.GRAD_REUSE_STATE_STAGE if reuse_state_stage else 0),
+                           flags=_lib.FLAG_OUT_TOKEN_MAJOR if out_token_major else 0)
     G = tables.group_count
     dq = torch.empty_like(qp) if bits & _lib.GRAD_Q else None
     dk = torch.empty_like(kp) if bits & _lib.GRAD_K else None
@@ -278,14 +287,16 @@ class _HDParallelBlockGemmFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx: Any, q, k, v, a, b, c, tables: GroupTables, scale: float, eps: float,
-                plan: HDParallelBlockPlan):
+                plan: HDParallelBlockPlan, out_token_major: bool = False):
         mask = tuple(bool(x) for x in ctx.needs_input_grad[:6])
         if plan.requested_gradient_mask != mask:
             raise ValueError("plan gradient mask must exactly match the six tensor inputs")
         ctx.set_materialize_grads(False)
         out, num, den, saved_state, padded = forward_impl(q, k, v, a, b, c, tables, scale, eps, plan,
-                                                          check="defer" if any(mask) else True)
+                                                          check="defer" if any(mask) else True,
+                                                          out_token_major=out_token_major)
         ctx.forward_status = forward_impl.last_pending
+        ctx.out_token_major = out_token_major
         ctx.tables, ctx.scale, ctx.eps, ctx.plan, ctx.mask = tables, float(scale), float(eps), plan, mask
         ctx.input_dtypes = tuple(t.dtype for t in (q, k, v, a, b, c))
         ctx.has_state = saved_state is not None
@@ -305,10 +316,11 @@ class _HDParallelBlockGemmFunction(torch.autograd.Function):
         state = saved[8] if ctx.has_state else None
         mask = ctx.mask
         if grad_output is None and grad_numerator is None and grad_denominator is None:
-            return (None,) * 10
+            return (None,) * 11
         dq, dk, dv, dA, dB, dC = backward_impl(padded, num, den, state, ctx.tables, ctx.scale, ctx.eps,
                                                ctx.plan, mask, grad_output, grad_numerator,
-                                               grad_denominator, forward_status=ctx.forward_status)
+                                               grad_denominator, forward_status=ctx.forward_status,
+                                               out_token_major=ctx.out_token_major)
         grads = [dq, dk, dv, dA, dB, dC]
         result = []
         for requested, g, dtype in zip(mask, grads, ctx.input_dtypes):
@@ -318,14 +330,14 @@ class _HDParallelBlockGemmFunction(torch.autograd.Function):
                 raise RuntimeError("requested HD Block-GEMM gradient was not produced")
             else:
                 result.append(g.to(dtype))
-        return (*result, None, None, None, None)
+        return (*result, None, None, None, None, None)
 
 
-def hd_parallel_block_gemm(q, k, v, a, b, c, *, tables, scale, eps, plan):
+def hd_parallel_block_gemm(q, k, v, a, b, c, *, tables, scale, eps, plan, out_token_major=False):
     """Forward only (no autograd graph), same return triple."""
-    out, num, den, _, _ = forward_impl(q, k, v, a, b, c, tables, scale, eps, plan)
+    out, num, den, _, _ = forward_impl(q, k, v, a, b, c, tables, scale, eps, plan, out_token_major=out_token_major)
     return out, num, den
 
 
-def hd_parallel_block_gemm_autograd(q, k, v, a, b, c, *, tables, scale, eps, plan):
-    return _HDParallelBlockGemmFunction.apply(q, k, v, a, b, c, tables, scale, eps, plan)
+def hd_parallel_block_gemm_autograd(q, k, v, a, b, c, *, tables, scale, eps, plan, out_token_major=False):
+    return _HDParallelBlockGemmFunction.apply(q, k, v, a, b, c, tables, scale, eps, plan, out_token_major)

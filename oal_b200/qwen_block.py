@@ -65,7 +65,7 @@ class QwenOalStack(nn.Module):
                  dtype=torch.bfloat16, device=None):
         super().__init__()
         self.geometry = geometry
-        self.cache = PreparedCallCache(precision=precision)
+        self.cache = PreparedCallCache(precision=precision, output_layout="tokens_first" if precision == "bf16_tensorcore" else "heads_first")
         layers = geometry.num_layers if num_layers is None else num_layers
         gen = torch.Generator().manual_seed(4000 + seed)
         self.embed = nn.Embedding(vocab, geometry.hidden_size, dtype=dtype, device=device)

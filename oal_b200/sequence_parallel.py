@@ -55,15 +55,17 @@ def exclusive_prefix_over_ranks(local: torch.Tensor, group=None, *, reverse: boo
     return total
 
 
-def local_state_total(k: torch.Tensor, v: torch.Tensor, plan, groups: int = 1) -> torch.Tensor:
-    """fp32 ``[B*Hkv, 2432, 80]``: this rank's contribution to the running state."""
+def local_state_total(k: torch.Tensor, v: torch.Tensor, plan, groups: int = 1, workspace=None) -> torch.Tensor:
+    """fp32 ``[B*Hkv, 2432, 80]``: this rank's contribution to the running state.  With ``workspace``
+    (``plan.forward_workspace_bytes`` bytes) the chunk-state increments stay there for the forward."""
     lib = _lib.load()
     B, Hq, Hkv, N, D, Dv = plan.geometry
     kp, vp = _pad_last(k), _pad_last(v)
     problem = make_problem(plan.geometry, groups=groups, io_dtype=k.dtype, out_dtype=k.dtype,
                            precision=plan.precision, chunk=plan.chunk_tokens, scale=1.0, floor=1e-38)
     total = torch.empty(B * Hkv, _lib.STATE_ROWS, _lib.E_PAD, dtype=torch.float32, device=k.device)
-    ws = torch.empty(max(_lib.workspace_bytes(problem, 0), 16), dtype=torch.uint8, device=k.device)
+    ws = workspace if workspace is not None else torch.empty(max(_lib.workspace_bytes(problem, 0), 16),
+                                                             dtype=torch.uint8, device=k.device)
     status = torch.zeros(1, dtype=torch.int32, device=k.device)
     with _lib.device_guard(kp):
         rc = lib.oal_forward_local_state(ctypes.byref(problem), _lib.ptr(kp), _lib.ptr(vp), _lib.ptr(total),
@@ -104,10 +106,12 @@ class _SequenceParallelFunction(torch.autograd.Function):
         plan = prepared.plan
         mask = tuple(bool(x) for x in ctx.needs_input_grad[:6])
         ctx.set_materialize_grads(False)
-        state_in = exclusive_prefix_over_ranks(local_state_total(k, v, plan, prepared.gmax), group)
+        ws = torch.empty(max(plan.forward_workspace_bytes, 16), dtype=torch.uint8, device=q.device)
+        state_in = exclusive_prefix_over_ranks(local_state_total(k, v, plan, prepared.gmax, workspace=ws), group)
         out, num, den, saved_state, padded = forward_impl(q, k, v, a, b, c, prepared.tables, prepared.scale,
                                                           prepared.normalization_floor, plan, state_in=state_in,
-                                                          check="defer" if any(mask) else True)
+                                                          check="defer" if any(mask) else True, workspace=ws,
+                                                          reuse_state_stage=True)
         ctx.forward_status = forward_impl.last_pending
         ctx.prepared, ctx.group, ctx.mask, ctx.reduce_coef = prepared, group, mask, reduce_coef
         ctx.input_dtypes = tuple(t.dtype for t in (q, k, v, a, b, c))

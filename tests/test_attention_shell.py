@@ -117,3 +117,58 @@ def test_fused_rope_prologue_matches_the_elementwise_statement_forward_and_backw
     assert torch.equal(outs[True][2], outs[False][2])   # v is only moved
     for fused_t, plain_t in zip(outs[True], outs[False]):
         assert err(fused_t, plain_t) < 2e-2             # the element-wise path rounds to bf16 after every step
+
+
+@pytest.mark.gpu
+def test_token_major_output_matches_the_restore_step_forward_and_backward():
+    """``output_layout="tokens_first"``: the kernels write ``out`` as ``[B, N, Hq, 64]`` and read its upstream
+    gradient in that layout; values and gradients must be those of the reference's restore step
+    (transpose + contiguous copy + reshape, qwen_lora_experiment/attention/common.py:575-596) applied to the
+    heads-first result -- bit for bit, since only the addresses of the stores and loads change."""
+    import oal_b200
+    from oal_b200 import synthetic
+
+    case = synthetic.qwen_head_case(21, batch=2, n=300, hq=6, hkv=2, g=8, bf16=True)
+    dev = "cuda"
+    groups = case.dim_groups.to(dev)
+    dflat = torch.randn(2, 300, 6 * 64, generator=torch.Generator().manual_seed(1)).to(dev, torch.bfloat16)
+    results = {}
+    for layout in ("heads_first", "tokens_first"):
+        q, k, v = (t.to(dev, torch.bfloat16).requires_grad_() for t in (case.q, case.k, case.v))
+        factor = case.factor.to(dev).requires_grad_()
+        prepared = oal_b200.prepare_grouped_hd_block_gemm(q, k, v, groups, factor, scale=case.scale,
+                                                          precision="bf16_tensorcore", output_layout=layout)
+        out, num, den = oal_b200.run_prepared_grouped_hd_block_gemm(prepared, q, k, v, factor)
+        if layout == "heads_first":
+            flat = out.transpose(1, 2).contiguous().reshape(2, 300, 6 * 64)       # the restore step
+        else:
+            assert out.shape == (2, 300, 6, 64) and out.is_contiguous()
+            flat = out.reshape(2, 300, 6 * 64)
+        flat.backward(dflat)
+        results[layout] = [t.detach().clone() for t in (flat, num, den, q.grad, k.grad, v.grad, factor.grad)]
+    for x, y in zip(results["heads_first"], results["tokens_first"]):
+        assert torch.equal(x, y)
+    with pytest.raises(ValueError, match="output_layout"):
+        oal_b200.prepare_grouped_hd_block_gemm(q, k, v, groups, factor, output_layout="columns_first")
+
+
+@pytest.mark.gpu
+def test_layer_with_token_major_output_equals_layer_with_restore_step():
+    torch.manual_seed(9)
+    geo = shell.ModelGeometry(num_layers=1, hidden_size=4 * 64, num_query_heads=4, num_kv_heads=2, head_dim=64)
+    groups = (torch.arange(64) % 4).to(torch.int32).expand(4, -1).contiguous()
+    factor = torch.rand(4, 15) * 0.9 + 0.1
+    x = (torch.randn(2, 150, geo.hidden_size, device="cuda") * 0.5).to(torch.bfloat16)
+    pe = shell.rope_tables(150, 64, device="cuda", dtype=torch.bfloat16)
+    outs = []
+    for layout in ("heads_first", "tokens_first"):
+        torch.manual_seed(3)
+        cache = shell.PreparedCallCache(precision="bf16_tensorcore", output_layout=layout)
+        layer = shell.OalAttentionLayer(0, groups.cuda(), factor.cuda(), cache=cache, geometry=geo, lora_rank=4,
+                                        lora_alpha=8.0, dtype=torch.bfloat16, device="cuda")
+        xi = x.clone().requires_grad_()
+        y = layer(xi, pe)
+        y.float().square().mean().backward()
+        outs.append((y.detach(), xi.grad.detach(), layer.factor.grad.detach()))
+    for a_, b_ in zip(*outs):
+        assert torch.equal(a_, b_)
