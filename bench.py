@@ -112,11 +112,13 @@ class ClockSampler:
         import shutil
         import subprocess
 
+        if self.index < 0:             # ranks other than 0 do not sample (rank 0 prints the line)
+            return self
         smi = shutil.which("nvidia-smi")
         if smi:
             try:
                 self.proc = subprocess.Popen([smi, f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                              "-i", self._uuid(), "-lms", "10"], stdout=subprocess.PIPE,
+                                              "-i", self._uuid(), "-lms", "20"], stdout=subprocess.PIPE,
                                              stderr=subprocess.DEVNULL, text=True)
             except Exception as exc:
                 self.error, self.proc = repr(exc), None
@@ -133,6 +135,9 @@ class ClockSampler:
         self.t_end = time.time()
 
     def __exit__(self, *exc):
+        if self.index < 0:
+            self.window = []
+            return
         if self.t_end is None:
             self.end()
         self.stop.set()
@@ -317,7 +322,7 @@ def run_gpu_arm(args) -> None:
     # ---- warm-up, then the timed region: K steps, CUDA events on the launching stream, L2 flushed between
     # steps; the clock sampler keeps the samples taken while the GPU is under load (warm-up + timed steps)
     events = []
-    with ClockSampler(local) as clocks:
+    with ClockSampler(local if rank == 0 else -1) as clocks:
         clocks.begin()
         for i in range(max(args.warmup, 3)):
             step(sets[i % 2]["dev"])
@@ -387,13 +392,16 @@ def run_gpu_arm(args) -> None:
                 copy_out.wait_event(compute_done[slot])
                 host_out[slot].copy_(dev_out[slot], non_blocking=True)
                 out_done[slot].record(copy_out)
+        enqueued = time.perf_counter()
         torch.cuda.synchronize()
+        return enqueued
 
     e2e_loop(2)
     barrier()
     t0 = time.perf_counter()
-    e2e_loop(args.steps)
+    e2e_enqueued = e2e_loop(args.steps)
     e2e_ms = (time.perf_counter() - t0) * 1e3
+    e2e_host_ms = (e2e_enqueued - t0) * 1e3 / args.steps          # host time to queue one step
     barrier()
     h2d = host_in[0].numel() * host_in[0].element_size()
     d2h = host_out[0].numel() * host_out[0].element_size()
@@ -536,7 +544,7 @@ def run_gpu_arm(args) -> None:
                                 chunk_tokens=KERNEL_CHUNK, flop_model_chunk_tokens=64,
                                 l2="256 MiB buffer written between timed steps", flop_per_token=fpt),
                     e2e=dict(value=e2e_value, unit="tokens/s", h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
-                             copies_per_step=dict(h2d=1, d2h=1), copy_gbs=copy_bw,
+                             copies_per_step=dict(h2d=1, d2h=1), copy_gbs=copy_bw, host_enqueue_ms_per_step=e2e_host_ms,
                              copy_bound_tokens_per_s=tok * world / max(h2d / (copy_bw["h2d"] * 1e9), d2h / (copy_bw["d2h"] * 1e9)),
                              note="uploads, kernels and downloads of neighbouring steps overlap; the slowest of the "
                                   "three bounds a step"),

@@ -112,6 +112,7 @@ class PendingStatus:
     call_id: int
     what: str
     done: bool = False
+    device_word: torch.Tensor | None = None
 
     def check(self, block: bool) -> bool:
         """Raise if the word reports a problem; returns False when it is not yet known (non-blocking)."""
@@ -122,18 +123,43 @@ class PendingStatus:
                 return False
             self.event.synchronize()
         self.done = True
+        self.device_word = None
         _raise_for_bits(int(self.host[0]), f" [{self.what}, call {self.call_id}]")
         return True
 
 
-def defer_status(status: torch.Tensor, what: str = "forward") -> PendingStatus:
-    host = torch.empty(1, dtype=torch.int32, pin_memory=True)
-    host.copy_(status, non_blocking=True)
-    event = torch.cuda.Event()
-    event.record(torch.cuda.current_stream(status.device))
-    entry = PendingStatus(host, event, next(_CALL_IDS), what)
+_STATUS_STREAMS: dict = {}
+
+
+def _status_stream(device: torch.device) -> torch.cuda.Stream:
     with _PENDING_LOCK:
-        _PENDING.setdefault(status.device.index, []).append(entry)
+        stream = _STATUS_STREAMS.get(device.index)
+        if stream is None:
+            stream = _STATUS_STREAMS[device.index] = torch.cuda.Stream(device)
+    return stream
+
+
+def defer_status(status: torch.Tensor, what: str = "forward") -> PendingStatus:
+    """Queue the copy of a call's status word to pinned host memory on the device's status stream.
+
+    The copy does not go on the caller's stream: the device runs all device-to-host copies of a
+    process through one copy queue, so a 4-byte copy on the compute stream waits behind whatever
+    large result copy the application has in flight on another stream, and the kernels after it wait
+    too (measured: 0.6 ms per step beside a 64 MB result copy).  The entry keeps the device word alive
+    until the copy has run, which is what lets it be read from a stream it was not allocated on."""
+    device = status.device
+    ready = torch.cuda.Event()
+    ready.record(torch.cuda.current_stream(device))
+    side = _status_stream(device)
+    side.wait_event(ready)
+    host = torch.empty(1, dtype=torch.int32, pin_memory=True)
+    with torch.cuda.stream(side):
+        host.copy_(status, non_blocking=True)
+    event = torch.cuda.Event()
+    event.record(side)
+    entry = PendingStatus(host, event, next(_CALL_IDS), what, device_word=status)
+    with _PENDING_LOCK:
+        _PENDING.setdefault(device.index, []).append(entry)
     return entry
 
 
