@@ -11,8 +11,8 @@
 //   dk += P^T-tile . stack(Q),  dU += W^T G   with W = sum_r sgn_r u_r^2,
 // per query head into fp32 partials that kv_head_reduce_kernel sums over the heads of a KV head in
 // fixed order.  The stacked scaled tile (oal_intra.cuh) is rebuilt per tile in a three-slot ring by
-// the warps themselves; lane 0 of warp 0 also issues every MMA, between that warp's own steps, driven
-// by warp-granular mbarrier arrivals.  The cross-chunk parts computed by the state kernels arrive as fp32 buffers and are added
+// the warps themselves; lane 0 of one compute warp (the one whose rows the causal mask idles most) also issues
+// every MMA, between that warp's own steps, driven by warp-granular mbarrier arrivals.  The cross-chunk parts computed by the state kernels arrive as fp32 buffers and are added
 // before the final cast.  Reference stages replaced: oal_attention/hd_block_gemm_backward_wave.py:253-476
 // (dS, local dphi_q / dphi_k / dU GEMMs) and the folds / coefficient partials of
 // oal_attention/hd_block_gemm_feature_backward.py:59-474.
@@ -329,7 +329,10 @@ __global__ void __launch_bounds__(KV_THREADS, 1) intra_bwd_kv_kernel(const Intra
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int kvh = h / (a.Hq / a.Hkv);
   const int part = warp >> 2, row = 32 * (warp & 3) + lane;       // row = key index inside the chunk; part = 4 queries of a tile
-  const bool issuer = warp == 3;        // key rows 96..127 are masked out of most tiles: that warp has the time
+  // Key rows 96..127 (warps 3, 7, 11, 15) are masked out of every tile but the last two, and every stack is
+  // built before those: these four warps are the builders, so the warps of rows 0..31, which work in every
+  // tile, never build.  Rows 64..95 are idle for the first four tiles: warp 2 issues the MMAs.
+  const bool issuer = warp == 2, builder = (warp & 3) == 3;
   if (warp == 0) tmem_alloc(&tmem_base, 512);
   if (tid == 0) {
     mbar_init(&gfull, 1);
@@ -457,8 +460,8 @@ __global__ void __launch_bounds__(KV_THREADS, 1) intra_bwd_kv_kernel(const Intra
     warp_arrive(&p_ready, lane);
     // stack of tile qt + 2 into the slot whose last reader was the dk MMA of tile qt - 1 (complete: see above)
     if (qt + 2 < tiles) {
-      if (part == (qt & 3))
-        build_stack_piece(St + ((qt + 2) % 3) * ST_BYTES, Qimg, (qt + 2) * KT, hf, tid & 127, Lo + (qt & 1) * STLO_BYTES);
+      if (builder)
+        build_stack_piece(St + ((qt + 2) % 3) * ST_BYTES, Qimg, (qt + 2) * KT, hf, 32 * part + lane, Lo + (qt & 1) * STLO_BYTES);
       fence_async_smem();
       warp_arrive(&st_ready[(qt + 2) % 3], lane);
     }

@@ -128,11 +128,11 @@ __global__ void __launch_bounds__(GEN_THREADS, 2) state_update_kernel(const Stat
     __syncthreads();
     if (tid == 0) {
       fence_after_sync();
-      const uint32_t a_addr = smem_u32(Abuf + buf * SLAB_A_BYTES);
+      const uint64_t da = smem_desc(smem_u32(Abuf + buf * SLAB_A_BYTES), 128, CT * 16);
+      const uint64_t du = smem_desc(u_addr, 128, CT * 16);
 #pragma unroll
       for (int ks = 0; ks < CT / 16; ++ks)
-        mma_bf16_ss(tacc + buf * EP, smem_desc(a_addr + ks * 256, 128, CT * 16),
-                    smem_desc(u_addr + ks * 256, 128, CT * 16), idesc, ks > 0);
+        mma_bf16_ss(tacc + buf * EP, desc_advance(da, ks * 256), desc_advance(du, ks * 256), idesc, ks > 0);
       mma_commit(&mma_done[buf]);
     }
     if (it >= 1) epilogue(it - 1);
@@ -344,20 +344,20 @@ __global__ void __launch_bounds__(CR_THREADS, 1) cross_read_kernel(const CrossRe
     // ---------------- MMA issue ----------------
     if (lane == 0) {
       const uint32_t idesc = instr_desc_bf16(128, EP, 0, 1);
+      // descriptors of slot 0 of both rings, advanced by adds: this thread is the serial path of every slab
+      const uint64_t da0 = smem_desc(smem_u32(Abuf), CT * 16, 128), ds0 = smem_desc(smem_u32(Sbuf), 128, 128 * 16);
       int s3 = 0, use = 0, gs = 0, guse = 0;
       for (int k = 0; k < my_items; ++k) {
         const uint32_t tacc = tmem_base + (k & 1) * EP;
         if (k >= 2) w.wait(&acc_free[k & 1], ((k >> 1) - 1) & 1, 0x43);   // item k-2 has left this accumulator
         for (int s = 0; s < F_SLABS; ++s) {
-          const uint32_t a_addr = smem_u32(Abuf + s3 * SLAB_A_BYTES);
-          const uint32_t s_addr = smem_u32(Sbuf + gs * SLAB_S_BYTES);
+          const uint64_t da = desc_advance(da0, s3 * SLAB_A_BYTES), dsl = desc_advance(ds0, gs * SLAB_S_BYTES);
           w.wait(&full_a[s3], use & 1, 0x44);
           w.wait(&s_full[gs], guse & 1, 0x45);
           fence_after_sync();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)       // 16 features per step
-            mma_bf16_ss(tacc, smem_desc(a_addr + ks * 2 * CT * 16, CT * 16, 128),
-                        smem_desc(s_addr + ks * 256, 128, 128 * 16), idesc, (s > 0 || ks > 0));
+            mma_bf16_ss(tacc, desc_advance(da, ks * 2 * CT * 16), desc_advance(dsl, ks * 256), idesc, (s > 0 || ks > 0));
           mma_commit(&a_free[s3]);
           mma_commit(&s_free[gs]);
           if (s == F_SLABS - 1) mma_commit(&acc_full[k & 1]);

@@ -166,9 +166,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
     const int fr = 32 * (warp & 3) + lane, ch = (warp - DS_GEN_WARPS) >> 2, col0 = ch * DS_COLS;
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
     float acc[DS_COLS];            // this thread's part of the dCarry row, summed over the heads of the item
-    uint4 cpk[DS_COLS / 8], cpl[DS_COLS / 8];
+    float carry[DS_COLS];          // this thread's part of the carry row (value + remainder), fp32, once per item
 #pragma unroll
-    for (int e = 0; e < DS_COLS / 8; ++e) cpk[e] = cpl[e] = make_uint4(0u, 0u, 0u, 0u);
+    for (int j = 0; j < DS_COLS; ++j) carry[j] = 0.f;
     DsCursor d, dn;
     d.start(a.NB, a.Hkv, rep);
     dn = d;
@@ -186,10 +186,19 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
                                                          (((size_t)d.u * a.NB + d.c) * F_SLABS + d.slab) * SLAB_S_BYTES);
         const uint4* cl = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(a.carry_lo) +
                                                          (((size_t)d.u * a.NB + d.c) * F_SLABS + d.slab) * SLAB_S_BYTES);
+        uint4 cpk[DS_COLS / 8], cpl[DS_COLS / 8];
 #pragma unroll
         for (int e = 0; e < DS_COLS / 8; ++e) {
           cpk[e] = cp[(col0 / 8 + e) * 128 + fr];
           cpl[e] = cl[(col0 / 8 + e) * 128 + fr];
+        }
+#pragma unroll
+        for (int e = 0; e < DS_COLS / 8; ++e) {
+          float c0[8], c1[8];
+          unpack_bf16x8(cpk[e], c0);
+          unpack_bf16x8(cpl[e], c1);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) carry[8 * e + j] = c0[j] + c1[j];
         }
       }
       w.wait(&mma_done[s], use & 1, 0x32);
@@ -207,12 +216,9 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
       for (int r = 0; r < DS_COLS / 8; ++r) {
         tmem_ld_wait();
         if (r + 1 < DS_COLS / 8) tmem_ld8(tz + lane_off + 8 * (r + 1), z[(r + 1) & 1]);
-        float c0[8], c1[8];
-        unpack_bf16x8(cpk[r], c0);
-        unpack_bf16x8(cpl[r], c1);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          dot[j & 3] = fmaf(z[r & 1][j], c0[j] + c1[j], dot[j & 3]);
+          dot[j & 3] = fmaf(z[r & 1][j], carry[8 * r + j], dot[j & 3]);
           acc[8 * r + j] = fmaf(cf, z[r & 1][j], acc[8 * r + j]);
         }
       }
@@ -239,10 +245,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
     // ---------------- MMA issue ----------------
     if (lane == 0) {
       const uint32_t idesc = instr_desc_bf16(128, EP, 1, 1);
+      // descriptors of slot 0 of both rings, advanced by adds: this thread is the serial path of every slab
+      const uint64_t da0 = smem_desc(smem_u32(Abuf), 128, CT * 16), dg0 = smem_desc(smem_u32(Gbuf), 128, CT * 16);
       int s = 0, use = 0, gs = 0, guse = 0;
       for (int it = 0; it < T; ++it) {
-        const uint32_t a_addr = smem_u32(Abuf + s * SLAB_A_BYTES);
-        const uint32_t g_addr = smem_u32(Gbuf + gs * SLAB_S_BYTES);
+        const uint64_t da = desc_advance(da0, s * SLAB_A_BYTES), dg = desc_advance(dg0, gs * SLAB_S_BYTES);
         const uint32_t tz = tmem_base + EP * s;
         w.wait(&full_a[s], use & 1, 0x33);
         w.wait(&g_full[gs], guse & 1, 0x34);
@@ -250,8 +257,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
         fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < CT / 16; ++ks)
-          mma_bf16_ss(tz, smem_desc(a_addr + ks * 256, 128, CT * 16), smem_desc(g_addr + ks * 256, 128, CT * 16), idesc,
-                      ks > 0);
+          mma_bf16_ss(tz, desc_advance(da, ks * 256), desc_advance(dg, ks * 256), idesc, ks > 0);
         mma_commit(&mma_done[s]);
         mma_commit(&g_free[gs]);               // the loader may refill this G slot when these MMAs are done
         if (++s == DS_RING) { s = 0; ++use; }
@@ -518,19 +524,20 @@ __global__ void __launch_bounds__(FG_THREADS, 1) feature_grad_kernel(const FeatG
     // ---------------- MMA issue ----------------
     if (lane == 0) {
       const uint32_t idesc = instr_desc_bf16(128, 128, 0, 0);
+      const uint64_t da0 = smem_desc(smem_u32(Aimg), CT * 16, 128), ds0 = smem_desc(smem_u32(Sbuf), 128 * 16, 128);
       int gs = 0, guse = 0, ds = 0, duse = 0;
       for (int k = 0; k < my_items; ++k) {
-        const uint32_t a_addr = smem_u32(Aimg + (k & 1) * SLAB_S_BYTES);
+        const uint64_t da = desc_advance(da0, (k & 1) * SLAB_S_BYTES);
         w.wait(&a_full[k & 1], (k >> 1) & 1, 0x54);
         for (int s = 0; s < F_SLABS; ++s) {
-          const uint32_t s_addr = smem_u32(Sbuf + gs * SLAB_S_BYTES);
+          const uint64_t dsl = desc_advance(ds0, gs * SLAB_S_BYTES);
           w.wait(&s_full[gs], guse & 1, 0x55);
           if (duse > 0) w.wait(&d_free[ds], (duse - 1) & 1, 0x56);
           fence_after_sync();
 #pragma unroll
           for (int ks = 0; ks < EP / 16; ++ks)
-            mma_bf16_ss(tmem_base + ds * 128, smem_desc(a_addr + ks * 2 * CT * 16, CT * 16, 128),
-                        smem_desc(s_addr + ks * 2 * 128 * 16, 128 * 16, 128), idesc, ks > 0);
+            mma_bf16_ss(tmem_base + ds * 128, desc_advance(da, ks * 2 * CT * 16), desc_advance(dsl, ks * 2 * 128 * 16), idesc,
+                        ks > 0);
           mma_commit(&d_full[ds]);
           mma_commit(&s_free[gs]);
           if (s == F_SLABS - 1) mma_commit(&a_free[k & 1]);

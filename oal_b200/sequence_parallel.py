@@ -46,12 +46,17 @@ def exclusive_prefix_over_ranks(local: torch.Tensor, group=None, *, reverse: boo
     if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
         return torch.zeros_like(local)
     world, rank = dist.get_world_size(group), dist.get_rank(group)
-    gathered = [torch.empty_like(local) for _ in range(world)]
-    dist.all_gather(gathered, local.contiguous(), group=group)
-    total = torch.zeros_like(local)
-    ranks = range(rank + 1, world) if reverse else range(rank)
-    for r in ranks:
-        total += gathered[r]
+    gathered = torch.empty((world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+    if local.is_cuda:
+        dist.all_gather_into_tensor(gathered, local.contiguous(), group=group)   # one NCCL call, no copy-out
+    else:
+        dist.all_gather(list(gathered.unbind(0)), local.contiguous(), group=group)
+    part = gathered[rank + 1:] if reverse else gathered[:rank]
+    if part.shape[0] == 0:
+        return torch.zeros_like(local)
+    total = part[0].clone()
+    for r in range(1, part.shape[0]):       # fixed order: rank r, then r + 1, ...
+        total += part[r]
     return total
 
 

@@ -139,3 +139,41 @@ def test_plan_rejects_bad_geometry():
         build_hd_block_gemm_plan(big, big, big, requested_gradient_mask=(False,) * 6)
     with pytest.raises(TypeError):
         build_hd_block_gemm_plan(q.double(), k.double(), v.double(), requested_gradient_mask=(False,) * 6)
+
+
+# ---- helper-level cases of the reference's operator tests (tests/operators/test_grouped_quadratic.py:464-512
+# there): group tables stay a logical broadcast, packed factor -> PSD coefficients, pair counts ----------------
+
+def test_shared_dim_groups_stay_one_row():
+    from oal_b200.grouped_quadratic import _canonicalize_dim_groups
+
+    canonical = _canonicalize_dim_groups(torch.tensor((0, 0, 1, 1), dtype=torch.int64), query_heads=4,
+                                         head_dimension=4, gmax=2, q_device=torch.device("cpu"))
+    assert canonical.ndim == 1 and canonical.shape == (4,) and canonical.dtype == torch.int32
+
+
+def test_packed_factor_expansion_matches_psd_coefficients():
+    from oal_b200.grouped_quadratic import _expand_factor_coefficients
+
+    constant, linear, quadratic = _expand_factor_coefficients(_factor(torch.float64), query_heads=1, gmax=2,
+                                                              kernel_eps=0.07, working_dtype=torch.float64)
+    lower = torch.tensor(((1.1, 0.0, 0.0), (0.5, 0.9, 0.0), (0.4, 0.8, 0.7)), dtype=torch.float64)
+    matrix = lower @ lower.T
+    torch.testing.assert_close(constant, matrix[0, 0].view(1) + 0.07)
+    torch.testing.assert_close(linear, 2 * matrix[0, 1:].view(1, 2))
+    torch.testing.assert_close(quadratic, matrix[1:, 1:].view(1, 2, 2))
+    assert quadratic.is_contiguous()
+    # and the per-head form with a gradient: d(sum C)/dL through the explicit products
+    factor = torch.rand(3, 6, dtype=torch.float64).requires_grad_()
+    _, _, c = _expand_factor_coefficients(factor, query_heads=3, gmax=2, kernel_eps=1e-6, working_dtype=torch.float64)
+    c.sum().backward()
+    assert factor.grad.shape == (3, 6) and torch.isfinite(factor.grad).all()
+
+
+def test_packed_pair_count_is_triangular():
+    from oal_b200.grouped_quadratic import _infer_gmax
+
+    for gmax in (1, 2, 8, 16):
+        assert _infer_gmax((gmax + 1) * (gmax + 2) // 2) == gmax
+    with pytest.raises(ValueError):
+        _infer_gmax(7)

@@ -238,3 +238,46 @@ def test_operator_on_second_gpu_while_first_is_current():
     want, _, _ = _oracle(q0, k0, v0, _groups(), _factor())
     assert out.device == torch.device("cuda:1") and ERR(out, want) < 1e-5
     assert torch.isfinite(q.grad).all()
+
+
+def test_gradcheck_case_of_the_reference_on_the_gpu_entry():
+    """The reference runs torch.autograd.gradcheck on its fp64 statement for B=1, H=1, N=2, D=2, Dv=1,
+    groups (0, 1), kernel_eps 0.1 (tests/operators/test_grouped_quadratic.py:267-297 there).  The CUDA
+    operator computes in fp32, so the same case is checked twice here: analytic gradients against the fp64
+    dense statement, and against central differences of the operator's own forward along random directions."""
+    q0, k0, v0 = _case(batch=1, query_heads=1, key_heads=1, sequence=2, dimension=2, value_dimension=1)
+    f0 = torch.tensor((1.0, 0.4, 0.8, 0.2, 0.3, 0.7))
+    groups = torch.tensor((0, 1), dtype=torch.int32)
+    gen = torch.Generator().manual_seed(11)
+    dout = torch.randn(1, 1, 2, 1, generator=gen)
+
+    def run(q, k, v, f):
+        return oal_b200.oal_attention(q, k, v, groups.cuda(), f, kernel_eps=0.1, precision="fp32_ieee")
+
+    leaves = [t.clone().cuda().requires_grad_() for t in (q0, k0, v0, f0)]
+    run(*leaves).backward(dout.cuda())
+    ref = [t.double().requires_grad_() for t in (q0, k0, v0, f0)]
+    a, b, c = orc.expand_factor(ref[3], 1, 0.1)
+    want, _, _ = orc.dense_forward(ref[0], ref[1], ref[2], groups, a, b, c, scale=2 ** -0.5)
+    want.backward(dout.double())
+    for got, r in zip(leaves, ref):
+        assert ERR(got.grad, r.grad) < 1e-4
+    # central differences of the fp32 forward: step 1e-2 keeps rounding (1e-7 / 1e-2) below the tolerance
+    for trial in range(4):
+        dirs = [torch.randn(t.shape, generator=gen) for t in (q0, k0, v0, f0)]
+        step = 1e-2
+        plus = run(*[(t + step * d).cuda() for t, d in zip((q0, k0, v0, f0), dirs)])
+        minus = run(*[(t - step * d).cuda() for t, d in zip((q0, k0, v0, f0), dirs)])
+        numeric = float(((plus - minus).cpu() * dout).sum() / (2 * step))
+        analytic = float(sum((leaf.grad.cpu() * d).sum() for leaf, d in zip(leaves, dirs)))
+        assert abs(numeric - analytic) <= 2e-3 * max(1.0, abs(analytic)), (trial, numeric, analytic)
+
+
+def test_group_ids_may_be_int64_on_the_gpu_entry():
+    """The reference widens group ids to int64 for torch indexing
+    (tests/operators/test_grouped_quadratic.py:439-461 there); here both widths give the same bits."""
+    q, k, v = (t.cuda() for t in _case(query_heads=1, key_heads=1, dimension=4))
+    factor = _factor().cuda()
+    narrow = oal_b200.oal_attention(q, k, v, torch.tensor((0, 0, 1, 1), dtype=torch.int32).cuda(), factor)
+    wide = oal_b200.oal_attention(q, k, v, torch.tensor((0, 0, 1, 1), dtype=torch.int64).cuda(), factor)
+    assert torch.equal(narrow, wide)
