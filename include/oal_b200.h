@@ -256,6 +256,31 @@ int oal_profile_report(char* buffer, size_t capacity);
  */
 void oal_set_overlap(int enable);
 
+/*
+ * Packed factor -> coefficients: L = lower-triangular matrix whose rows, packed in the order of
+ * torch.tril_indices, are `factor` [factor_rows, (G+1)(G+2)/2] with factor_rows 1 (shared) or q_heads;
+ * M = L L^T, coef_a[h] = M00 + kernel_eps, coef_b[h, g] = 2 M[0, 1+g], coef_c[h, g, g'] = M[1+g, 1+g'].
+ * Replaces _expand_factor_coefficients (oal_attention/grouped_quadratic.py:184-219) and, with
+ * oal_expand_factor_grad (d_factor from d_coef_a/b/c; a shared factor row sums the heads in order), its
+ * autograd graph.  fp32.
+ */
+int oal_expand_factor(const float* factor, int factor_rows, int q_heads, int groups, float kernel_eps, float* coef_a,
+                      float* coef_b, float* coef_c, void* stream);
+int oal_expand_factor_grad(const float* factor, int factor_rows, int q_heads, int groups, const float* d_coef_a,
+                           const float* d_coef_b, const float* d_coef_c, float* d_factor, void* stream);
+
+/*
+ * Deferred status words.  The reference synchronises after every forward to read its checks
+ * (oal_attention/hd_block_gemm_runtime.py:392-408); here a call leaves a status word on the device, and
+ * oal_status_defer queues its copy to pinned host memory on a stream the library owns, ordered after
+ * everything `stream` holds so far (the word must stay allocated until the ticket has been polled as
+ * finished).  oal_status_poll returns 1 and the word once the copy has run, 0 while it has not (`block`
+ * = 0), or waits for it (`block` = 1).  A ticket stays valid for the next 1023 oal_status_defer calls on
+ * its device.
+ */
+int oal_status_defer(const int32_t* status, void* stream, int64_t* ticket);
+int oal_status_poll(int64_t ticket, int block, int32_t* value);
+
 /* Library / build identification: "oal_b200 <version> sm_100a". Host pointer. */
 const char* oal_version_string(void);
 

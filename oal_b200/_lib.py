@@ -38,6 +38,10 @@ EXPORTED_SYMBOLS = (
     "oal_profile_enable",
     "oal_profile_report",
     "oal_set_overlap",
+    "oal_status_defer",
+    "oal_status_poll",
+    "oal_expand_factor",
+    "oal_expand_factor_grad",
     "oal_forward_static_scratch",
     "oal_forward_local_state",
     "oal_backward_local_state",
@@ -111,6 +115,14 @@ def load() -> ctypes.CDLL:
     lib.oal_profile_enable.restype = None
     lib.oal_set_overlap.argtypes = [ctypes.c_int]
     lib.oal_set_overlap.restype = None
+    lib.oal_status_defer.argtypes = [i32p, vp, ctypes.POINTER(ctypes.c_int64)]
+    lib.oal_status_defer.restype = ctypes.c_int
+    lib.oal_status_poll.argtypes = [ctypes.c_int64, ctypes.c_int, ctypes.POINTER(ctypes.c_int32)]
+    lib.oal_status_poll.restype = ctypes.c_int
+    lib.oal_expand_factor.argtypes = [f32p, ci, ci, ci, ctypes.c_float, f32p, f32p, f32p, vp]
+    lib.oal_expand_factor.restype = ctypes.c_int
+    lib.oal_expand_factor_grad.argtypes = [f32p, ci, ci, ci, f32p, f32p, f32p, f32p, vp]
+    lib.oal_expand_factor_grad.restype = ctypes.c_int
     lib.oal_profile_report.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
     lib.oal_profile_report.restype = ctypes.c_int
     lib.oal_last_error_string.restype = ctypes.c_char_p

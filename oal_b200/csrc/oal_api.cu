@@ -60,6 +60,22 @@ struct LaunchScope {
 
 size_t align_up(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// ---- deferred status words ------------------------------------------------------------------
+// A ring of pinned host words per device, filled by 4-byte copies on a stream of the library's own: the
+// copy never sits on the caller's stream (where it would queue behind the application's own device-to-host
+// copies and hold the kernels after it), and queueing one costs two event records and a copy instead of
+// the tensor, stream and event objects a Python implementation creates per call.
+constexpr int STATUS_RING = 1024;
+struct StatusRing {
+  cudaStream_t stream = nullptr;
+  int32_t* host = nullptr;
+  cudaEvent_t ready[STATUS_RING] = {};
+  cudaEvent_t done[STATUS_RING] = {};
+  long long next = 0;
+};
+std::mutex g_status_mutex;
+StatusRing g_status[64];
+
 // ---- side streams ------------------------------------------------------------------------------
 // Small kernels that nothing on the main chain waits for (the per-head factor table of the forward, the
 // coefficient-gradient reductions, the reverse state scan and the whole key/value chain of the backward)
@@ -452,6 +468,87 @@ int oal_forward(const OalProblem* p, const void* q, const void* k, const void* v
 }
 
 void oal_set_overlap(int enable) { g_overlap.store(enable ? 1 : 0); }
+
+int oal_status_defer(const int32_t* status, void* stream, int64_t* ticket) {
+  if (!status || !ticket) return fail(OAL_ERR_ARGUMENT, "oal_status_defer: NULL pointer");
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e, "oal_status_defer");
+  if (dev < 0 || dev >= 64) return fail(OAL_ERR_ARGUMENT, "oal_status_defer: device index out of range");
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  StatusRing& r = g_status[dev];
+  if (!r.stream) {
+    if ((e = cudaStreamCreateWithFlags(&r.stream, cudaStreamNonBlocking)) != cudaSuccess) return fail_cuda(e, "oal_status_defer");
+    if ((e = cudaHostAlloc(reinterpret_cast<void**>(&r.host), STATUS_RING * sizeof(int32_t), cudaHostAllocPortable)) !=
+        cudaSuccess)
+      return fail_cuda(e, "oal_status_defer");
+  }
+  const int slot = (int)(r.next % STATUS_RING);
+  if (!r.done[slot]) {
+    if ((e = cudaEventCreateWithFlags(&r.ready[slot], cudaEventDisableTiming)) != cudaSuccess ||
+        (e = cudaEventCreateWithFlags(&r.done[slot], cudaEventDisableTiming)) != cudaSuccess)
+      return fail_cuda(e, "oal_status_defer");
+  } else if ((e = cudaEventSynchronize(r.done[slot])) != cudaSuccess) {   // the slot's previous copy (1024 calls ago)
+    return fail_cuda(e, "oal_status_defer");
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if ((e = cudaEventRecord(r.ready[slot], st)) != cudaSuccess || (e = cudaStreamWaitEvent(r.stream, r.ready[slot], 0)) != cudaSuccess ||
+      (e = cudaMemcpyAsync(r.host + slot, status, sizeof(int32_t), cudaMemcpyDeviceToHost, r.stream)) != cudaSuccess ||
+      (e = cudaEventRecord(r.done[slot], r.stream)) != cudaSuccess)
+    return fail_cuda(e, "oal_status_defer");
+  *ticket = ((int64_t)dev << 48) | (int64_t)r.next;
+  ++r.next;
+  return OAL_OK;
+}
+
+int oal_status_poll(int64_t ticket, int block, int32_t* value) {
+  if (!value) return fail(OAL_ERR_ARGUMENT, "oal_status_poll: NULL pointer");
+  const int dev = (int)(ticket >> 48);
+  const long long seq = (long long)(ticket & (((int64_t)1 << 48) - 1));
+  if (dev < 0 || dev >= 64) return fail(OAL_ERR_ARGUMENT, "oal_status_poll: bad ticket");
+  cudaEvent_t done;
+  int32_t* word;
+  {
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    StatusRing& r = g_status[dev];
+    if (seq >= r.next || seq + STATUS_RING <= r.next) return fail(OAL_ERR_ARGUMENT, "oal_status_poll: ticket expired or unknown");
+    done = r.done[seq % STATUS_RING];
+    word = r.host + seq % STATUS_RING;
+  }
+  if (block) {
+    cudaError_t e = cudaEventSynchronize(done);
+    if (e != cudaSuccess) return fail_cuda(e, "oal_status_poll");
+  } else {
+    cudaError_t e = cudaEventQuery(done);
+    if (e == cudaErrorNotReady) return 0;
+    if (e != cudaSuccess) return fail_cuda(e, "oal_status_poll");
+  }
+  *value = *static_cast<volatile int32_t*>(word);
+  return 1;
+}
+
+int oal_expand_factor(const float* factor, int factor_rows, int q_heads, int groups, float kernel_eps, float* coef_a,
+                      float* coef_b, float* coef_c, void* stream) {
+  if (!factor || !coef_a || !coef_b || !coef_c) return fail(OAL_ERR_ARGUMENT, "oal_expand_factor: NULL pointer");
+  if (q_heads < 1 || groups < 1 || groups > OAL_MAX_GROUPS || (factor_rows != 1 && factor_rows != q_heads))
+    return fail(OAL_ERR_ARGUMENT, "oal_expand_factor: bad geometry");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LaunchScope scope("expand_factor", st);
+  cudaError_t e = oal::expand_factor(factor, factor_rows, q_heads, groups, kernel_eps, coef_a, coef_b, coef_c, st);
+  return e == cudaSuccess ? OAL_OK : fail_cuda(e, "oal_expand_factor");
+}
+
+int oal_expand_factor_grad(const float* factor, int factor_rows, int q_heads, int groups, const float* d_coef_a,
+                           const float* d_coef_b, const float* d_coef_c, float* d_factor, void* stream) {
+  if (!factor || !d_coef_a || !d_coef_b || !d_coef_c || !d_factor)
+    return fail(OAL_ERR_ARGUMENT, "oal_expand_factor_grad: NULL pointer");
+  if (q_heads < 1 || groups < 1 || groups > OAL_MAX_GROUPS || (factor_rows != 1 && factor_rows != q_heads))
+    return fail(OAL_ERR_ARGUMENT, "oal_expand_factor_grad: bad geometry");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LaunchScope scope("expand_factor_grad", st);
+  cudaError_t e = oal::expand_factor_grad(factor, factor_rows, q_heads, groups, d_coef_a, d_coef_b, d_coef_c, d_factor, st);
+  return e == cudaSuccess ? OAL_OK : fail_cuda(e, "oal_expand_factor_grad");
+}
 
 int oal_backward(const OalProblem* p, const void* q, const void* k, const void* v, const int32_t* dim_perm,
                  const int32_t* group_start, const float* coef_a, const float* coef_b, const float* coef_c,

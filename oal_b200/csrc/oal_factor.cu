@@ -239,6 +239,52 @@ __global__ void __launch_bounds__(128) intra_coef_finish_kernel(const float* par
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Packed factor -> coefficients and back.  L is the lower-triangular matrix whose packed rows
+// (row-major over (row, col <= row), the order of torch.tril_indices) are `factor`; M = L L^T;
+// A = M00 + eps, B = 2 M[0, 1:], C = M[1:, 1:].  One block per query head, thread = (i, j).
+// Replaces the tensor-op sequence of oal_attention/grouped_quadratic.py (_expand_factor_coefficients there)
+// and its autograd graph: two launches per step instead of about forty.
+// ---------------------------------------------------------------------------
+constexpr int XS = GMAX + 1;     // largest side of L
+
+__device__ __forceinline__ float packed_l(const float* f, int r, int c) { return c <= r ? f[r * (r + 1) / 2 + c] : 0.f; }
+
+__global__ void __launch_bounds__(XS * XS) expand_factor_kernel(const float* factor, int factor_rows, int G, float eps,
+                                                                float* A, float* B, float* C) {
+  const int h = blockIdx.x, side = G + 1;
+  const float* f = factor + (size_t)(factor_rows == 1 ? 0 : h) * (side * (side + 1) / 2);
+  const int i = threadIdx.x / side, j = threadIdx.x % side;
+  if (i >= side) return;
+  float m = 0.f;
+  for (int k = 0; k <= min(i, j); ++k) m = fmaf(packed_l(f, i, k), packed_l(f, j, k), m);
+  if (i == 0 && j == 0) A[h] = m + eps;
+  else if (i == 0) B[(size_t)h * G + j - 1] = 2.f * m;
+  else if (j > 0) C[((size_t)h * G + i - 1) * G + j - 1] = m;
+}
+
+// dL = (S + S^T) L on the lower triangle, S[0][0] = dA, S[0][j] = 2 dB[j-1], S[i][j] = dC[i-1][j-1] (i, j >= 1),
+// S[i][0] = 0.  With one shared factor row (factor_rows == 1) a single block walks the heads in order.
+__global__ void __launch_bounds__(XS * XS) expand_factor_grad_kernel(const float* factor, int factor_rows, int Hq, int G,
+                                                                     const float* dA, const float* dB, const float* dC,
+                                                                     float* dfactor) {
+  const int side = G + 1, P = side * (side + 1) / 2;
+  const int i = threadIdx.x / side, k = threadIdx.x % side;
+  const bool mine = i < side && k <= i;
+  const int h0 = factor_rows == 1 ? 0 : blockIdx.x, h1 = factor_rows == 1 ? Hq : h0 + 1;
+  const float* f = factor + (size_t)(factor_rows == 1 ? 0 : h0) * P;
+  float acc = 0.f;
+  for (int h = h0; h < h1 && mine; ++h) {
+    auto S = [&](int r, int c) -> float {
+      if (r == 0) return c == 0 ? dA[h] : 2.f * dB[(size_t)h * G + c - 1];
+      return c == 0 ? 0.f : dC[((size_t)h * G + r - 1) * G + c - 1];
+    };
+    for (int j = k; j < side; ++j) acc = fmaf(S(i, j) + S(j, i), packed_l(f, j, k), acc);
+  }
+  if (mine) dfactor[(size_t)(factor_rows == 1 ? 0 : h0) * P + i * (i + 1) / 2 + k] = acc;
+}
+
 }  // namespace
 
 size_t head_factor_bytes(int Hq) { return (size_t)Hq * sizeof(HeadFactor); }
@@ -254,6 +300,20 @@ cudaError_t intra_coef_finish(const float* partial, int tiles, int nu_stride, in
                               cudaStream_t st) {
   intra_coef_finish_kernel<<<Hq, 128, 0, st>>>(partial, tiles, nu_stride, rm, static_cast<const HeadFactor*>(table),
                                                extra, B, Hq, G, dA, dB, dC);
+  return cudaGetLastError();
+}
+
+
+cudaError_t expand_factor(const float* factor, int factor_rows, int Hq, int G, float eps, float* A, float* B, float* C,
+                          cudaStream_t st) {
+  expand_factor_kernel<<<Hq, (GMAX + 1) * (GMAX + 1), 0, st>>>(factor, factor_rows, G, eps, A, B, C);
+  return cudaGetLastError();
+}
+
+cudaError_t expand_factor_grad(const float* factor, int factor_rows, int Hq, int G, const float* dA, const float* dB,
+                               const float* dC, float* dfactor, cudaStream_t st) {
+  expand_factor_grad_kernel<<<factor_rows == 1 ? 1 : Hq, (GMAX + 1) * (GMAX + 1), 0, st>>>(factor, factor_rows, Hq, G, dA,
+                                                                                           dB, dC, dfactor);
   return cudaGetLastError();
 }
 

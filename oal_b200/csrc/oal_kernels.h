@@ -82,6 +82,11 @@ cudaError_t norm_vjp_image(const void* grad_out, int out_dt, const float* grad_n
 // ---- factored intra-chunk weight (oal_factor.cu) -----------------------------------------
 // Per-head table of the factored quadratic form (c_r, l_r[d], back-transform, sign split).
 size_t head_factor_bytes(int Hq);
+// Packed lower-triangular factor rows [factor_rows (1 or Hq), (G+1)(G+2)/2] -> A, B, C, and the transpose map.
+cudaError_t expand_factor(const float* factor, int factor_rows, int Hq, int G, float eps, float* A, float* B, float* C,
+                          cudaStream_t st);
+cudaError_t expand_factor_grad(const float* factor, int factor_rows, int Hq, int G, const float* dA, const float* dB,
+                               const float* dC, float* dfactor, cudaStream_t st);
 cudaError_t build_head_factors(const int32_t* dim_perm, const int32_t* group_start, const float* A, const float* Bc,
                                const float* Cc, int Hq, int G, float scale, void* table, cudaStream_t st);
 // dA, dB, dC = back-transformed sum of the query-side partial sums [B][Hq][tiles][nu_stride] (rm terms,

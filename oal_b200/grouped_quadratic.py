@@ -135,9 +135,54 @@ def _canonicalize_dim_groups(dim_groups: object, *, query_heads: int, head_dimen
     return dim_groups.to(dtype=torch.int32).contiguous()
 
 
+class _ExpandFactorOnDevice(torch.autograd.Function):
+    """fp32 CUDA factors: one kernel for the expansion and one for its gradient (``oal_expand_factor`` /
+    ``oal_expand_factor_grad``) instead of about forty tensor operations and autograd nodes per step."""
+
+    @staticmethod
+    def forward(ctx, factor, query_heads: int, gmax: int, kernel_eps: float):
+        import ctypes
+
+        from . import _lib
+
+        rows = factor.contiguous()
+        rows = rows.unsqueeze(0) if rows.ndim == 1 else rows
+        a = torch.empty(query_heads, dtype=torch.float32, device=factor.device)
+        b = torch.empty(query_heads, gmax, dtype=torch.float32, device=factor.device)
+        c = torch.empty(query_heads, gmax, gmax, dtype=torch.float32, device=factor.device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(factor.device).cuda_stream)
+        with _lib.device_guard(factor):
+            _lib.check(_lib.load().oal_expand_factor(_lib.ptr(rows), rows.shape[0], query_heads, gmax, float(kernel_eps),
+                                                     _lib.ptr(a), _lib.ptr(b), _lib.ptr(c), stream))
+        ctx.save_for_backward(rows)
+        ctx.geometry = (query_heads, gmax, factor.shape)
+        return a, b, c
+
+    @staticmethod
+    def backward(ctx, grad_a, grad_b, grad_c):
+        import ctypes
+
+        from . import _lib
+
+        (rows,) = ctx.saved_tensors
+        query_heads, gmax, shape = ctx.geometry
+        zeros = lambda *dims: torch.zeros(dims, dtype=torch.float32, device=rows.device)
+        ga = zeros(query_heads) if grad_a is None else grad_a.float().contiguous()
+        gb = zeros(query_heads, gmax) if grad_b is None else grad_b.float().contiguous()
+        gc = zeros(query_heads, gmax, gmax) if grad_c is None else grad_c.float().contiguous()
+        out = torch.empty_like(rows)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(rows.device).cuda_stream)
+        with _lib.device_guard(rows):
+            _lib.check(_lib.load().oal_expand_factor_grad(_lib.ptr(rows), rows.shape[0], query_heads, gmax, _lib.ptr(ga),
+                                                          _lib.ptr(gb), _lib.ptr(gc), _lib.ptr(out), stream))
+        return out.reshape(shape), None, None, None
+
+
 def _expand_factor_coefficients(factor: torch.Tensor, *, query_heads: int, gmax: int, kernel_eps: float,
                                 working_dtype: torch.dtype):
     """Packed lower triangle L -> A = M00 + eps, B = 2 M[0,1:], C = M[1:,1:], M = L L^T (differentiable)."""
+    if factor.is_cuda and factor.dtype == torch.float32 and working_dtype == torch.float32:
+        return _ExpandFactorOnDevice.apply(factor, query_heads, gmax, kernel_eps)
     factor_by_head = factor.unsqueeze(0) if factor.ndim == 1 else factor
     factor_by_head = factor_by_head.to(dtype=working_dtype)
     if factor_by_head.shape[0] == 1:

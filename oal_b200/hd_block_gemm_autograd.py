@@ -93,73 +93,66 @@ def raise_on_status(status: torch.Tensor) -> None:
 # assertion can poison a CUDA context ... until a safe asynchronous status mechanism is available"
 # (hd_block_gemm_runtime.py:395-398).  The status word is that mechanism: when autograd will run a
 # backward anyway, the forward only queues an asynchronous copy of its status word to pinned host
-# memory and keeps the (host word, event, call id) entry.  The backward of the same call looks at exactly
-# that entry before it launches anything -- without waiting: the host normally runs ahead of the GPU, and
-# a wait here would serialise host and device in every step (measured: it costs the whole forward time
-# per step and stalls input pipelines).  An entry that is not finished yet stays on a per-device list
-# that every later entry into the library drains without blocking; ``check_pending_status(block=True)``
-# drains it completely and is the call to make before an optimizer step consumes the gradients.  Every
-# error names the call it belongs to.
+# memory (``oal_status_defer``: a ring of pinned words and a copy stream inside the library) and keeps the
+# ticket.  The backward of the same call looks at exactly that ticket before it launches anything --
+# without waiting: the host normally runs ahead of the GPU, and a wait here would serialise host and
+# device in every step (measured: it costs the whole forward time per step and stalls input pipelines).
+# A ticket that is not finished yet stays on a per-device list that every later entry into the library
+# drains without blocking; ``check_pending_status(block=True)`` drains it completely and is the call to
+# make before an optimizer step consumes the gradients.  Every error names the call it belongs to.
 _PENDING: dict = {}
 _PENDING_LOCK = threading.Lock()
 _CALL_IDS = itertools.count(1)
+_PENDING_LIMIT = 256          # a ticket stays valid for 1023 later ones on its device: drain well before that
 
 
 @dataclass
 class PendingStatus:
-    host: torch.Tensor
-    event: torch.cuda.Event
+    ticket: int
     call_id: int
     what: str
     done: bool = False
-    device_word: torch.Tensor | None = None
+    device_word: torch.Tensor | None = None     # kept alive until the copy has run
 
     def check(self, block: bool) -> bool:
         """Raise if the word reports a problem; returns False when it is not yet known (non-blocking)."""
         if self.done:
             return True
-        if not self.event.query():
-            if not block:
-                return False
-            self.event.synchronize()
+        value = ctypes.c_int32(0)
+        rc = _lib.load().oal_status_poll(self.ticket, 1 if block else 0, ctypes.byref(value))
+        if rc == 0:
+            return False
         self.done = True
         self.device_word = None
-        _raise_for_bits(int(self.host[0]), f" [{self.what}, call {self.call_id}]")
+        _lib.check(rc)
+        _raise_for_bits(int(value.value), f" [{self.what}, call {self.call_id}]")
         return True
 
 
-_STATUS_STREAMS: dict = {}
+def defer_status(status: torch.Tensor, what: str = "forward", *, guarded: bool = False) -> PendingStatus:
+    """Queue the copy of a call's status word to pinned host memory; returns the entry that owns the ticket.
 
-
-def _status_stream(device: torch.device) -> torch.cuda.Stream:
-    with _PENDING_LOCK:
-        stream = _STATUS_STREAMS.get(device.index)
-        if stream is None:
-            stream = _STATUS_STREAMS[device.index] = torch.cuda.Stream(device)
-    return stream
-
-
-def defer_status(status: torch.Tensor, what: str = "forward") -> PendingStatus:
-    """Queue the copy of a call's status word to pinned host memory on the device's status stream.
-
-    The copy does not go on the caller's stream: the device runs all device-to-host copies of a
-    process through one copy queue, so a 4-byte copy on the compute stream waits behind whatever
-    large result copy the application has in flight on another stream, and the kernels after it wait
-    too (measured: 0.6 ms per step beside a 64 MB result copy).  The entry keeps the device word alive
-    until the copy has run, which is what lets it be read from a stream it was not allocated on."""
+    The copy runs on a stream of the library's own, never on the caller's: the device runs all
+    device-to-host copies of a process through one copy queue, so a 4-byte copy on the compute stream
+    waits behind whatever large result copy the application has in flight on another stream, and the
+    kernels after it wait too (measured: 0.6 ms per step beside a 64 MB result copy).  ``guarded``: the
+    caller already holds the device guard of ``status``."""
     device = status.device
-    ready = torch.cuda.Event()
-    ready.record(torch.cuda.current_stream(device))
-    side = _status_stream(device)
-    side.wait_event(ready)
-    host = torch.empty(1, dtype=torch.int32, pin_memory=True)
-    with torch.cuda.stream(side):
-        host.copy_(status, non_blocking=True)
-    event = torch.cuda.Event()
-    event.record(side)
-    entry = PendingStatus(host, event, next(_CALL_IDS), what, device_word=status)
+    ticket = ctypes.c_int64(0)
+    lib = _lib.load()
+    if guarded:
+        rc = lib.oal_status_defer(_lib.ptr(status), _stream_ptr(device), ctypes.byref(ticket))
+    else:
+        with _lib.device_guard(status):
+            rc = lib.oal_status_defer(_lib.ptr(status), _stream_ptr(device), ctypes.byref(ticket))
+    _lib.check(rc)
+    entry = PendingStatus(int(ticket.value), next(_CALL_IDS), what, device_word=status)
     with _PENDING_LOCK:
-        _PENDING.setdefault(device.index, []).append(entry)
+        queue = _PENDING.setdefault(device.index, [])
+        queue.append(entry)
+        overfull = len(queue) > _PENDING_LIMIT
+    if overfull:
+        check_pending_status(block=True, device=device)
     return entry
 
 
@@ -177,12 +170,18 @@ def check_pending_status(block: bool = False, device=None) -> None:
                 entry = queue[0] if queue else None
             if entry is None:
                 break
-            if not entry.done and not block and not entry.event.query():
+            try:
+                finished = entry.check(block)
+            except Exception:
+                with _PENDING_LOCK:
+                    if queue and queue[0] is entry:
+                        queue.pop(0)
+                raise
+            if not finished:
                 break
             with _PENDING_LOCK:
                 if queue and queue[0] is entry:
                     queue.pop(0)
-            entry.check(block=True)
 
 
 def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: float,
@@ -226,11 +225,9 @@ def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: flo
                              _lib.ptr(b32), _lib.ptr(c32), _lib.ptr(out), _lib.ptr(num), _lib.ptr(den),
                              _lib.ptr(saved), _lib.ptr(state_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status),
                              _stream_ptr(dev))
-    _lib.check(rc)
-    forward_impl.last_pending = None
-    if check == "defer":
-        forward_impl.last_pending = defer_status(status, "forward")
-    elif check:
+        _lib.check(rc)
+        forward_impl.last_pending = defer_status(status, "forward", guarded=True) if check == "defer" else None
+    if check and check != "defer":
         raise_on_status(status)
     if Dv != _lib.HEAD_DIM:
         out, num = out[..., :Dv].contiguous(), num[..., :Dv].contiguous()
@@ -297,9 +294,9 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
                               _lib.ptr(saved_state), _lib.ptr(go), _lib.ptr(gn), _lib.ptr(gd), _lib.ptr(dq),
                               _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dA), _lib.ptr(dB), _lib.ptr(dC),
                               _lib.ptr(dstate_in), _lib.ptr(ws), ws.numel(), _lib.ptr(status), _stream_ptr(dev))
-    _lib.check(rc)
-    if plan.precision == "bf16_tensorcore":
-        defer_status(status, "backward")         # only a bounded wait that gave up can set it here
+        _lib.check(rc)
+        if plan.precision == "bf16_tensorcore":
+            defer_status(status, "backward", guarded=True)    # only a bounded wait that gave up can set it here
     if D != _lib.HEAD_DIM:
         dq = None if dq is None else dq[..., :D].contiguous()
         dk = None if dk is None else dk[..., :D].contiguous()

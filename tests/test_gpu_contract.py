@@ -281,3 +281,46 @@ def test_group_ids_may_be_int64_on_the_gpu_entry():
     narrow = oal_b200.oal_attention(q, k, v, torch.tensor((0, 0, 1, 1), dtype=torch.int32).cuda(), factor)
     wide = oal_b200.oal_attention(q, k, v, torch.tensor((0, 0, 1, 1), dtype=torch.int64).cuda(), factor)
     assert torch.equal(narrow, wide)
+
+
+@pytest.mark.parametrize("gmax", [1, 2, 8, 16])
+@pytest.mark.parametrize("shared", [True, False])
+def test_factor_expansion_kernel_matches_the_tensor_statement(gmax, shared):
+    """Packed factor -> (A, B, C) and its gradient on the device (one kernel each) against the tensor-op
+    statement of the same map that CPU tensors take (oal_attention/grouped_quadratic.py:184-219 there)."""
+    from oal_b200.grouped_quadratic import _expand_factor_coefficients
+
+    heads, pairs = 5, (gmax + 1) * (gmax + 2) // 2
+    g = torch.Generator().manual_seed(gmax)
+    f0 = torch.randn(pairs if shared else (heads, pairs), generator=g)
+    weights = [torch.randn(heads, generator=g), torch.randn(heads, gmax, generator=g),
+               torch.randn(heads, gmax, gmax, generator=g)]
+    results = []
+    for device in ("cpu", "cuda"):
+        f = f0.double().requires_grad_() if device == "cpu" else f0.cuda().requires_grad_()
+        dtype = torch.float64 if device == "cpu" else torch.float32
+        a, b, c = _expand_factor_coefficients(f, query_heads=heads, gmax=gmax, kernel_eps=0.07, working_dtype=dtype)
+        sum((t * w.to(t)).sum() for t, w in zip((a, b, c), weights)).backward()
+        results.append([t.detach().cpu().double() for t in (a, b, c, f.grad)])
+    for got, want in zip(results[1], results[0]):
+        assert got.shape == want.shape and ERR(got, want) < 1e-6
+    assert results[1][2].is_contiguous()
+
+
+def test_status_ring_wraps_and_reports_the_right_call():
+    """More deferred status words than the library's ring holds, drained as they finish; a nonzero word in
+    the middle is raised with its own call id."""
+    from oal_b200 import hd_block_gemm_autograd as hd
+
+    hd.check_pending_status(block=True)
+    clean = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(1500):
+        hd.defer_status(clean, "probe")
+    hd.check_pending_status(block=True)
+    bad = torch.full((1,), 2, dtype=torch.int32, device="cuda")           # OAL_STATUS_DENOMINATOR
+    hd.defer_status(clean, "probe")
+    entry = hd.defer_status(bad, "marked")
+    hd.defer_status(clean, "probe")
+    with pytest.raises(RuntimeError, match=rf"marked, call {entry.call_id}\]"):
+        hd.check_pending_status(block=True)
+    hd.check_pending_status(block=True)                                     # the queue is usable afterwards
