@@ -52,7 +52,14 @@ def build_group_tables(groups: torch.Tensor, group_count: int) -> GroupTables:
     return GroupTables(perm.contiguous(), start.to(torch.int32).contiguous(), int(group_count))
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
+    """The device's current stream as a raw handle (the accessor without the Stream object when torch has it:
+    this runs four times per training step on the host's critical path)."""
+    if _RAW_STREAM is not None and device.index is not None:
+        return ctypes.c_void_p(_RAW_STREAM(device.index))
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
