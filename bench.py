@@ -461,6 +461,7 @@ def run_gpu_arm(args) -> None:
     from oal_b200.unit_sharding import unit_shard
 
     strong = None
+    strong_graph, graph_error = None, None
     try:
         shard = unit_shard(WORKLOAD["batch"], WORKLOAD["hq"], WORKLOAD["hkv"], rank, world)
     except ValueError:
@@ -493,6 +494,34 @@ def run_gpu_arm(args) -> None:
             ev.append((e0, e1))
         barrier()
         strong = sum(a_.elapsed_time(b_) for a_, b_ in ev)
+        # the same step recorded into a CUDA graph: at one or two units per rank the host needs about as long to
+        # queue a step as the GPU to run it
+        from oal_b200.captured_step import CapturedStep
+
+        captured, graph_error = None, None
+        try:
+            captured = CapturedStep(prep_s, qs, ks, vs, factor_s.detach(), ds_)
+            for _ in range(3):
+                captured.replay()
+            torch.cuda.synchronize()
+        except Exception as exc:      # reported in the line; the eager numbers above stand on their own
+            captured, graph_error = None, repr(exc)[:300]
+        ok = torch.tensor([1.0 if captured is not None else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() > 0:
+            barrier()
+            ev = []
+            for i in range(args.steps):
+                flush.fill_(i & 0xFF)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                captured.replay()
+                e1.record()
+                ev.append((e0, e1))
+            barrier()
+            strong_graph = sum(a_.elapsed_time(b_) for a_, b_ in ev)
+            captured.check_status()
 
     # ---- per-kernel breakdown (separate pass with the library's event pairs switched on)
     _lib.profile_enable(True)
@@ -504,10 +533,11 @@ def run_gpu_arm(args) -> None:
     report = _lib.profile_report()
     _lib.profile_enable(False)
 
-    times = torch.tensor([total_ms, e2e_ms, strong if strong is not None else -1.0], dtype=torch.float64, device=dev)
+    times = torch.tensor([total_ms, e2e_ms, strong if strong is not None else -1.0,
+                          strong_graph if strong_graph is not None else -1.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, strong_ms = times.tolist()
+    total_ms, e2e_ms, strong_ms, strong_graph_ms = times.tolist()
     tokens_per_step = w["batch"] * w["n"] * world
     value = tokens_per_step * args.steps / (total_ms * 1e-3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms * 1e-3)
@@ -607,6 +637,13 @@ def run_gpu_arm(args) -> None:
                                   ms_per_step=strong_ms / args.steps, units_per_rank=units / world,
                                   workload="the one B=4 call sharded by (batch row, KV head) unit; coefficient "
                                            "gradients stay per-rank partial sums")
+            if strong_graph_ms > 0:
+                line["strong"]["cuda_graph"] = dict(
+                    tokens_per_s=WORKLOAD["batch"] * WORKLOAD["n"] * args.steps / (strong_graph_ms * 1e-3),
+                    ms_per_step=strong_graph_ms / args.steps,
+                    note="the same step recorded once with oal_b200.captured_step.CapturedStep and replayed")
+            elif graph_error:
+                line["strong"]["cuda_graph"] = dict(error=graph_error)
         if cpu:
             line["cpu_baseline"] = dict(value=cpu["tokens_per_s"], unit="tokens/s", cores=cpu["threads"],
                                         kind="port", sample=cpu["sample"], host=cpu["host"])

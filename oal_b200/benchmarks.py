@@ -62,10 +62,16 @@ def sweep(ns, gs, steps: int, warmup: int) -> None:
                 out.backward(dout)
 
             ms = _time_steps(step, steps, warmup)
+            # the same step as a CUDA graph replay: short sequences are bound by the host's queueing otherwise
+            from .captured_step import CapturedStep
+
+            captured = CapturedStep(prepared, q, k, v, factor.detach(), dout)
+            graph_ms = _time_steps(captured.replay, steps, warmup)
+            captured.check_status()
             print(json.dumps(dict(benchmark="sweep", n=n, groups=g, ms_per_step=ms, ns_per_token=ms * 1e6 / n,
-                                  tokens_per_s=n / (ms * 1e-3),
+                                  tokens_per_s=n / (ms * 1e-3), cuda_graph_ms_per_step=graph_ms,
                                   intra_chunk="tcgen05" if g <= 8 else "token-pair kernels")), flush=True)
-            del q, k, v, dout, prepared
+            del q, k, v, dout, prepared, captured
             torch.cuda.empty_cache()
 
 

@@ -136,7 +136,35 @@ class PendingStatus:
         return True
 
 
-def defer_status(status: torch.Tensor, what: str = "forward", *, guarded: bool = False) -> PendingStatus:
+# Status words of calls that were recorded into a CUDA graph: nothing may be polled or copied to the host
+# while a stream is capturing, and a replay runs no Python, so these words stay on the device (they live
+# in the graph's memory pool and are rewritten by every replay) until check_captured_status() reads them.
+_CAPTURED: dict = {}
+
+
+def check_captured_status(device=None) -> None:
+    """One host synchronisation: raise if any call recorded into a CUDA graph on ``device`` (default: every
+    device) reported a problem in the replays so far.  Call it where a training loop synchronises anyway."""
+    with _PENDING_LOCK:
+        keys = list(_CAPTURED) if device is None else [torch.device(device).index if not isinstance(device, int) else device]
+        words = [(w, what) for key in keys for w, what in _CAPTURED.get(key, [])]
+    if not words:
+        return
+    values = torch.stack([w.reshape(()) for w, _ in words]).cpu().tolist()
+    for bits, (_, what) in zip(values, words):
+        _raise_for_bits(int(bits), f" [{what}, recorded in a CUDA graph]")
+
+
+def forget_captured_status(device=None) -> None:
+    """Drop the recorded words (when the graphs that own them are destroyed)."""
+    with _PENDING_LOCK:
+        if device is None:
+            _CAPTURED.clear()
+        else:
+            _CAPTURED.pop(torch.device(device).index if not isinstance(device, int) else device, None)
+
+
+def defer_status(status: torch.Tensor, what: str = "forward", *, guarded: bool = False) -> "PendingStatus | None":
     """Queue the copy of a call's status word to pinned host memory; returns the entry that owns the ticket.
 
     The copy runs on a stream of the library's own, never on the caller's: the device runs all
@@ -145,6 +173,10 @@ def defer_status(status: torch.Tensor, what: str = "forward", *, guarded: bool =
     kernels after it wait too (measured: 0.6 ms per step beside a 64 MB result copy).  ``guarded``: the
     caller already holds the device guard of ``status``."""
     device = status.device
+    if torch.cuda.is_current_stream_capturing():
+        with _PENDING_LOCK:
+            _CAPTURED.setdefault(device.index, []).append((status, what))
+        return None
     ticket = ctypes.c_int64(0)
     lib = _lib.load()
     if guarded:
@@ -168,6 +200,8 @@ def check_pending_status(block: bool = False, device=None) -> None:
 
     ``device``: a torch device / index, or None for every device.  With ``block`` the queues are
     drained completely (call it before an optimizer step when a forward ran without its backward)."""
+    if torch.cuda.is_current_stream_capturing():
+        return                  # no event may be queried while a stream is capturing
     with _PENDING_LOCK:
         keys = list(_PENDING) if device is None else [torch.device(device).index if not isinstance(device, int) else device]
     for key in keys:
@@ -235,7 +269,10 @@ def forward_impl(q, k, v, a, b, c, tables: GroupTables, scale: float, floor: flo
         _lib.check(rc)
         forward_impl.last_pending = defer_status(status, "forward", guarded=True) if check == "defer" else None
     if check and check != "defer":
-        raise_on_status(status)
+        if torch.cuda.is_current_stream_capturing():
+            defer_status(status, "forward")          # recorded: read by check_captured_status()
+        else:
+            raise_on_status(status)
     if Dv != _lib.HEAD_DIM:
         out, num = out[..., :Dv].contiguous(), num[..., :Dv].contiguous()
     if out_dtype != kernel_out:
@@ -274,7 +311,7 @@ def backward_impl(saved_inputs, num, den, saved_state, tables: GroupTables, scal
     qp, kp, vp, a32, b32, c32 = saved_inputs
     B, Hq, Hkv, N, D, Dv = plan.geometry
     dev = qp.device
-    if forward_status is not None:
+    if forward_status is not None and not torch.cuda.is_current_stream_capturing():
         forward_status.check(block=False)      # this call's own forward, if it has finished: raise before launching
     check_pending_status(device=dev)
     kernel_out, num_p, den_c, go, gn, gd = backward_operands(plan, num, den, grad_out, grad_num, grad_den)

@@ -134,7 +134,8 @@ class _SequenceParallelFunction(torch.autograd.Function):
         if grad_output is None and grad_numerator is None and grad_denominator is None:
             return (None,) * 9
         if ctx.forward_status is not None:
-            ctx.forward_status.check(block=False)    # this call's own forward, if it has finished
+            if not torch.cuda.is_current_stream_capturing():
+                ctx.forward_status.check(block=False)    # this call's own forward, if it has finished
         ws = torch.empty(max(plan.backward_workspace_bytes, 16), dtype=torch.uint8, device=num.device)
         local = local_dstate_total(padded, num, den, state, prepared.tables, prepared.scale,
                                    prepared.normalization_floor, plan, mask, grad_output, grad_numerator,
