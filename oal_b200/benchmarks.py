@@ -75,7 +75,7 @@ def sweep(ns, gs, steps: int, warmup: int) -> None:
             torch.cuda.empty_cache()
 
 
-def sequence_parallel(n: int, steps: int, warmup: int) -> None:
+def sequence_parallel(n: int, steps: int, warmup: int, cuda_graph: bool = False) -> None:
     import torch.distributed as dist
 
     from .sequence_parallel import sequence_parallel_attention
@@ -108,18 +108,54 @@ def sequence_parallel(n: int, steps: int, warmup: int) -> None:
         exclusive_prefix_over_ranks(state, None)
         exclusive_prefix_over_ranks(state, None, reverse=True)
 
-    ms = torch.tensor([_time_steps(step, steps, warmup), _time_steps(exchange, steps, warmup)], device=dev,
-                      dtype=torch.float64)
+    eager_ms, exchange_only_ms = _time_steps(step, steps, warmup), _time_steps(exchange, steps, warmup)
+    graph_ms, graph_error = -1.0, None
+    if cuda_graph:
+        # the rank's whole step, both all-gathers included, recorded once and replayed: recording queues nothing,
+        # so a rank whose capture fails cannot leave the others waiting; the ranks vote before anyone replays
+        graph = torch.cuda.CUDAGraph()
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    step()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            q.grad = k.grad = v.grad = factor.grad = None
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                step()
+            recorded = 1.0
+        except Exception as exc:
+            recorded, graph_error = 0.0, repr(exc)[:300]
+        vote = torch.tensor([recorded], device=dev)
+        if world > 1:
+            dist.all_reduce(vote, op=dist.ReduceOp.MIN)
+        if vote.item() > 0:
+            graph_ms = _time_steps(graph.replay, steps, warmup)
+            from .hd_block_gemm_autograd import check_captured_status
+
+            check_captured_status(dev)
+    ms = torch.tensor([eager_ms, exchange_only_ms, graph_ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if rank == 0:
-        step_ms, exchange_ms = ms.tolist()
+        step_ms, exchange_ms, graph_ms = ms.tolist()
+        extra = {}
+        if cuda_graph:
+            extra = (dict(cuda_graph_ms_per_step=graph_ms, cuda_graph_tokens_per_s=n / (graph_ms * 1e-3)) if graph_ms > 0
+                     else dict(cuda_graph_error=graph_error or "capture failed on another rank"))
         print(json.dumps(dict(benchmark="sequence_parallel", n=n, ranks=world, ms_per_step=step_ms,
-                              tokens_per_s=n / (step_ms * 1e-3),
+                              tokens_per_s=n / (step_ms * 1e-3), **extra,
                               exchange_ms_per_step=exchange_ms, exchange_share=exchange_ms / step_ms,
                               exchange_bytes_per_rank_per_direction=2 * _lib.STATE_ROWS * _lib.E_PAD * 4,
                               collective="one all-gather of the range-final fp32 states per direction (NCCL), "
                                          "summed locally in rank order")), flush=True)
+    if cuda_graph:
+        # a recorded graph holds the communicator's kernels: release it before the process group is torn down
+        # (with the graph alive, the teardown waited until the launcher's timeout)
+        graph.reset()
+        del graph
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -192,12 +228,13 @@ def main():
     ap.add_argument("--groups", default="1,4,8,16")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--cuda-graph", action="store_true", help="sp: also time the step as a CUDA graph replay")
     a = ap.parse_args()
     if a.mode == "sweep":
         ns = [int(x) for x in (a.seq or "1024,4096,16384,65536").split(",")]
         sweep(ns, [int(x) for x in a.groups.split(",")], a.steps, a.warmup)
     elif a.mode == "sp":
-        sequence_parallel(int(a.seq or 32768), a.steps, a.warmup)
+        sequence_parallel(int(a.seq or 32768), a.steps, a.warmup, a.cuda_graph)
     else:
         training_step(a.layers, a.batch, int(a.seq or 4096), a.steps, a.warmup)
 
