@@ -466,23 +466,37 @@ def run_gpu_arm(args) -> None:
         shard = unit_shard(WORKLOAD["batch"], WORKLOAD["hq"], WORKLOAD["hkv"], rank, world)
     except ValueError:
         shard = None
+    strong_error = None
+    ready = 0.0
     if shard is not None and args.batch == WORKLOAD["batch"]:
-        case_s = synthetic.qwen_head_case(0, bf16=True, **WORKLOAD)      # the same inputs on every rank, cut locally
-        qs, ks, vs, ds_ = (t.to(dev, torch.bfloat16) for t in shard.take(case_s.q, case_s.k, case_s.v, case_s.grad_out))
-        factor_s = shard.factor_rows(case_s.factor).to(dev).requires_grad_()
-        prep_s = oal_b200.prepare_grouped_hd_block_gemm(qs.clone().requires_grad_(), ks.clone().requires_grad_(),
-                                                        vs.clone().requires_grad_(), groups, factor_s,
-                                                        scale=case_s.scale, kernel_eps=case_s.kernel_eps,
-                                                        precision=precision, token_block=64, feature_wave_blocks=4)
+        # set-up and warm-up under a guard: a failure here must not take the headline numbers above with it,
+        # and the ranks agree on whether to go on before anyone enters the timed loop
+        try:
+            case_s = synthetic.qwen_head_case(0, bf16=True, **WORKLOAD)      # the same inputs on every rank, cut locally
+            qs, ks, vs, ds_ = (t.to(dev, torch.bfloat16).contiguous()
+                               for t in shard.take(case_s.q, case_s.k, case_s.v, case_s.grad_out))
+            factor_s = shard.factor_rows(case_s.factor).to(dev).requires_grad_()
+            prep_s = oal_b200.prepare_grouped_hd_block_gemm(qs.clone().requires_grad_(), ks.clone().requires_grad_(),
+                                                            vs.clone().requires_grad_(), groups, factor_s,
+                                                            scale=case_s.scale, kernel_eps=case_s.kernel_eps,
+                                                            precision=precision, token_block=64, feature_wave_blocks=4)
 
-        def step_s():
-            q_, k_, v_ = (t.detach().requires_grad_() for t in (qs, ks, vs))
-            factor_s.grad = None
-            out_, _, _ = oal_b200.run_prepared_grouped_hd_block_gemm(prep_s, q_, k_, v_, factor_s)
-            out_.backward(ds_)
+            def step_s():
+                q_, k_, v_ = (t.detach().requires_grad_() for t in (qs, ks, vs))
+                factor_s.grad = None
+                out_, _, _ = oal_b200.run_prepared_grouped_hd_block_gemm(prep_s, q_, k_, v_, factor_s)
+                out_.backward(ds_)
 
-        for _ in range(max(args.warmup, 3)):
-            step_s()
+            for _ in range(max(args.warmup, 3)):
+                step_s()
+            torch.cuda.synchronize()
+            ready = 1.0
+        except Exception as exc:
+            strong_error = repr(exc)[:300]
+    vote = torch.tensor([ready], device=dev)
+    if world > 1:
+        dist.all_reduce(vote, op=dist.ReduceOp.MIN)
+    if vote.item() > 0:
         barrier()
         ev = []
         for i in range(args.steps):
@@ -644,6 +658,8 @@ def run_gpu_arm(args) -> None:
                     note="the same step recorded once with oal_b200.captured_step.CapturedStep and replayed")
             elif graph_error:
                 line["strong"]["cuda_graph"] = dict(error=graph_error)
+        elif strong_error:
+            line["strong"] = dict(error=strong_error)
         if cpu:
             line["cpu_baseline"] = dict(value=cpu["tokens_per_s"], unit="tokens/s", cores=cpu["threads"],
                                         kind="port", sample=cpu["sample"], host=cpu["host"])

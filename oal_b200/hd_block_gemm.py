@@ -160,7 +160,10 @@ def _validate_geometry(q, k, v):
     if any(t.layout != torch.strided for t in (q, k, v)):
         raise ValueError("Q, K, and V must use torch.strided layout")
     for t in (q, k, v):
-        if tuple(t.stride()) != _contiguous_strides(tuple(t.shape)):
+        # the stride of a dimension of size 1 addresses nothing (a slice of one KV head keeps its parent's): only
+        # the dimensions that are walked must have the row-major strides
+        want = _contiguous_strides(tuple(t.shape))
+        if any(n > 1 and have != need for n, have, need in zip(t.shape, t.stride(), want)):
             raise ValueError("Q, K, and V must use exact row-major contiguous layout")
     b, hq, n, d = q.shape
     kb, hkv, kn, kd = k.shape

@@ -73,3 +73,21 @@ def test_two_gloo_ranks_reassemble_the_whole_call(tmp_path):
     for key in ("out", "dq", "dk", "dv"):
         assert torch.allclose(torch.cat([p[key] for p in parts], dim=1), whole[key], rtol=1e-12, atol=1e-12), key
     assert torch.allclose(torch.cat([p["dA"] for p in parts]), whole["dA"], rtol=1e-12, atol=1e-12)
+
+
+def test_single_unit_shards_pass_the_plan_layout_check():
+    """One (batch row, KV head) unit per rank: the shard has two dimensions of size 1, whose strides are
+    whatever the slice left them (`.contiguous()` returns such a tensor unchanged); the plan must take it."""
+    from oal_b200.hd_block_gemm import build_hd_block_gemm_plan
+
+    q = torch.randn(4, 14, 256, 64)
+    k = torch.randn(4, 2, 256, 64)
+    v = torch.randn(4, 2, 256, 64)
+    shard = unit_shard(4, 14, 2, rank=5, world=8)
+    qs, ks, vs = shard.take(q, k, v)
+    assert ks.shape == (1, 1, 256, 64) and ks.is_contiguous()
+    plan = build_hd_block_gemm_plan(qs, ks, vs, requested_gradient_mask=(False,) * 6)
+    assert plan.geometry[:3] == (1, 7, 1)
+    bad = q.transpose(2, 3).contiguous().transpose(2, 3)[:1, :7]
+    with pytest.raises(ValueError, match="row-major"):
+        build_hd_block_gemm_plan(bad, ks, vs, requested_gradient_mask=(False,) * 6)
