@@ -42,9 +42,14 @@ def main():
     o2, n2, d2 = oal_b200.grouped_causal_attention(qf, kf, vf, groups, f2, scale=case.scale,
                                                    precision="bf16_tensorcore")
     o2.backward(dout)
-    errs = dict(out=ERR(out, o2[:, :, sl]), num=ERR(num, n2[:, :, sl]), den=ERR(den, d2[:, :, sl]),
-                dq=ERR(qr.grad, qf.grad[:, :, sl]), dk=ERR(kr.grad, kf.grad[:, :, sl]),
-                dv=ERR(vr.grad, vf.grad[:, :, sl]), dfactor=ERR(factor.grad, f2.grad))
+    # normalised by the size of the WHOLE single-GPU result, as every other comparison of the suite is: a
+    # rank's own range can hold much smaller values than the sequence's maximum (with 8 ranks some do)
+    def err(part, whole):
+        whole = whole.detach().float()
+        return ((part.detach().float() - whole[:, :, sl]).abs().max() / whole.abs().max().clamp_min(1e-30)).item()
+
+    errs = dict(out=err(out, o2), num=err(num, n2), den=err(den, d2), dq=err(qr.grad, qf.grad), dk=err(kr.grad, kf.grad),
+                dv=err(vr.grad, vf.grad), dfactor=ERR(factor.grad, f2.grad))
     bad = {k_: e for k_, e in errs.items() if not e < 5e-3}
     if n == 32768:
         # the reference's own rows (every 1024th token): this rank checks the ones that fall into its range
@@ -62,6 +67,8 @@ def main():
             errs["ref_" + key] = diff
             if not diff < 2e-2:
                 bad["ref_" + key] = diff
+    if bad:
+        print(f"rank {rank} out of tolerance: {bad}", flush=True)
     flag = torch.tensor([len(bad)], device=dev)
     dist.all_reduce(flag)
     if rank == 0:
