@@ -165,10 +165,11 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
     // ---------------- drain warps ----------------
     const int fr = 32 * (warp & 3) + lane, ch = (warp - DS_GEN_WARPS) >> 2, col0 = ch * DS_COLS;
     const uint32_t lane_off = (uint32_t)(32 * (warp & 3)) << 16;
-    float acc[DS_COLS];            // this thread's part of the dCarry row, summed over the heads of the item
-    float carry[DS_COLS];          // this thread's part of the carry row (value + remainder), fp32, once per item
+    // packed fp32 pairs: the drain is bound by issue slots, and a packed multiply-add is one slot for two columns
+    f32x2 acc[DS_COLS / 2];        // this thread's part of the dCarry row, summed over the heads of the item
+    f32x2 carry[DS_COLS / 2];      // this thread's part of the carry row (value + remainder), fp32, once per item
 #pragma unroll
-    for (int j = 0; j < DS_COLS; ++j) carry[j] = 0.f;
+    for (int j = 0; j < DS_COLS / 2; ++j) carry[j] = 0ull;
     DsCursor d, dn;
     d.start(a.NB, a.Hkv, rep);
     dn = d;
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
           unpack_bf16x8(cpk[e], c0);
           unpack_bf16x8(cpl[e], c1);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) carry[8 * e + j] = c0[j] + c1[j];
+          for (int j = 0; j < 4; ++j) carry[4 * e + j] = f2_pack(c0[2 * j] + c1[2 * j], c0[2 * j + 1] + c1[2 * j + 1]);
         }
       }
       w.wait(&mma_done[s], use & 1, 0x32);
@@ -206,9 +207,10 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
       const uint32_t tz = tmem_base + EP * s + col0;
       if (d.hh == 0) {
 #pragma unroll
-        for (int j = 0; j < DS_COLS; ++j) acc[j] = 0.f;
+        for (int j = 0; j < DS_COLS / 2; ++j) acc[j] = 0ull;
       }
-      float dot[4] = {0.f, 0.f, 0.f, 0.f};
+      f32x2 dot[2] = {0ull, 0ull};
+      const f32x2 cf2 = f2_bcast(cf);
       // two register stages: the loads of the next 8 columns are in flight while these are combined
       float z[2][8];
       tmem_ld8(tz + lane_off, z[0]);
@@ -217,25 +219,32 @@ __global__ void __launch_bounds__(DS_THREADS, 1) dstate_heads_kernel(const DStat
         tmem_ld_wait();
         if (r + 1 < DS_COLS / 8) tmem_ld8(tz + lane_off + 8 * (r + 1), z[(r + 1) & 1]);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          dot[j & 3] = fmaf(z[r & 1][j], carry[8 * r + j], dot[j & 3]);
-          acc[8 * r + j] = fmaf(cf, z[r & 1][j], acc[8 * r + j]);
+        for (int j = 0; j < 4; ++j) {
+          const f32x2 z2 = f2_pack(z[r & 1][2 * j], z[r & 1][2 * j + 1]);
+          dot[j & 1] = f2_fma(z2, carry[4 * r + j], dot[j & 1]);
+          acc[4 * r + j] = f2_fma(cf2, z2, acc[4 * r + j]);
         }
       }
       fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&z_free[s]);      // every lane has its Z values in registers
+      float d0, d1, d2, d3;
+      f2_unpack(dot[0], d0, d1);
+      f2_unpack(dot[1], d2, d3);
+      const float dot_sum = (d0 + d2) + (d1 + d3);
       if (a.dcoef_partial)      // one partial per column half, summed by the reduction over (batch, chunk, half)
         a.dcoef_partial[((((size_t)b * a.NB + d.c) * 2 + ch) * a.Hq + h) * F_ROWS + f] =
-            fs * ((dot[0] + dot[1]) + (dot[2] + dot[3]));
+            fs * dot_sum;
       if (d.hh == rep - 1) {
         // dCarry rows of this slab -> HBM; the next group of 8 columns of a row lies one 128-row block further
         float* dst = a.dcarry + ((size_t)d.u * a.NB + d.c) * F_ROWS * EP + state_inc_offset(f, col0);
 #pragma unroll
         for (int r = 0; r < DS_COLS / 8; ++r) {
-          *reinterpret_cast<float4*>(dst + r * 1024) = make_float4(acc[8 * r], acc[8 * r + 1], acc[8 * r + 2], acc[8 * r + 3]);
-          *reinterpret_cast<float4*>(dst + r * 1024 + 4) =
-              make_float4(acc[8 * r + 4], acc[8 * r + 5], acc[8 * r + 6], acc[8 * r + 7]);
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) f2_unpack(acc[4 * r + j], o[2 * j], o[2 * j + 1]);
+          *reinterpret_cast<float4*>(dst + r * 1024) = make_float4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<float4*>(dst + r * 1024 + 4) = make_float4(o[4], o[5], o[6], o[7]);
         }
       }
       d = dn;
