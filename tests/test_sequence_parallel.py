@@ -133,3 +133,68 @@ def test_nccl_sequence_parallel_at_configured_length():
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "SP_OK" in res.stdout
+
+
+@pytest.mark.gpu
+def test_eight_rank_emulation_at_configured_length_against_reference_golden():
+    """The sequence-parallel configuration itself (N = 32768 cut into 8 ranges of 4096 tokens) with the ranks'
+    kernels run one after another on one GPU and the states passed by hand: against one call over the whole
+    sequence (errors normalised by the whole result) and against the stored rows of the reference's chunked
+    fp32 path (tests/golden/long_rows.npz).  The NCCL test runs the same ranges on real ranks when the box has
+    more than one GPU."""
+    import numpy as np
+
+    import oal_b200
+    from oal_b200.grouped_quadratic import _expand_factor_coefficients
+    from oal_b200.hd_block_gemm_adapters import prepare_grouped_hd_block_gemm
+    from oal_b200.hd_block_gemm_autograd import backward_impl, forward_impl
+    from oal_b200.sequence_parallel import local_dstate_total, local_state_total
+
+    world, n, dev = 8, 32768, "cuda"
+    case = synthetic.qwen_head_case(7, batch=1, n=n, hq=14, hkv=2, g=8, bf16=True)
+    q, k, v, dout = (t.to(dev, torch.bfloat16) for t in (case.q, case.k, case.v, case.grad_out))
+    groups, factor = case.dim_groups.to(dev), case.factor.to(dev).requires_grad_()
+    qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+    out, num, den = oal_b200.grouped_causal_attention(qf, kf, vf, groups, factor, scale=case.scale,
+                                                      precision="bf16_tensorcore")
+    out.backward(dout)
+    full = dict(out=out, num=num, den=den, dq=qf.grad, dk=kf.grad, dv=vf.grad)
+    a, b, c = (t.detach().contiguous() for t in _expand_factor_coefficients(
+        case.factor.to(dev), query_heads=14, gmax=8, kernel_eps=case.kernel_eps, working_dtype=torch.float32))
+    mask, ranks = (True,) * 6, []
+    for r in range(world):
+        sl = slice(r * n // world, (r + 1) * n // world)
+        qr, kr, vr = (t[:, :, sl].contiguous().requires_grad_() for t in (q, k, v))
+        prep = prepare_grouped_hd_block_gemm(qr, kr, vr, groups, factor, scale=case.scale, precision="bf16_tensorcore")
+        ranks.append(dict(q=qr, k=kr, v=vr, prep=prep, sl=sl, total=local_state_total(kr, vr, prep.plan, prep.gmax)))
+    for r, st in enumerate(ranks):
+        p = st["prep"]
+        state_in = sum((x["total"] for x in ranks[:r]), torch.zeros_like(st["total"]))
+        st["fwd"] = forward_impl(st["q"], st["k"], st["v"], a, b, c, p.tables, p.scale, p.normalization_floor, p.plan,
+                                 state_in=state_in)
+    for st in ranks:
+        p = st["prep"]
+        _, nm, dn, saved, padded = st["fwd"]
+        st["ws"] = torch.empty(p.plan.backward_workspace_bytes, dtype=torch.uint8, device=dev)
+        st["dtotal"] = local_dstate_total(padded, nm, dn, saved, p.tables, p.scale, p.normalization_floor, p.plan, mask,
+                                          dout[:, :, st["sl"]].contiguous(), None, None, st["ws"])
+    parts = dict(out=[], num=[], den=[], dq=[], dk=[], dv=[])
+    for r, st in enumerate(ranks):
+        p = st["prep"]
+        o, nm, dn, saved, padded = st["fwd"]
+        dstate_in = sum((x["dtotal"] for x in ranks[r + 1:]), torch.zeros_like(st["dtotal"]))
+        dq, dk, dv, _, _, _ = backward_impl(padded, nm, dn, saved, p.tables, p.scale, p.normalization_floor, p.plan, mask,
+                                            dout[:, :, st["sl"]].contiguous(), None, None, dstate_in=dstate_in,
+                                            workspace=st["ws"], reuse_state_stage=True)
+        for key, val in dict(out=o, num=nm, den=dn, dq=dq, dk=dk, dv=dv).items():
+            parts[key].append(val)
+    got = {key: torch.cat(vals, dim=2).detach().float() for key, vals in parts.items()}
+    for key, val in got.items():
+        whole = full[key].detach().float()
+        assert ((val - whole).abs().max() / whole.abs().max()).item() < 5e-3, key
+    with np.load(ROOT / "tests" / "golden" / "long_rows.npz") as z:
+        stride = int(z["row_stride"])
+        for key, val in got.items():
+            gold = torch.from_numpy(z["hd_" + key].astype("float64"))
+            rows = val[:, :, ::stride].double().cpu()
+            assert ((rows - gold).abs().max() / gold.abs().max()).item() < 2e-2, key
