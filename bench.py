@@ -376,6 +376,8 @@ def run_gpu_arm(args) -> None:
     def views(buf):
         return {n_: buf[o:o + z].view(sh) for n_, o, z, sh in zip(names, offs, sizes, shapes)}
 
+    held = [None, None]
+
     def e2e_loop(n_steps):
         for i in range(n_steps):
             slot = i % 2
@@ -387,13 +389,16 @@ def run_gpu_arm(args) -> None:
             compute.wait_event(out_done[slot])                  # the download that last read dev_out[slot]
             flush.fill_(i & 0xFF)
             results = step(views(dev_in[slot]))
-            for r_, o, z in zip(results, out_offs, out_sizes):
-                dev_out[slot][o:o + z].copy_(r_.reshape(-1))
             compute_done[slot].record(compute)
-            with torch.cuda.stream(copy_out):
+            with torch.cuda.stream(copy_out):                   # packing and download beside the next step's kernels
                 copy_out.wait_event(compute_done[slot])
+                for r_, o, z in zip(results, out_offs, out_sizes):
+                    dev_out[slot][o:o + z].copy_(r_.reshape(-1))
                 host_out[slot].copy_(dev_out[slot], non_blocking=True)
                 out_done[slot].record(copy_out)
+            # the step's result tensors stay allocated until their packing copies have run: the slot's previous
+            # results are dropped only here, after this step waited for out_done[slot] on the compute stream
+            held[slot] = results
         enqueued = time.perf_counter()
         torch.cuda.synchronize()
         return enqueued
